@@ -1,0 +1,106 @@
+// Shared device and host helpers of every kernel file.
+//
+// Conventions (the same as x0ne-core/kernels/cuda/x0ne_kernels.h:1-3 states for its
+// kernels): C linkage for every entry point, row-major tensors, 32-bit accumulation,
+// token ids / positions / slots read from device memory, and every index checked without
+// trapping: an id outside the vocabulary gives a zero row, a position with no page writes
+// nothing.  Reductions run in a fixed order, so a row's result does not depend on what else
+// is in the launch (x0ne-core/kernels/cuda/common.cuh:1,24-44).
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <math.h>
+#include <stdint.h>
+
+typedef __nv_bfloat16 bf16;
+
+#define X0NE_API extern "C" __attribute__((visibility("default")))
+
+// dtype tags of the C interface
+#define X0NE_F32 0
+#define X0NE_BF16 1
+
+// Error codes of the C interface (0 = ok; positive values below 10000 are cudaError_t).
+#define X0NE_ERR_ARG 10001
+
+void x0ne_set_error(const char* fmt, ...);
+
+#define X0NE_REQUIRE(cond, ...)            \
+    do {                                   \
+        if (!(cond)) {                     \
+            x0ne_set_error(__VA_ARGS__);   \
+            return X0NE_ERR_ARG;           \
+        }                                  \
+    } while (0)
+
+#define X0NE_LAUNCH_CHECK()                                          \
+    do {                                                             \
+        cudaError_t e_ = cudaGetLastError();                         \
+        if (e_ != cudaSuccess) {                                     \
+            x0ne_set_error("%s:%d: %s", __FILE__, __LINE__, cudaGetErrorString(e_)); \
+            return (int)e_;                                          \
+        }                                                            \
+        return 0;                                                    \
+    } while (0)
+
+__device__ __forceinline__ float to_f32(float x) { return x; }
+__device__ __forceinline__ float to_f32(bf16 x) { return __bfloat162float(x); }
+template <typename T> __device__ __forceinline__ T from_f32(float x);
+template <> __device__ __forceinline__ float from_f32<float>(float x) { return x; }
+template <> __device__ __forceinline__ bf16 from_f32<bf16>(float x) { return __float2bfloat16_rn(x); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Sum over the block (blockDim.x a multiple of 32, at most 1024); every thread gets it.
+// `sh` holds 32 floats.  The order is fixed by blockDim alone.
+__device__ __forceinline__ float block_sum(float v, float* sh) {
+    v = warp_sum(v);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    __syncthreads();
+    if (lane == 0) sh[warp] = v;
+    __syncthreads();
+    return warp_sum(lane < nw ? sh[lane] : 0.f);
+}
+
+__device__ __forceinline__ float block_max(float v, float* sh) {
+    v = warp_max(v);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    __syncthreads();
+    if (lane == 0) sh[warp] = v;
+    __syncthreads();
+    return warp_max(lane < nw ? sh[lane] : -INFINITY);
+}
+
+// The paged cache of one run-order entry.  A page holds `page_size` positions of every kv
+// head, K then V: [2][kv_heads][page_size][head_dim].  A sequence's logical page
+// (pos / page_size) % ring_pages is found in its row of the page table.
+struct PagedCache {
+    void* base;                 // first page of this entry
+    const int32_t* page_table;  // [slots][table_stride]
+    int64_t page_stride;        // elements between consecutive pages
+    int32_t table_stride;
+    int32_t ring_pages;         // logical pages wrap at this count (= table_stride for a full cache)
+    int32_t page_size;
+    int32_t kv_heads;
+    int32_t head_dim;
+    int32_t n_pages;            // pages in the pool, for the bounds check
+};
+
+// Element offset of (slot, pos, kv head, which = 0 for K / 1 for V); -1 if there is no page.
+__device__ __forceinline__ int64_t cache_row_offset(const PagedCache& c, int slot, int pos, int kv_head, int which) {
+    const int lp = (pos / c.page_size) % c.ring_pages;
+    const int page = c.page_table[(int64_t)slot * c.table_stride + lp];
+    if (page < 0 || page >= c.n_pages) return -1;
+    return (int64_t)page * c.page_stride +
+           (((int64_t)which * c.kv_heads + kv_head) * c.page_size + (pos % c.page_size)) * c.head_dim;
+}

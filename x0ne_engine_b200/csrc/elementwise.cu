@@ -1,0 +1,227 @@
+// Row-wise kernels: embedding, residual add + RMSNorm, q/k head norm + RoPE + cache write,
+// SwiGLU.  Each is templated on the activation type (float for the 32-bit path, bfloat16 for
+// the serving path); per-channel weights are always float32.
+#include <stdarg.h>
+#include <stdio.h>
+
+#include "common.cuh"
+
+static thread_local char g_error[512];
+
+void x0ne_set_error(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_error, sizeof g_error, fmt, ap);
+    va_end(ap);
+}
+
+X0NE_API const char* x0ne_last_error() { return g_error; }
+
+// ----------------------------------------------------------------------------------------
+// Embedding: resid[r] = f32(table[tokens[r]]); an id outside the table gives a zero row
+// (x0ne-core/kernels/cuda/embedding.cu:5-17).  The engine there copies the row and lets the
+// first add-norm add it to a zeroed residual (x0ne-core/runtime/src/engine.rs:744-745); here
+// the row is written straight into the float32 residual, which is the same value.
+// ----------------------------------------------------------------------------------------
+template <typename T>
+__global__ void embedding_kernel(const T* __restrict__ table, const int32_t* __restrict__ tokens,
+                                 float* __restrict__ resid, int hidden, int vocab) {
+    const int row = blockIdx.x;
+    const int t = tokens[row];
+    float* dst = resid + (int64_t)row * hidden;
+    if (t < 0 || t >= vocab) {
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = 0.f;
+        return;
+    }
+    const T* src = table + (int64_t)t * hidden;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = to_f32(src[i]);
+}
+
+X0NE_API int x0ne_embedding(const void* table, int dt, const int32_t* tokens, float* resid, int n_rows,
+                            int hidden, int vocab, cudaStream_t stream) {
+    X0NE_REQUIRE(n_rows >= 0 && hidden > 0 && vocab > 0, "embedding: rows %d hidden %d vocab %d", n_rows, hidden, vocab);
+    if (n_rows == 0) return 0;
+    const int block = hidden >= 1024 ? 256 : 128;
+    if (dt == X0NE_F32)
+        embedding_kernel<float><<<n_rows, block, 0, stream>>>((const float*)table, tokens, resid, hidden, vocab);
+    else if (dt == X0NE_BF16)
+        embedding_kernel<bf16><<<n_rows, block, 0, stream>>>((const bf16*)table, tokens, resid, hidden, vocab);
+    else
+        X0NE_REQUIRE(false, "embedding: unknown dtype tag %d", dt);
+    X0NE_LAUNCH_CHECK();
+}
+
+// ----------------------------------------------------------------------------------------
+// Residual add, then RMSNorm: r = resid + f32(delta) (one IEEE add, stored back);
+// out = T(r * rsqrt(mean(r^2) + eps) * w)  (x0ne-core/kernels/cuda/rmsnorm.cu:11-20; eps is
+// inside the root; the weight multiplies directly).  `delta` may be null (norm only).
+// `rows`, if given, lists the source rows to process; output row i then belongs to source row
+// rows[i] (used to norm only the rows whose logits are wanted).
+// One block per row; the sum of squares is a fixed-order block sum.
+// ----------------------------------------------------------------------------------------
+template <typename T>
+__global__ void add_rmsnorm_kernel(float* __restrict__ resid, const T* __restrict__ delta,
+                                   const float* __restrict__ w, T* __restrict__ out,
+                                   const int32_t* __restrict__ rows, int hidden, float eps) {
+    __shared__ float sh[32];
+    const int64_t src = rows ? rows[blockIdx.x] : blockIdx.x;
+    float* r = resid + src * hidden;
+    const T* d = delta ? delta + src * hidden : nullptr;
+    T* o = out + (int64_t)blockIdx.x * hidden;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        float v = r[i];
+        if (d) {
+            v = v + to_f32(d[i]);
+            r[i] = v;
+        }
+        ss += v * v;
+    }
+    const float total = block_sum(ss, sh);
+    const float scale = 1.0f / sqrtf(total / (float)hidden + eps);
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = from_f32<T>(r[i] * scale * w[i]);
+}
+
+X0NE_API int x0ne_add_rmsnorm(float* resid, const void* delta, const float* w, void* out, int dt,
+                              const int32_t* rows, int n_rows, int hidden, float eps, cudaStream_t stream) {
+    X0NE_REQUIRE(n_rows >= 0 && hidden > 0, "add_rmsnorm: rows %d hidden %d", n_rows, hidden);
+    if (n_rows == 0) return 0;
+    const int block = 256;
+    if (dt == X0NE_F32)
+        add_rmsnorm_kernel<float><<<n_rows, block, 0, stream>>>(resid, (const float*)delta, w, (float*)out, rows, hidden, eps);
+    else if (dt == X0NE_BF16)
+        add_rmsnorm_kernel<bf16><<<n_rows, block, 0, stream>>>(resid, (const bf16*)delta, w, (bf16*)out, rows, hidden, eps);
+    else
+        X0NE_REQUIRE(false, "add_rmsnorm: unknown dtype tag %d", dt);
+    X0NE_LAUNCH_CHECK();
+}
+
+// ----------------------------------------------------------------------------------------
+// Per-head RMSNorm of q and k (optional), rotate-half RoPE, and the K/V write into the
+// paged cache (x0ne-core/kernels/cuda/rope.cu:7-47).  One warp per (row, head); heads
+// 0..q_heads-1 are q heads, the rest k heads, whose warps also copy the v head.
+//   scale = rsqrt(mean(x^2 over head_dim) + eps); n = x * scale * w
+//   angle = (float)pos * inv_freq[i]; (a, b) = (n[i], n[i + rot/2])
+//   out[i] = a cos - b sin; out[i + rot/2] = b cos + a sin; dims >= rot pass through.
+// `norm_q`/`norm_k` null: no head norm.  rot == 0: no rotation.
+// A row whose position has no page writes nothing into the cache.
+// ----------------------------------------------------------------------------------------
+template <typename T>
+__global__ void qk_norm_rope_kv_write_kernel(const T* __restrict__ qkv, const float* __restrict__ norm_q,
+                                             const float* __restrict__ norm_k,
+                                             const float* __restrict__ inv_freq, int rot, T* __restrict__ q_out,
+                                             PagedCache cache, const int32_t* __restrict__ row_slot,
+                                             const int32_t* __restrict__ row_pos, int n_rows, int q_heads,
+                                             float eps, int write_kv) {
+    const int lane = threadIdx.x & 31;
+    const int heads = q_heads + cache.kv_heads;
+    const int64_t item = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (item >= (int64_t)n_rows * heads) return;
+    const int row = (int)(item / heads), head = (int)(item % heads);
+    const int hd = cache.head_dim, half = rot >> 1;
+    const int q_dim = q_heads * hd, kv_dim = cache.kv_heads * hd;
+    const bool is_q = head < q_heads;
+    const int kh = is_q ? 0 : head - q_heads;
+    if (!is_q && !write_kv) return;
+    const T* src = qkv + (int64_t)row * (q_dim + 2 * kv_dim) + (is_q ? head * hd : q_dim + kh * hd);
+    const float* nw = is_q ? norm_q : norm_k;
+    const int pos = row_pos[row];
+
+    float scale = 1.f;
+    if (nw) {
+        float ss = 0.f;
+        for (int i = lane; i < hd; i += 32) {
+            const float x = to_f32(src[i]);
+            ss += x * x;
+        }
+        ss = warp_sum(ss);
+        scale = 1.0f / sqrtf(ss / (float)hd + eps);
+    }
+
+    T* dst;
+    if (is_q) {
+        dst = q_out + (int64_t)row * q_dim + head * hd;
+    } else {
+        const int64_t off = cache_row_offset(cache, row_slot[row], pos, kh, 0);
+        if (off < 0) return;
+        dst = (T*)cache.base + off;
+    }
+    for (int i = lane; i < half; i += 32) {
+        float a = to_f32(src[i]), b = to_f32(src[i + half]);
+        if (nw) {
+            a = a * scale * nw[i];
+            b = b * scale * nw[i + half];
+        }
+        float s, c;
+        sincosf((float)pos * inv_freq[i], &s, &c);
+        dst[i] = from_f32<T>(a * c - b * s);
+        dst[i + half] = from_f32<T>(b * c + a * s);
+    }
+    for (int i = rot + lane; i < hd; i += 32) {
+        float a = to_f32(src[i]);
+        if (nw) a = a * scale * nw[i];
+        dst[i] = from_f32<T>(a);
+    }
+    if (!is_q) {
+        const T* vs = src + kv_dim;
+        T* vd = dst + (int64_t)cache.kv_heads * cache.page_size * hd;
+        for (int i = lane; i < hd; i += 32) vd[i] = vs[i];
+    }
+}
+
+X0NE_API int x0ne_qk_norm_rope_kv_write(const void* qkv, int dt, const float* norm_q, const float* norm_k,
+                                        const float* inv_freq, int rotary_dim, void* q_out, PagedCache cache,
+                                        const int32_t* row_slot, const int32_t* row_pos, int n_rows, int q_heads,
+                                        float eps, int write_kv, cudaStream_t stream) {
+    X0NE_REQUIRE(n_rows >= 0 && q_heads > 0 && cache.kv_heads > 0 && cache.head_dim > 0, "rope: bad sizes");
+    X0NE_REQUIRE(rotary_dim >= 0 && rotary_dim % 2 == 0 && rotary_dim <= cache.head_dim,
+                 "rope: rotary_dim %d must be even and at most head_dim %d", rotary_dim, cache.head_dim);
+    X0NE_REQUIRE(rotary_dim == 0 || inv_freq != nullptr, "rope: no inv_freq table");
+    if (n_rows == 0) return 0;
+    const int warps = 4;
+    const int64_t items = (int64_t)n_rows * (q_heads + cache.kv_heads);
+    const unsigned grid = (unsigned)((items + warps - 1) / warps);
+    if (dt == X0NE_F32)
+        qk_norm_rope_kv_write_kernel<float><<<grid, warps * 32, 0, stream>>>(
+            (const float*)qkv, norm_q, norm_k, inv_freq, rotary_dim, (float*)q_out, cache, row_slot, row_pos, n_rows,
+            q_heads, eps, write_kv);
+    else if (dt == X0NE_BF16)
+        qk_norm_rope_kv_write_kernel<bf16><<<grid, warps * 32, 0, stream>>>(
+            (const bf16*)qkv, norm_q, norm_k, inv_freq, rotary_dim, (bf16*)q_out, cache, row_slot, row_pos, n_rows,
+            q_heads, eps, write_kv);
+    else
+        X0NE_REQUIRE(false, "rope: unknown dtype tag %d", dt);
+    X0NE_LAUNCH_CHECK();
+}
+
+// ----------------------------------------------------------------------------------------
+// SwiGLU on the packed [gate; up] row: out[i] = T(g / (1 + expf(-g)) * u)
+// (x0ne-core/kernels/cuda/swiglu.cu:5-11).
+// ----------------------------------------------------------------------------------------
+template <typename T>
+__global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x, r = blockIdx.y;
+    if (i >= inter) return;
+    const T* row = gate_up + (int64_t)r * 2 * inter;
+    const float g = to_f32(row[i]), u = to_f32(row[inter + i]);
+    out[(int64_t)r * inter + i] = from_f32<T>(g / (1.0f + expf(-g)) * u);
+}
+
+X0NE_API int x0ne_swiglu(const void* gate_up, void* out, int dt, int n_rows, int inter, cudaStream_t stream) {
+    X0NE_REQUIRE(n_rows >= 0 && inter > 0, "swiglu: rows %d inter %d", n_rows, inter);
+    if (n_rows == 0) return 0;
+    X0NE_REQUIRE(n_rows <= 65535 * 1024, "swiglu: too many rows for one launch");
+    for (int r0 = 0; r0 < n_rows; r0 += 65535) {
+        const int nr = n_rows - r0 < 65535 ? n_rows - r0 : 65535;
+        dim3 grid((inter + 255) / 256, nr);
+        if (dt == X0NE_F32)
+            swiglu_kernel<float><<<grid, 256, 0, stream>>>((const float*)gate_up + (int64_t)r0 * 2 * inter,
+                                                           (float*)out + (int64_t)r0 * inter, inter);
+        else if (dt == X0NE_BF16)
+            swiglu_kernel<bf16><<<grid, 256, 0, stream>>>((const bf16*)gate_up + (int64_t)r0 * 2 * inter,
+                                                          (bf16*)out + (int64_t)r0 * inter, inter);
+        else
+            X0NE_REQUIRE(false, "swiglu: unknown dtype tag %d", dt);
+    }
+    X0NE_LAUNCH_CHECK();
+}

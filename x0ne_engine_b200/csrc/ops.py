@@ -1,0 +1,217 @@
+"""Python entry points of the CUDA kernels: argument checks, then one C call each.
+
+Tensors are torch CUDA tensors; a kernel gets raw device pointers and runs on torch's current
+stream, so calls order themselves with torch work and can be captured into a CUDA graph.
+Every function raises `KernelError` when the C entry point refuses its arguments or the launch
+fails; nothing here computes on the CPU or through another library.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import POINTER, Structure, c_float, c_int, c_int32, c_int64, c_void_p
+from typing import Optional
+
+import torch
+
+from . import build as _build
+
+F32, BF16 = 0, 1
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def dtype_tag(dtype: torch.dtype) -> int:
+    if dtype == torch.float32:
+        return F32
+    if dtype == torch.bfloat16:
+        return BF16
+    raise KernelError(f"no kernel for dtype {dtype}")
+
+
+class PagedCacheArg(Structure):
+    """Mirror of `struct PagedCache` in common.cuh."""
+    _fields_ = [("base", c_void_p), ("page_table", c_void_p), ("page_stride", c_int64),
+                ("table_stride", c_int32), ("ring_pages", c_int32), ("page_size", c_int32),
+                ("kv_heads", c_int32), ("head_dim", c_int32), ("n_pages", c_int32)]
+
+
+class SampleIOArg(Structure):
+    """Mirror of `struct SampleIO` in sampling.cu."""
+    _fields_ = [("logits", c_void_p), ("temperature", c_void_p), ("top_p", c_void_p), ("seed", c_void_p),
+                ("draw_counter", c_void_p), ("stop_ids", c_void_p), ("finished", c_void_p), ("budget", c_void_p),
+                ("out_token", c_void_p), ("next_token", c_void_p), ("next_pos", c_void_p),
+                ("ld", c_int64), ("vocab", c_int32), ("n_stop", c_int32)]
+
+
+_libs = {}
+
+
+def _lib(name: str) -> ctypes.CDLL:
+    lib = _libs.get(name)
+    if lib is None:
+        lib = _build.load(name)
+        lib.x0ne_last_error.restype = ctypes.c_char_p
+        _libs[name] = lib
+    return lib
+
+
+def loaded_libraries():
+    """Paths of the kernel libraries this process has loaded."""
+    return [lib._name for lib in _libs.values()]
+
+
+def _check(lib, code: int, what: str) -> None:
+    if code != 0:
+        msg = lib.x0ne_last_error()
+        raise KernelError(f"{what}: {msg.decode() if msg else 'error'} (code {code})")
+
+
+def _stream() -> c_void_p:
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _ptr(t: Optional[torch.Tensor]) -> c_void_p:
+    return c_void_p(0 if t is None else t.data_ptr())
+
+
+def _need(t: torch.Tensor, dtype, what: str) -> None:
+    if not t.is_cuda:
+        raise KernelError(f"{what} is not on the GPU")
+    if t.dtype != dtype:
+        raise KernelError(f"{what} is {t.dtype}, the kernel needs {dtype}")
+    if not t.is_contiguous():
+        raise KernelError(f"{what} is not contiguous")
+
+
+def embedding(table: torch.Tensor, tokens: torch.Tensor, resid: torch.Tensor, n_rows: int) -> None:
+    """resid[r] = float32(table[tokens[r]]); an id outside the table gives a zero row."""
+    lib = _lib("core")
+    _need(tokens, torch.int32, "tokens")
+    _need(resid, torch.float32, "residual")
+    _need(table, table.dtype, "embedding table")
+    vocab, hidden = table.shape
+    if resid.shape[-1] != hidden or resid.numel() < n_rows * hidden or tokens.numel() < n_rows:
+        raise KernelError("embedding: buffers are smaller than the rows asked for")
+    _check(lib, lib.x0ne_embedding(_ptr(table), c_int(dtype_tag(table.dtype)), _ptr(tokens), _ptr(resid),
+                                   c_int(n_rows), c_int(hidden), c_int(vocab), _stream()), "embedding")
+
+
+def add_rmsnorm(resid: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, out: torch.Tensor,
+                n_rows: int, eps: float, rows: Optional[torch.Tensor] = None) -> None:
+    """resid += delta (if given); out = rmsnorm(resid) * weight.  `rows` gathers source rows."""
+    lib = _lib("core")
+    hidden = weight.numel()
+    _need(resid, torch.float32, "residual")
+    _need(weight, torch.float32, "norm weight")
+    _need(out, out.dtype, "norm output")
+    if delta is not None:
+        _need(delta, out.dtype, "delta")
+        if delta.shape[-1] != hidden:
+            raise KernelError("add_rmsnorm: delta width differs from the norm's")
+    if rows is not None:
+        _need(rows, torch.int32, "row list")
+        if rows.numel() < n_rows:
+            raise KernelError("add_rmsnorm: row list shorter than the rows asked for")
+    elif resid.numel() < n_rows * hidden:
+        raise KernelError("add_rmsnorm: residual smaller than the rows asked for")
+    if resid.shape[-1] != hidden or out.shape[-1] != hidden or out.numel() < n_rows * hidden:
+        raise KernelError("add_rmsnorm: widths differ or output too small")
+    _check(lib, lib.x0ne_add_rmsnorm(_ptr(resid), _ptr(delta), _ptr(weight), _ptr(out), c_int(dtype_tag(out.dtype)),
+                                     _ptr(rows), c_int(n_rows), c_int(hidden), c_float(eps), _stream()), "add_rmsnorm")
+
+
+def qk_norm_rope_kv_write(qkv: torch.Tensor, q_norm: Optional[torch.Tensor], k_norm: Optional[torch.Tensor],
+                          inv_freq: Optional[torch.Tensor], rotary_dim: int, q_out: torch.Tensor,
+                          cache: PagedCacheArg, row_slot: torch.Tensor, row_pos: torch.Tensor, n_rows: int,
+                          q_heads: int, eps: float, write_kv: bool = True) -> None:
+    lib = _lib("core")
+    _need(qkv, qkv.dtype, "qkv")
+    _need(q_out, qkv.dtype, "q output")
+    _need(row_slot, torch.int32, "row slots")
+    _need(row_pos, torch.int32, "row positions")
+    hd, kvh = cache.head_dim, cache.kv_heads
+    if qkv.shape[-1] != (q_heads + 2 * kvh) * hd or q_out.shape[-1] != q_heads * hd:
+        raise KernelError("rope: qkv or q widths do not match the head counts")
+    if qkv.numel() < n_rows * qkv.shape[-1] or q_out.numel() < n_rows * q_out.shape[-1]:
+        raise KernelError("rope: buffers smaller than the rows asked for")
+    for w, what in ((q_norm, "q_norm"), (k_norm, "k_norm")):
+        if w is not None:
+            _need(w, torch.float32, what)
+            if w.numel() != hd:
+                raise KernelError(f"rope: {what} has {w.numel()} values, head_dim is {hd}")
+    if inv_freq is not None:
+        _need(inv_freq, torch.float32, "inv_freq")
+        if inv_freq.numel() * 2 != rotary_dim:
+            raise KernelError("rope: inv_freq length is not rotary_dim / 2")
+    _check(lib, lib.x0ne_qk_norm_rope_kv_write(
+        _ptr(qkv), c_int(dtype_tag(qkv.dtype)), _ptr(q_norm), _ptr(k_norm), _ptr(inv_freq), c_int(rotary_dim),
+        _ptr(q_out), cache, _ptr(row_slot), _ptr(row_pos), c_int(n_rows), c_int(q_heads), c_float(eps),
+        c_int(1 if write_kv else 0), _stream()), "qk_norm_rope_kv_write")
+
+
+def attention_rows(q: torch.Tensor, out: torch.Tensor, cache: PagedCacheArg, row_slot: torch.Tensor,
+                   row_pos: torch.Tensor, n_rows: int, q_heads: int, scale: float, window: int = 0) -> None:
+    """The plain attention kernel: any head size up to 256, any window (0 = none)."""
+    lib = _lib("core")
+    _need(q, q.dtype, "q")
+    _need(out, q.dtype, "attention output")
+    _need(row_slot, torch.int32, "row slots")
+    _need(row_pos, torch.int32, "row positions")
+    width = q_heads * cache.head_dim
+    if q.shape[-1] != width or out.shape[-1] != width or q.numel() < n_rows * width or out.numel() < n_rows * width:
+        raise KernelError("attention: q or output do not match the head counts and rows")
+    _check(lib, lib.x0ne_attention_rows(_ptr(q), _ptr(out), c_int(dtype_tag(q.dtype)), cache, _ptr(row_slot),
+                                        _ptr(row_pos), c_int(n_rows), c_int(q_heads), c_float(scale), c_int(window),
+                                        _stream()), "attention_rows")
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor, n_rows: int) -> None:
+    lib = _lib("core")
+    _need(gate_up, gate_up.dtype, "gate_up")
+    _need(out, gate_up.dtype, "swiglu output")
+    inter = out.shape[-1]
+    if gate_up.shape[-1] != 2 * inter or gate_up.numel() < n_rows * 2 * inter or out.numel() < n_rows * inter:
+        raise KernelError("swiglu: widths or rows do not match")
+    _check(lib, lib.x0ne_swiglu(_ptr(gate_up), _ptr(out), c_int(dtype_tag(out.dtype)), c_int(n_rows), c_int(inter),
+                                _stream()), "swiglu")
+
+
+def gemm_f32_nt(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, m: int) -> None:
+    """c[:m] = a[:m] @ w.T in true float32, one fixed-order FMA chain per output."""
+    lib = _lib("core")
+    _need(a, torch.float32, "gemm input")
+    _need(w, torch.float32, "gemm weight")
+    _need(c, torch.float32, "gemm output")
+    n, k = w.shape
+    if a.shape[-1] != k or c.shape[-1] != n or a.numel() < m * k or c.numel() < m * n:
+        raise KernelError(f"gemm_f32: shapes a {tuple(a.shape)} w {tuple(w.shape)} c {tuple(c.shape)} m {m}")
+    _check(lib, lib.x0ne_gemm_f32_nt(_ptr(a), _ptr(w), _ptr(c), c_int(m), c_int(n), c_int(k), c_int(k), c_int(k),
+                                     c_int(n), _stream()), "gemm_f32_nt")
+
+
+def sample(logits: torch.Tensor, n_rows: int, out_token: torch.Tensor, *, temperature=None, top_p=None, seed=None,
+           draw_counter=None, stop_ids=None, finished=None, budget=None, next_token=None, next_pos=None) -> None:
+    """Picks a token per logits row on the device (see sampling.cu for the rules)."""
+    lib = _lib("core")
+    _need(logits, torch.float32, "logits")
+    _need(out_token, torch.int32, "token output")
+    if logits.dim() != 2 or logits.shape[0] < n_rows or out_token.numel() < n_rows:
+        raise KernelError("sample: logits or output smaller than the rows asked for")
+    for t, dt, what in ((temperature, torch.float32, "temperature"), (top_p, torch.float32, "top_p"),
+                        (seed, torch.int64, "seed"), (draw_counter, torch.int32, "draw counter"),
+                        (finished, torch.int32, "finished flags"), (budget, torch.int32, "budget"),
+                        (next_token, torch.int32, "next token"), (next_pos, torch.int32, "next position")):
+        if t is not None:
+            _need(t, dt, what)
+            if t.numel() < n_rows:
+                raise KernelError(f"sample: {what} shorter than the rows asked for")
+    n_stop = 0
+    if stop_ids is not None and stop_ids.numel() > 0:
+        _need(stop_ids, torch.int32, "stop ids")
+        n_stop = stop_ids.numel()
+    io = SampleIOArg(_ptr(logits), _ptr(temperature), _ptr(top_p), _ptr(seed), _ptr(draw_counter),
+                     _ptr(stop_ids if n_stop else None), _ptr(finished), _ptr(budget), _ptr(out_token),
+                     _ptr(next_token), _ptr(next_pos), logits.stride(0), logits.shape[1], n_stop)
+    _check(lib, lib.x0ne_sample(io, c_int(n_rows), _stream()), "sample")

@@ -1,0 +1,302 @@
+// Picking the next token of every sequence on the device: greedy, temperature, nucleus.
+//
+// One block of 1024 threads per logits row.  The pick also feeds the next decode step: it
+// writes the token where that step reads it, advances the sequence's position and draw
+// counter, and marks the sequence finished on a stop token or a spent budget, so token and
+// position never leave the device between two steps (the library engine's decode graph ends
+// with argmax into tokens[0] and a position advance: x0ne-core/runtime/src/engine.rs:495-501,
+// x0ne-core/kernels/cuda/argmax.cu, advance.cu).
+//
+// Rules (x0ne-infer/src/sampler.rs:59-147, x0ne-core/kernels/cuda/argmax.cu:4-10):
+//   * any NaN in the row: no token, the row's output is -1 and the host refuses it;
+//   * temperature < 1e-7 or top_p <= 0: argmax, lowest index on ties;
+//   * otherwise x_i = v_i * (1/t), e_i = expf(x_i - max x), and the token is drawn by inverse
+//     CDF in index order over the kept tokens; top_p >= 1 keeps all, else the nucleus: in the
+//     order (probability descending, index ascending) every token whose predecessors hold less
+//     than top_p of the mass.
+// The uniform for draw number c of a sequence with seed s is the top 24 bits of
+// splitmix64(s + (c + 1) * 0x9E3779B97F4A7C15) / 2^24: a sequence's draws depend on its seed
+// and on how many tokens it has drawn, not on its batch mates.
+// Sums run in a fixed order: thread t owns the contiguous index range [t*c, (t+1)*c) and adds
+// it front to back; the 1024 partial sums are combined by a fixed scan.
+#include "common.cuh"
+
+#define SB 1024
+
+__device__ __forceinline__ bool better(float v, int i, float bv, int bi) { return v > bv || (v == bv && i < bi); }
+
+// Inclusive scan of one value per thread over the block; returns this thread's inclusive
+// prefix, and the block total through `total`.  `sh` holds 33 floats.
+__device__ __forceinline__ float block_scan(float v, float* sh, float* total) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    float x = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const float y = __shfl_up_sync(0xffffffffu, x, o);
+        if (lane >= o) x += y;
+    }
+    __syncthreads();
+    if (lane == 31) sh[warp] = x;
+    __syncthreads();
+    if (warp == 0) {
+        float w = sh[lane];
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const float y = __shfl_up_sync(0xffffffffu, w, o);
+            if (lane >= o) w += y;
+        }
+        sh[lane] = w;
+        if (lane == 31) sh[32] = w;
+    }
+    __syncthreads();
+    const float before = warp > 0 ? sh[warp - 1] : 0.f;
+    *total = sh[32];
+    return before + x;
+}
+
+__device__ __forceinline__ int block_scan_int(int v, int* sh, int* total) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    int x = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int y = __shfl_up_sync(0xffffffffu, x, o);
+        if (lane >= o) x += y;
+    }
+    __syncthreads();
+    if (lane == 31) sh[warp] = x;
+    __syncthreads();
+    if (warp == 0) {
+        int w = sh[lane];
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int y = __shfl_up_sync(0xffffffffu, w, o);
+            if (lane >= o) w += y;
+        }
+        sh[lane] = w;
+        if (lane == 31) sh[32] = w;
+    }
+    __syncthreads();
+    const int before = warp > 0 ? sh[warp - 1] : 0;
+    *total = sh[32];
+    return before + x;
+}
+
+__device__ __forceinline__ float uniform_of(uint64_t seed, uint32_t counter) {
+    uint64_t z = seed + (uint64_t)(counter + 1u) * 0x9E3779B97F4A7C15ull;
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    z = z ^ (z >> 31);
+    return (float)(z >> 40) * (1.0f / 16777216.0f);
+}
+
+struct SampleIO {
+    const float* logits;         // [rows][ld]
+    const float* temperature;    // [rows] or null (greedy)
+    const float* top_p;          // [rows] or null (1)
+    const uint64_t* seed;        // [rows] or null (0)
+    int32_t* draw_counter;       // [rows] or null
+    const int32_t* stop_ids;     // [n_stop]
+    int32_t* finished;           // [rows] or null
+    int32_t* budget;             // [rows] or null: tokens still allowed
+    int32_t* out_token;          // [rows]: the pick, -1 for a NaN row, -2 for a row already finished
+    int32_t* next_token;         // [rows] or null: where the next step reads its token
+    int32_t* next_pos;           // [rows] or null: advanced by one when the token will be fed
+    int64_t ld;
+    int32_t vocab;
+    int32_t n_stop;
+};
+
+__global__ void __launch_bounds__(SB) sample_kernel(SampleIO io) {
+    __shared__ float shf[33];
+    __shared__ int shi[33];
+    __shared__ float s_bv[32];
+    __shared__ int s_bi[32];
+    __shared__ int s_pick;
+    const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (io.finished && io.finished[row]) {
+        if (tid == 0) io.out_token[row] = -2;
+        return;
+    }
+    const float* x = io.logits + (int64_t)row * io.ld;
+    const int V = io.vocab;
+
+    // ---- max, argmax, NaN
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    bool nan = false;
+    for (int i = tid; i < V; i += SB) {
+        const float v = x[i];
+        nan |= v != v;
+        if (better(v, i, bv, bi)) { bv = v; bi = i; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
+    }
+    if (lane == 0) { s_bv[warp] = bv; s_bi[warp] = bi; }
+    if (__syncthreads_or(nan)) {
+        if (tid == 0) {
+            io.out_token[row] = -1;
+            if (io.finished) io.finished[row] = 1;
+        }
+        return;
+    }
+    if (warp == 0) {
+        bv = s_bv[lane];
+        bi = s_bi[lane];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
+        }
+        if (lane == 0) { s_bv[0] = bv; s_pick = bi; }
+    }
+    __syncthreads();
+    const float vmax = s_bv[0];
+
+    const float t = io.temperature ? io.temperature[row] : 0.f;
+    const float top_p = io.top_p ? io.top_p[row] : 1.f;
+    if (t >= 1e-7f && top_p > 0.f && V > 1) {
+        const float mul = 1.0f / t;
+        const float xmax = vmax * mul;
+        const int c = (V + SB - 1) / SB;
+        const int lo = min(V, tid * c), hi = min(V, lo + c);
+        // ---- total mass
+        float s = 0.f;
+        for (int i = lo; i < hi; ++i) s += expf(x[i] * mul - xmax);
+        float Z;
+        block_scan(s, shf, &Z);
+        float tau = -1.f;  // keep e > tau, plus n_tie tokens with e == tau, lowest indices first
+        int n_tie = 0;
+        if (top_p < 1.f) {
+            // Largest tau (as float bits) with mass{e >= tau} >= top_p * Z.
+            const float need = top_p * Z;
+            uint32_t lo_b = 0u, hi_b = 0x3f800000u;  // e lies in [0, 1]
+            while (lo_b < hi_b) {
+                const uint32_t mid = lo_b + (hi_b - lo_b + 1u) / 2u;
+                const float th = __uint_as_float(mid);
+                float ms = 0.f;
+                for (int i = lo; i < hi; ++i) {
+                    const float e = expf(x[i] * mul - xmax);
+                    if (e >= th) ms += e;
+                }
+                float mass;
+                block_scan(ms, shf, &mass);
+                if (mass >= need) lo_b = mid; else hi_b = mid - 1u;
+            }
+            tau = __uint_as_float(lo_b);
+            float mg = 0.f;
+            for (int i = lo; i < hi; ++i) {
+                const float e = expf(x[i] * mul - xmax);
+                if (e > tau) mg += e;
+            }
+            float mass_gt;
+            block_scan(mg, shf, &mass_gt);
+            n_tie = 1;
+            if (tau > 0.f) {
+                const float k = ceilf((need - mass_gt) / tau);
+                n_tie = k < 1.f ? 1 : (k > 2.0e9f ? 2000000000 : (int)k);
+            } else {
+                n_tie = 0x7fffffff;
+            }
+        }
+        // ---- kept mass per thread, tie ranks in index order
+        int ties = 0;
+        if (top_p < 1.f)
+            for (int i = lo; i < hi; ++i) ties += expf(x[i] * mul - xmax) == tau;
+        int tie_total;
+        const int tie_incl = block_scan_int(ties, shi, &tie_total);
+        int rank = tie_incl - ties;
+        float ks = 0.f;
+        for (int i = lo; i < hi; ++i) {
+            const float e = expf(x[i] * mul - xmax);
+            bool keep = e > tau;
+            if (top_p < 1.f && e == tau) keep = rank++ < n_tie;
+            if (keep) ks += e;
+        }
+        float Zk;
+        const float incl = block_scan(ks, shf, &Zk);
+        const float excl = incl - ks;
+        const uint64_t seed = io.seed ? io.seed[row] : 0ull;
+        const uint32_t counter = io.draw_counter ? (uint32_t)io.draw_counter[row] : 0u;
+        const float target = uniform_of(seed, counter) * Zk;
+        if (tid == 0) s_pick = -1;
+        __syncthreads();
+        if (ks > 0.f && excl <= target && target < incl) {
+            float run = excl;
+            int pick = -1, last_kept = -1;
+            rank = tie_incl - ties;
+            for (int i = lo; i < hi; ++i) {
+                const float e = expf(x[i] * mul - xmax);
+                bool keep = e > tau;
+                if (top_p < 1.f && e == tau) keep = rank++ < n_tie;
+                if (!keep) continue;
+                last_kept = i;
+                run += e;
+                if (run > target) { pick = i; break; }
+            }
+            s_pick = pick >= 0 ? pick : last_kept;
+        }
+        __syncthreads();
+        if (s_pick < 0) {
+            // target fell on or past the last boundary by rounding: the last kept token.
+            int last = -1;
+            rank = tie_incl - ties;
+            for (int i = lo; i < hi; ++i) {
+                const float e = expf(x[i] * mul - xmax);
+                bool keep = e > tau;
+                if (top_p < 1.f && e == tau) keep = rank++ < n_tie;
+                if (keep) last = i;
+            }
+            // max over threads
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) last = max(last, __shfl_xor_sync(0xffffffffu, last, o));
+            if (lane == 0) s_bi[warp] = last;
+            __syncthreads();
+            if (warp == 0) {
+                last = s_bi[lane];
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) last = max(last, __shfl_xor_sync(0xffffffffu, last, o));
+                if (lane == 0) s_pick = last;
+            }
+            __syncthreads();
+        }
+    }
+
+    if (tid == 0) {
+        const int tok = s_pick;
+        io.out_token[row] = tok;
+        bool stop = false;
+        for (int i = 0; i < io.n_stop; ++i) stop |= io.stop_ids[i] == tok;
+        if (stop) {
+            if (io.finished) io.finished[row] = 1;
+        } else {
+            if (io.draw_counter) io.draw_counter[row] += 1;
+            bool spent = false;
+            if (io.budget) {
+                const int b = io.budget[row] - 1;
+                io.budget[row] = b;
+                spent = b <= 0;
+            }
+            if (spent) {
+                if (io.finished) io.finished[row] = 1;
+            } else {
+                if (io.next_token) io.next_token[row] = tok;
+                if (io.next_pos) io.next_pos[row] += 1;
+            }
+        }
+    }
+}
+
+X0NE_API int x0ne_sample(SampleIO io, int n_rows, cudaStream_t stream) {
+    X0NE_REQUIRE(n_rows >= 0 && io.vocab > 0 && io.ld >= io.vocab, "sample: rows %d vocab %d ld %lld", n_rows,
+                 io.vocab, (long long)io.ld);
+    X0NE_REQUIRE(io.logits && io.out_token, "sample: null logits or output");
+    X0NE_REQUIRE(io.n_stop == 0 || io.stop_ids, "sample: %d stop ids but no list", io.n_stop);
+    if (n_rows == 0) return 0;
+    sample_kernel<<<n_rows, SB, 0, stream>>>(io);
+    X0NE_LAUNCH_CHECK();
+}

@@ -1,0 +1,248 @@
+"""The engine: a model on one GPU, its cache, and ONE step function.
+
+`Engine.step` takes a batch of sequences, each with the tokens it brings now (a whole prompt, a
+further piece of it, or one token), runs exactly those tokens as one batch against what the
+cache already holds for each sequence, appends their keys and values, and returns float32
+logits at the wanted places.  Prefill, chunked prefill and decode are the same call; generation,
+trace replay and the benchmark all go through it (decode steps may go through a CUDA graph of
+the same launches, see decode.py).
+
+The library engine's forward takes one sequence, a start position and a row count
+(x0ne-core/runtime/src/engine.rs:702-839); here every row carries its own (slot, position), so
+sequences of unequal length share a pass and padding never exists.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from ..cache import PAGE_SIZE, CacheFull, SequenceCache
+from ..config import config_from_folder
+from ..config.spec import ModelSpec
+from ..weights import RandomInit, load_folder, make_tensor
+from ..weights.loader import held_dtype
+from .model import CausalLM, optional_duplicates_of_spec, tensor_needs_of_spec
+from .workspace import Workspace
+
+DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32,
+          torch.bfloat16: torch.bfloat16, torch.float32: torch.float32}
+
+
+class StepError(ValueError):
+    """A step the engine refuses before any launch: bad ids, bad slots, no room."""
+
+
+@dataclass
+class StepContext:
+    """What the parts see of one pass."""
+    n_rows: int
+    tokens: torch.Tensor        # int32 [>= n_rows]
+    row_slot: torch.Tensor      # int32: the cache slot of each row's sequence
+    row_pos: torch.Tensor       # int32: the absolute position of each row
+    dtype: torch.dtype
+    ws: Workspace
+    cache: SequenceCache
+    decode: bool                # every sequence brings exactly one token
+    n_seqs: int = 0
+    max_seq_rows: int = 0       # most rows one sequence brings to this pass
+    max_context: int = 0        # upper bound on the keys any row reads
+    seq_first_row: Optional[torch.Tensor] = None   # int32 [n_seqs + 1]
+    seq_slot: Optional[torch.Tensor] = None        # int32 [n_seqs]
+    seq_pos0: Optional[torch.Tensor] = None        # int32 [n_seqs]: position of the sequence's first row
+
+
+def require_gpu(device) -> torch.device:
+    device = torch.device(device)
+    if device.type != "cuda":
+        raise RuntimeError("this library runs its models on a CUDA device only; it has no CPU path")
+    if not torch.cuda.is_available():
+        raise RuntimeError("no CUDA device is available; this library has no CPU path")
+    return device
+
+
+class Engine:
+    def __init__(self, spec: ModelSpec, tensors: Dict[str, torch.Tensor], dtype, device="cuda:0",
+                 max_tokens: int = 8192, max_seq_len: Optional[int] = None, max_step_tokens: Optional[int] = None,
+                 max_slots: Optional[int] = None):
+        self.device = require_gpu(device)
+        self.dtype = DTYPES[dtype]
+        self.spec = spec
+        torch.cuda.set_device(self.device)
+        self.model = CausalLM(spec, self.dtype, self.device)
+        self.model.bind(tensors)
+        self.vocab_size = spec.vocab_size
+        self.max_seq_len = min(max_seq_len or spec.max_position_embeddings, spec.max_position_embeddings)
+        needs = self.model.cache_needs()
+        self.cache = SequenceCache(needs, [e.reads_cache_of for e in spec.run_order], max_tokens, self.max_seq_len,
+                                   self.dtype, self.device, max_slots=max_slots)
+        self.max_step_tokens = int(max_step_tokens or min(8192, max(PAGE_SIZE, max_tokens)))
+        self.ws = Workspace(self.max_step_tokens, self.device)
+        self.ws.max_want = self.max_step_tokens
+        # pass metadata: tokens, slots, positions, wanted rows; a small ring of pinned staging buffers
+        self._meta_dev = torch.zeros((4, self.max_step_tokens), dtype=torch.int32, device=self.device)
+        self._stage = [torch.zeros((4, self.max_step_tokens), dtype=torch.int32).pin_memory() for _ in range(4)]
+        self._stage_events: List[Optional[torch.cuda.Event]] = [None] * len(self._stage)
+        self._stage_at = 0
+        self._seq_dev = torch.zeros((3, self.max_step_tokens + 1), dtype=torch.int32, device=self.device)
+        self.launch_count = 0
+
+    # ------------------------------------------------------------------ construction
+    @classmethod
+    def from_folder(cls, folder: str, dtype="bfloat16", device="cuda:0", **kw) -> "Engine":
+        """Loads config.json and the safetensors of `folder`; the model class is chosen by config.json."""
+        device = require_gpu(device)
+        config = config_from_folder(folder)
+        spec = config.to_spec()
+        needs = tensor_needs_of_spec(spec)
+        tensors = load_folder(folder, needs, DTYPES[dtype], device, same_as=optional_duplicates_of_spec(spec))
+        eng = cls(spec, tensors, dtype, device, **kw)
+        eng.config = config
+        return eng
+
+    @classmethod
+    def random(cls, config, seed: int = 0, dtype="bfloat16", device="cuda:0", linear_std: float = 0.02,
+               norm_jitter: float = 0.0, **kw) -> "Engine":
+        """A model with random weights made on the device (no folder): the values a folder written
+        by `write_model_folder` with the same seed holds, in the config's stored dtype."""
+        device = require_gpu(device)
+        spec = config.to_spec()
+        init = RandomInit(seed, linear_std, norm_jitter)
+        stored = DTYPES[config.dtype]
+        tensors = {}
+        for need in tensor_needs_of_spec(spec):
+            t = make_tensor(need, init, stored, device)
+            tensors[need.name] = t.to(held_dtype(need, stored, DTYPES[dtype]))
+        eng = cls(spec, tensors, dtype, device, **kw)
+        eng.config = config
+        return eng
+
+    # ------------------------------------------------------------------ sequences
+    def new_sequence(self, reserve_tokens: int = 0) -> int:
+        return self.cache.acquire(reserve_tokens)
+
+    def free_sequence(self, slot: int) -> None:
+        self.cache.release(slot)
+
+    def length(self, slot: int) -> int:
+        return self.cache.lengths[slot]
+
+    # ------------------------------------------------------------------ the step
+    def _stage_buffer(self) -> Tuple[torch.Tensor, int]:
+        i = self._stage_at
+        self._stage_at = (i + 1) % len(self._stage)
+        ev = self._stage_events[i]
+        if ev is not None:
+            ev.synchronize()
+        return self._stage[i], i
+
+    def step(self, slots: Sequence[int], tokens: Sequence[Sequence[int]],
+             want: Optional[Sequence[Sequence[int]]] = None) -> torch.Tensor:
+        """Runs `tokens[i]` as the next tokens of the sequence in `slots[i]`.
+
+        `want[i]` lists the places among `tokens[i]` whose logits are returned (default: the last
+        one).  Returns float32 [number wanted, vocab] in the order of the sequences and of `want`.
+        All checks happen before the first launch; a refused step changes nothing.
+        """
+        n_seqs = len(slots)
+        if n_seqs == 0:
+            return torch.empty((0, self.vocab_size), dtype=torch.float32, device=self.device)
+        if len(tokens) != n_seqs or (want is not None and len(want) != n_seqs):
+            raise StepError("slots, tokens and want must have one entry per sequence")
+        if len(set(slots)) != n_seqs:
+            raise StepError("a slot is named twice in one step")
+        lens = [len(t) for t in tokens]
+        if min(lens) == 0:
+            raise StepError("a sequence brings no token")
+        starts = []
+        for s, n in zip(slots, lens):
+            if not self.cache.slots.is_held(s):
+                raise StepError(f"slot {s} is not held by a sequence")
+            start = self.cache.lengths[s]
+            if start + n > self.max_seq_len:
+                raise StepError(f"slot {s}: {start} + {n} tokens exceed the longest sequence, {self.max_seq_len}")
+            starts.append(start)
+        flat = np.concatenate([np.asarray(t, dtype=np.int64) for t in tokens])
+        if flat.min() < 0 or flat.max() >= self.vocab_size:
+            raise StepError(f"a token id lies outside the vocabulary of {self.vocab_size}")
+        if want is None:
+            want = [[n - 1] for n in lens]
+        for w, n in zip(want, lens):
+            for j in w:
+                if not 0 <= j < n:
+                    raise StepError(f"a wanted place {j} lies outside the {n} tokens its sequence brings")
+        # pages for every sequence, all or nothing
+        try:
+            self.cache.ensure_all([(s, st + n) for s, st, n in zip(slots, starts, lens)])
+        except CacheFull as e:
+            raise StepError(f"the cache has no room for this step: {e}") from None
+
+        total = int(flat.shape[0])
+        row_slot = np.repeat(np.asarray(slots, dtype=np.int32), lens)
+        row_pos = np.concatenate([np.arange(st, st + n, dtype=np.int32) for st, n in zip(starts, lens)])
+        first_row = np.concatenate([[0], np.cumsum(lens)]).astype(np.int64)
+        want_flat = np.asarray([first_row[i] + j for i, w in enumerate(want) for j in w], dtype=np.int64)
+        order = np.argsort(want_flat, kind="stable")
+        n_want = len(want_flat)
+        logits = torch.empty((n_want, self.vocab_size), dtype=torch.float32, device=self.device)
+
+        decode = max(lens) == 1
+        chunk = min(self.max_step_tokens, self.cache.max_chunk)
+        sorted_want = want_flat[order]
+        for r0 in range(0, total, chunk):
+            r1 = min(total, r0 + chunk)
+            lo, hi = np.searchsorted(sorted_want, [r0, r1])
+            self._run_pass(flat[r0:r1], row_slot[r0:r1], row_pos[r0:r1], sorted_want[lo:hi] - r0, order[lo:hi],
+                           logits, decode, slots, starts, lens, first_row, r0, r1)
+        for s, n in zip(slots, lens):
+            self.cache.lengths[s] += n
+        return logits
+
+    def _run_pass(self, toks, rslot, rpos, want_rows, want_dest, logits, decode, slots, starts, lens, first_row,
+                  r0, r1) -> None:
+        n = len(toks)
+        stage, si = self._stage_buffer()
+        stage[0, :n] = torch.from_numpy(toks.astype(np.int32))
+        stage[1, :n] = torch.from_numpy(rslot)
+        stage[2, :n] = torch.from_numpy(rpos)
+        nw = len(want_rows)
+        if nw:
+            stage[3, :nw] = torch.from_numpy(want_rows.astype(np.int32))
+        self._meta_dev.copy_(stage, non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        self._stage_events[si] = ev
+        # sequence-level view of the pass (for kernels that work per sequence)
+        seq_ids = [i for i in range(len(slots)) if first_row[i] < r1 and first_row[i + 1] > r0]
+        sfirst = np.asarray([max(first_row[i], r0) - r0 for i in seq_ids] + [r1 - r0], dtype=np.int32)
+        sslot = np.asarray([slots[i] for i in seq_ids], dtype=np.int32)
+        spos0 = np.asarray([starts[i] + (max(first_row[i], r0) - first_row[i]) for i in seq_ids], dtype=np.int32)
+        ns = len(seq_ids)
+        seq_host = np.zeros((3, ns + 1), dtype=np.int32)
+        seq_host[0, :ns + 1] = sfirst
+        seq_host[1, :ns] = sslot
+        seq_host[2, :ns] = spos0
+        self._seq_dev[:, :ns + 1].copy_(torch.from_numpy(seq_host))
+        ctx = StepContext(
+            n_rows=n, tokens=self._meta_dev[0], row_slot=self._meta_dev[1], row_pos=self._meta_dev[2],
+            dtype=self.dtype, ws=self.ws, cache=self.cache, decode=decode, n_seqs=ns,
+            max_seq_rows=int(np.max(np.diff(sfirst))), max_context=int(rpos.max()) + 1,
+            seq_first_row=self._seq_dev[0], seq_slot=self._seq_dev[1], seq_pos0=self._seq_dev[2])
+        if nw == 0:
+            self.model.forward(ctx, None, 0, None)
+        elif nw == logits.shape[0] and np.array_equal(want_dest, np.arange(nw)):
+            self.model.forward(ctx, self._meta_dev[3], nw, logits)
+        else:
+            out = torch.empty((nw, self.vocab_size), dtype=torch.float32, device=self.device)
+            self.model.forward(ctx, self._meta_dev[3], nw, out)
+            logits[torch.from_numpy(want_dest).to(self.device)] = out
+
+    # ------------------------------------------------------------------ facts for reports
+    def describe(self) -> str:
+        p = torch.cuda.get_device_properties(self.device)
+        return (f"{self.spec.architecture} {len(self.spec.layers)} layers hidden {self.spec.hidden_size} "
+                f"vocab {self.spec.vocab_size} dtype {self.dtype} on {p.name} (sm_{p.major}{p.minor}, "
+                f"{p.multi_processor_count} SMs); cache {self.cache.groups[0].n_pages if self.cache.groups else 0} "
+                f"pages of {self.cache.page_size} tokens, {self.cache.bytes_per_token()} B/token")

@@ -1,0 +1,35 @@
+"""Activation buffers of a step, allocated once per name and reused by every layer."""
+from __future__ import annotations
+
+from typing import Dict, Tuple
+
+import torch
+
+
+class Workspace:
+    """`buffer(name, shape, dtype)` returns the same tensor for the same name every time.
+
+    Parts name their scratch generically ("attn.qkv", "ffn.act", "delta"), so layers of the same
+    kind share it; a name asked for with a larger shape is grown (outside graph capture only).
+    """
+
+    def __init__(self, max_rows: int, device):
+        self.max_rows = max_rows
+        self.device = device
+        self._bufs: Dict[str, torch.Tensor] = {}
+        self.frozen = False
+
+    def buffer(self, name: str, shape: Tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
+        t = self._bufs.get(name)
+        n = 1
+        for s in shape:
+            n *= s
+        if t is None or t.dtype != dtype or t.numel() < n:
+            if self.frozen:
+                raise RuntimeError(f"workspace buffer {name!r} would be reallocated after the workspace was frozen")
+            t = torch.empty(n, dtype=dtype, device=self.device)
+            self._bufs[name] = t
+        return t[:n].view(shape)
+
+    def bytes(self) -> int:
+        return sum(t.numel() * t.element_size() for t in self._bufs.values())

@@ -1,0 +1,141 @@
+"""What a layer is made of: the interfaces of the parts, and one registry per kind of part.
+
+A part is built from a `PartSpec` (its sizes, constants and checkpoint tensor names) and a
+`BuildEnv` (the run's dtype and device, and the model's position encodings by name).  It never
+sees the model's name or its config.json.  The kinds:
+
+  * `Norm`         — `add_norm(ctx, resid, delta, out, n_rows, rows=None)`: adds `delta` (may be
+                     None) into the float32 residual and writes the normed rows.
+  * `Mixer`        — mixes information between the positions of a sequence.  Says what it keeps
+                     per sequence with `cache_need(spec)`; `forward(ctx, entry, x, n_rows)` reads
+                     and writes that through `ctx.cache` for run-order entry `entry` and returns
+                     its output rows (the "delta" the next norm adds to the residual).
+  * `FeedForward`  — `forward(ctx, x, n_rows)`: per-row transformation, returns the delta.
+  * `PositionEncoding` — `rotary()` gives (inv_freq float32 [rotary_dim/2], rotary_dim) for
+                     mixers that rotate q and k, or None; `on_embedding(ctx, resid, n_rows)` lets
+                     an additive encoding change the residual after the token embedding.
+  * `Block`        — how a layer's norms, mixer and feed-forward are arranged around the
+                     residual: `forward(ctx, entry, resid, delta)` returns the pending delta.
+
+To add a part: subclass the kind, implement `tensor_needs(spec)` (static: the checkpoint
+tensors, by name, with shapes) and `bind(tensors)`, and call the kind's `register`.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Callable, Dict, List, Mapping, Optional, Tuple
+
+import torch
+
+from ..config.spec import PartSpec
+from ..weights.loader import TensorNeed
+
+
+@dataclass(frozen=True)
+class CacheNeed:
+    """What a mixer keeps for each sequence.
+
+    kind "kv": keys and values of `kv_heads` x `head_dim` per position; all positions, or the
+    last `window` of them.  kind "state": a float32 array of `state_shape` per sequence, zero
+    when the sequence starts.  kind "none": nothing.
+    """
+    kind: str = "none"
+    kv_heads: int = 0
+    head_dim: int = 0
+    window: Optional[int] = None
+    state_shape: Tuple[int, ...] = ()
+
+
+@dataclass
+class BuildEnv:
+    dtype: torch.dtype
+    device: torch.device
+    positions: Dict[str, "PositionEncoding"] = field(default_factory=dict)
+
+
+class Part:
+    def __init__(self, spec: PartSpec, env: BuildEnv):
+        self.spec = spec
+        self.env = env
+
+    @staticmethod
+    def tensor_needs(spec: PartSpec) -> List[TensorNeed]:
+        return []
+
+    def bind(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        """Receives the device tensors named in `tensor_needs`."""
+
+    def weight_bytes(self) -> int:
+        """Bytes of weights a step reads (for the roofline)."""
+        return 0
+
+
+class Norm(Part):
+    def add_norm(self, ctx, resid, delta, out, n_rows: int, rows=None) -> None:
+        raise NotImplementedError
+
+
+class Mixer(Part):
+    @staticmethod
+    def cache_need(spec: PartSpec) -> CacheNeed:
+        return CacheNeed()
+
+    def forward(self, ctx, entry: int, x: torch.Tensor, n_rows: int, cache_entry: Optional[int] = None,
+                write_cache: bool = True) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, ctx, x: torch.Tensor, n_rows: int) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    def rotary(self) -> Optional[Tuple[torch.Tensor, int]]:
+        return None
+
+    def on_embedding(self, ctx, resid: torch.Tensor, n_rows: int) -> None:
+        return None
+
+
+class Block:
+    """Arrangement of one layer's parts; built by the engine from a LayerSpec."""
+
+    def __init__(self, mixer_norm: Norm, mixer: Mixer, ffn_norm: Norm, ffn: FeedForward):
+        self.mixer_norm, self.mixer, self.ffn_norm, self.ffn = mixer_norm, mixer, ffn_norm, ffn
+
+    def parts(self) -> List[Part]:
+        return [self.mixer_norm, self.mixer, self.ffn_norm, self.ffn]
+
+    def forward(self, ctx, entry: int, resid, delta, cache_entry=None, write_cache=True):
+        raise NotImplementedError
+
+
+class Registry:
+    def __init__(self, what: str):
+        self.what = what
+        self._kinds: Dict[str, Any] = {}
+
+    def register(self, kind: str, cls: Any, replace: bool = False) -> None:
+        if kind in self._kinds and not replace:
+            raise ValueError(f"{self.what} kind {kind!r} is already registered")
+        self._kinds[kind] = cls
+
+    def unregister(self, kind: str) -> None:
+        self._kinds.pop(kind, None)
+
+    def get(self, kind: str) -> Any:
+        try:
+            return self._kinds[kind]
+        except KeyError:
+            raise KeyError(f"no {self.what} of kind {kind!r}; registered: {sorted(self._kinds)}") from None
+
+    def kinds(self) -> List[str]:
+        return sorted(self._kinds)
+
+
+NORMS = Registry("norm")
+MIXERS = Registry("mixer")
+FEED_FORWARDS = Registry("feed-forward")
+POSITIONS = Registry("position encoding")
+BLOCKS = Registry("block")
