@@ -6,10 +6,12 @@ from registered parts, a paged cache with a slot per sequence, one step function
 loop with greedy / temperature / nucleus sampling, trace replay, and hand-written CUDA kernels.
 """
 from .config import ConfigError, Qwen3Config, config_from_folder, register_architecture
+from .api import GenerateResult, Model
 from .engine import Engine, StepError
+from .sampling import SamplingParams
 from .weights import RandomInit, WeightsError, write_model_folder
 
 __version__ = "0.1.0"
 
-__all__ = ["ConfigError", "Qwen3Config", "config_from_folder", "register_architecture", "Engine", "StepError",
+__all__ = ["ConfigError", "Qwen3Config", "config_from_folder", "register_architecture", "Engine", "StepError", "Model", "GenerateResult", "SamplingParams",
            "RandomInit", "WeightsError", "write_model_folder"]

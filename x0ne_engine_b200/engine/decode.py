@@ -1,0 +1,162 @@
+"""A batch of sequences on the device: prompts in one step, then one token each per step.
+
+Between two decode steps the token, the position and the draw counter of every sequence stay on
+the device: the sampler kernel writes each pick where the next step reads it and advances the
+position, and the step's launches read them from there.  So a decode step has no host-to-device
+copy, and its launches are captured once per batch size into a CUDA graph and replayed, as the
+library engine does for its single sequence (x0ne-core/runtime/src/engine.rs:484-501,
+1095-1132).  Per step the host reads back one int32 per live sequence.
+
+When sequences finish, the live rows are compacted on the device and the graph of the smaller
+batch size is used.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..cache import CacheFull
+from ..csrc import ops
+from .engine import Engine, StepContext
+from .generate import GenerationError, Row
+
+
+class DeviceBatch:
+    def __init__(self, engine: Engine, max_batch: int, cuda_graph: bool = True):
+        self.engine = engine
+        self.max_batch = max_batch
+        self.cuda_graph = cuda_graph
+        dev = engine.device
+        i32 = dict(dtype=torch.int32, device=dev)
+        self.tokens = torch.zeros(max_batch, **i32)
+        self.row_slot = torch.zeros(max_batch, **i32)
+        self.row_pos = torch.zeros(max_batch, **i32)
+        self.counter = torch.zeros(max_batch, **i32)
+        self.finished = torch.zeros(max_batch, **i32)
+        self.budget = torch.zeros(max_batch, **i32)
+        self.out_token = torch.zeros(max_batch, **i32)
+        self.temperature = torch.zeros(max_batch, dtype=torch.float32, device=dev)
+        self.top_p = torch.ones(max_batch, dtype=torch.float32, device=dev)
+        self.seed = torch.zeros(max_batch, dtype=torch.int64, device=dev)
+        self.seq_first_row = torch.arange(max_batch + 1, **i32)
+        self.want_rows = torch.arange(max_batch, **i32)
+        self.logits = torch.empty((max_batch, engine.vocab_size), dtype=torch.float32, device=dev)
+        self._out_host = torch.zeros(max_batch, dtype=torch.int32).pin_memory()
+        self._per_row = [self.tokens, self.row_slot, self.row_pos, self.counter, self.finished, self.budget,
+                         self.temperature, self.top_p, self.seed]
+        self.stop_ids: Optional[torch.Tensor] = None
+        self.graphs: Dict[int, torch.cuda.CUDAGraph] = {}
+        self.slots: List[int] = []
+        self.rows: Sequence[Row] = ()
+        self.live: List[int] = []
+        self.graph_replays = 0
+        self.eager_steps = 0
+        if engine.ws.max_rows < max_batch:
+            raise ValueError("the engine's largest pass is smaller than the batch")
+
+    # ------------------------------------------------------------------ BatchRunner
+    def start(self, rows: Sequence[Row]) -> List[int]:
+        eng, n = self.engine, len(rows)
+        if n > self.max_batch:
+            raise GenerationError(f"{n} sequences in a batch of at most {self.max_batch}")
+        self.slots = []
+        try:
+            for r in rows:
+                self.slots.append(eng.new_sequence(len(r.prompt) + r.budget))
+        except CacheFull:
+            self.close()
+            raise
+        self.rows, self.live = rows, list(range(n))
+        host = np.zeros((6, n), dtype=np.int64)
+        host[0] = self.slots
+        host[1] = [len(r.prompt) - 1 for r in rows]
+        host[2] = [r.budget for r in rows]
+        host[3] = [r.seed if r.seed < (1 << 63) else r.seed - (1 << 64) for r in rows]
+        meta = torch.from_numpy(host).to(eng.device)
+        self.row_slot[:n] = meta[0].to(torch.int32)
+        self.row_pos[:n] = meta[1].to(torch.int32)
+        self.budget[:n] = meta[2].to(torch.int32)
+        self.seed[:n] = meta[3]
+        self.counter[:n] = 0
+        self.finished[:n] = 0
+        fl = torch.tensor([[r.params.temperature if not r.params.greedy else 0.0 for r in rows],
+                           [r.params.top_p for r in rows]], dtype=torch.float32).to(eng.device)
+        self.temperature[:n] = fl[0]
+        self.top_p[:n] = fl[1]
+        stops = {tuple(sorted(r.params.stop_token_ids)) for r in rows}
+        common = stops.pop() if len(stops) == 1 else ()
+        self.stop_ids = torch.tensor(common, dtype=torch.int32, device=eng.device) if common else None
+        logits = eng.step(self.slots, [r.prompt for r in rows])
+        self._sample(logits, n)
+        return self._read(n)
+
+    def step(self, live: Sequence[int]) -> List[int]:
+        live = list(live)
+        if live != self.live:
+            self._compact(live)
+        n = len(live)
+        if self.cuda_graph:
+            g = self.graphs.get(n)
+            if g is None:
+                g = self._capture(n)
+            g.replay()
+            self.graph_replays += 1
+        else:
+            self._launch(n)
+            self.eager_steps += 1
+        for i in live:
+            self.engine.cache.lengths[self.slots[i]] += 1
+        return self._read(n)
+
+    def close(self) -> None:
+        for s in self.slots:
+            self.engine.free_sequence(s)
+        self.slots, self.rows, self.live = [], (), []
+
+    # ------------------------------------------------------------------ pieces
+    def _sample(self, logits: torch.Tensor, n: int) -> None:
+        ops.sample(logits, n, self.out_token, temperature=self.temperature, top_p=self.top_p, seed=self.seed,
+                   draw_counter=self.counter, stop_ids=self.stop_ids, finished=self.finished, budget=self.budget,
+                   next_token=self.tokens, next_pos=self.row_pos)
+
+    def _read(self, n: int) -> List[int]:
+        self._out_host[:n].copy_(self.out_token[:n], non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        return self._out_host[:n].tolist()
+
+    def _compact(self, live: List[int]) -> None:
+        where = {row: k for k, row in enumerate(self.live)}
+        idx = torch.tensor([where[i] for i in live], dtype=torch.int64, device=self.engine.device)
+        n = len(live)
+        for t in self._per_row:
+            t[:n] = t[idx]
+        self.live = live
+
+    def _launch(self, n: int) -> None:
+        eng = self.engine
+        ctx = StepContext(n_rows=n, tokens=self.tokens, row_slot=self.row_slot, row_pos=self.row_pos,
+                          dtype=eng.dtype, ws=eng.ws, cache=eng.cache, decode=True, n_seqs=n, max_seq_rows=1,
+                          max_context=eng.max_seq_len, seq_first_row=self.seq_first_row, seq_slot=self.row_slot,
+                          seq_pos0=self.row_pos)
+        eng.model.forward(ctx, self.want_rows, n, self.logits)
+        self._sample(self.logits, n)
+
+    def _capture(self, n: int) -> torch.cuda.CUDAGraph:
+        """Captures the launches of one decode step of `n` rows.  The warm-up run before the capture
+        would advance the sequences, so their state is saved and restored around it."""
+        saved = [t[:n].clone() for t in self._per_row]
+        saved_out = self.out_token[:n].clone()
+        torch.cuda.synchronize()
+        self._launch(n)            # lets libraries and the workspace finish their lazy set-up
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            self._launch(n)
+        for t, s in zip(self._per_row, saved):
+            t[:n] = s
+        self.out_token[:n] = saved_out
+        torch.cuda.synchronize()
+        self.graphs[n] = g
+        return g

@@ -34,7 +34,7 @@ class Linear:
                 if out.dtype == torch.bfloat16:
                     torch.mm(x[:m], w.t(), out=out[:m])
                 else:
-                    out[:m] = torch.mm(x[:m], w.t(), out_dtype=torch.float32)
+                    torch.mm(x[:m], w.t(), out_dtype=torch.float32, out=out[:m])
         else:
             raise ops.KernelError(f"no matrix product for weights of {w.dtype}")
         return out
