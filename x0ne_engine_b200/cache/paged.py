@@ -44,7 +44,7 @@ class KVGroup:
         self.n_pages = n_pages
         self.ring_pages = ring_pages if ring_pages is not None else max_seq_pages
         self.table_stride = self.ring_pages
-        self.storage = torch.empty((len(entries), n_pages, 2, need.kv_heads, page_size, need.head_dim),
+        self.storage = torch.zeros((len(entries), n_pages, 2, need.kv_heads, page_size, need.head_dim),
                                    dtype=dtype, device=device)
         self.pool = FreeList(n_pages, "page")
         self.table_host = np.full((n_slots, self.table_stride), -1, dtype=np.int32)

@@ -1,0 +1,569 @@
+// bfloat16 attention over the paged cache on the tensor cores: a varlen causal flash kernel for
+// passes that bring several tokens per sequence, and a split-KV flash-decoding kernel for passes
+// that bring one.
+//
+// What they compute is what the plain kernel computes (attention_generic.cu; formulas from
+// x0ne-core/kernels/cuda/attention.cu:20-59,138-157,165-171,257-269): q head h reads kv head
+// h / (q_heads / kv_heads); the query at position p sees keys max(0, p - window + 1) .. p; scores,
+// running max, exponentials, sums and the output accumulator are float32; one rounding to
+// bfloat16 at the end.  Scores are kept in the log2 domain (scale * log2 e folded into one
+// multiply, exp2f for the exponentials).
+//
+// Both kernels take key tiles of one cache page (64 positions) at a time: a page of one kv head
+// is one contiguous block of 64 x head_dim values, copied to shared memory with 16-byte
+// cp.async, rows padded by 16 bytes so that ldmatrix reads are free of bank conflicts.
+// Tensor-core path: mma.sync m16n8k16 (bf16 in, f32 accumulate).
+// head_dim: any multiple of 16 up to 128 (template); other shapes use the plain kernel.
+#include "common.cuh"
+
+#define PAGE 64
+#define PADE 8  // padding elements per shared-memory row (16 bytes)
+#define LOG2E 1.4426950408889634f
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void cp_async16(void* dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(smem_u32(dst)), "l"(src));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+__device__ __forceinline__ void ldsm_x4(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void mma_bf16(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Copies rows [0, PAGE) of one page of one kv head (K or V) into padded shared memory; rows whose
+// position is past `last_pos` are zero-filled (a page's tail may never have been written).
+template <int HD, int THREADS>
+__device__ __forceinline__ void load_page_tile(bf16* dst, const bf16* src, int first_pos, int last_pos, int tid) {
+    constexpr int CH = HD / 8;  // 16-byte chunks per row
+    for (int c = tid; c < PAGE * CH; c += THREADS) {
+        const int r = c / CH, k = c % CH;
+        bf16* d = dst + r * (HD + PADE) + k * 8;
+        if (src != nullptr && first_pos + r <= last_pos)
+            cp_async16(d, src + r * HD + k * 8);
+        else
+            *reinterpret_cast<uint4*>(d) = make_uint4(0, 0, 0, 0);
+    }
+}
+
+__device__ __forceinline__ const bf16* page_ptr(const PagedCache& c, int slot, int logical_page, int kv_head, int which) {
+    const int page = c.page_table[(int64_t)slot * c.table_stride + (logical_page % c.ring_pages)];
+    if (page < 0 || page >= c.n_pages) return nullptr;
+    return (const bf16*)c.base + (int64_t)page * c.page_stride +
+           ((int64_t)which * c.kv_heads + kv_head) * c.page_size * c.head_dim;
+}
+
+// One warp: S(16 x 16*NT8/2 keys) = Q(16 x HD) K^T from a padded K tile, keys [key0, key0 + 8*NT8).
+template <int HD, int NT8>
+__device__ __forceinline__ void qk_tile(float (*s)[4], const uint32_t (*qf)[4], const bf16* ks, int key0, int lane) {
+#pragma unroll
+    for (int n = 0; n < NT8; ++n)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) s[n][i] = 0.f;
+#pragma unroll
+    for (int kk = 0; kk < HD / 16; ++kk) {
+#pragma unroll
+        for (int n2 = 0; n2 < NT8 / 2; ++n2) {
+            uint32_t b0, b1, b2, b3;
+            const int row = key0 + n2 * 16 + (lane & 7) + ((lane >> 4) << 3);
+            const int col = kk * 16 + (((lane >> 3) & 1) << 3);
+            ldsm_x4(b0, b1, b2, b3, ks + row * (HD + PADE) + col);
+            mma_bf16(s[2 * n2], qf[kk], b0, b1);
+            mma_bf16(s[2 * n2 + 1], qf[kk], b2, b3);
+        }
+    }
+}
+
+// One warp: O(16 x HD) += P(16 x 8*NT8 keys) V from a padded V tile, keys [key0, key0 + 8*NT8).
+template <int HD, int NT8>
+__device__ __forceinline__ void pv_tile(float (*o)[4], const float (*s)[4], const bf16* vs, int key0, int lane) {
+#pragma unroll
+    for (int kk = 0; kk < NT8 / 2; ++kk) {
+        uint32_t a[4];
+        a[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+        a[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+        a[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+        a[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+        for (int n2 = 0; n2 < HD / 16; ++n2) {
+            uint32_t b0, b1, b2, b3;
+            const int row = key0 + kk * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
+            const int col = n2 * 16 + ((lane >> 4) << 3);
+            ldsm_x4_t(b0, b1, b2, b3, vs + row * (HD + PADE) + col);
+            mma_bf16(o[2 * n2], a, b0, b1);
+            mma_bf16(o[2 * n2 + 1], a, b2, b3);
+        }
+    }
+}
+
+// Online-softmax update of one warp's 16 rows with the scores s (already scaled to the log2 domain
+// and masked with -inf); leaves p in s.
+template <int HD, int NT8>
+__device__ __forceinline__ void softmax_update(float (*s)[4], float (*o)[4], float* m, float* l) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        float mx = -INFINITY;
+#pragma unroll
+        for (int n = 0; n < NT8; ++n) mx = fmaxf(mx, fmaxf(s[n][2 * h], s[n][2 * h + 1]));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        const float m_new = fmaxf(m[h], mx);
+        const float base = m_new == -INFINITY ? 0.f : m_new;
+        const float alpha = exp2f(m[h] - base);
+        float sum = 0.f;
+#pragma unroll
+        for (int n = 0; n < NT8; ++n) {
+            s[n][2 * h] = exp2f(s[n][2 * h] - base);
+            s[n][2 * h + 1] = exp2f(s[n][2 * h + 1] - base);
+            sum += s[n][2 * h] + s[n][2 * h + 1];
+        }
+        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+        l[h] = l[h] * alpha + sum;
+        m[h] = m_new;
+#pragma unroll
+        for (int n = 0; n < HD / 8; ++n) {
+            o[n][2 * h] *= alpha;
+            o[n][2 * h + 1] *= alpha;
+        }
+    }
+}
+
+// ----------------------------------------------------------------------------------------
+// Prefill: grid (q_heads, tiles); a tile is up to 64 consecutive rows of one sequence.
+// 4 warps, 16 query rows each.
+// ----------------------------------------------------------------------------------------
+struct PrefillArgs {
+    const bf16* q;
+    bf16* out;
+    const int32_t* tile_seq;       // [tiles]
+    const int32_t* tile_row0;      // [tiles] first row of the tile within the pass
+    const int32_t* seq_first_row;  // [seqs + 1]
+    const int32_t* seq_slot;       // [seqs]
+    const int32_t* seq_pos0;       // [seqs] position of the sequence's first row in this pass
+    int32_t q_heads;
+    int32_t window;
+    float scale_log2;
+};
+
+template <int HD>
+__global__ void __launch_bounds__(128) attention_prefill_kernel(PrefillArgs a, PagedCache cache) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    constexpr int LD = HD + PADE;
+    bf16* qs = reinterpret_cast<bf16*>(smem_raw);   // [64][LD]
+    bf16* ks = qs + 64 * LD;                        // [2][64][LD]
+    bf16* vs = ks + 2 * 64 * LD;                    // [2][64][LD]
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int head = blockIdx.x, tile = blockIdx.y;
+    const int kh = head / (a.q_heads / cache.kv_heads);
+    const int seq = a.tile_seq[tile], row0 = a.tile_row0[tile];
+    const int seq_end = a.seq_first_row[seq + 1];
+    const int nrows = min(64, seq_end - row0);
+    const int slot = a.seq_slot[seq];
+    const int pos_first = a.seq_pos0[seq] + (row0 - a.seq_first_row[seq]);
+    const int pos_last = pos_first + nrows - 1;
+    const int q_dim = a.q_heads * HD;
+
+    // Q tile -> shared (rows past the tile's end are zero)
+    constexpr int CH = HD / 8;
+    for (int c = tid; c < 64 * CH; c += 128) {
+        const int r = c / CH, k = c % CH;
+        bf16* d = qs + r * LD + k * 8;
+        if (r < nrows)
+            cp_async16(d, a.q + (int64_t)(row0 + r) * q_dim + head * HD + k * 8);
+        else
+            *reinterpret_cast<uint4*>(d) = make_uint4(0, 0, 0, 0);
+    }
+    const int j_lo = a.window > 0 ? max(0, pos_first - a.window + 1) : 0;
+    const int kt_lo = j_lo / PAGE, kt_hi = pos_last / PAGE;
+    // first K/V tile
+    load_page_tile<HD, 128>(ks, page_ptr(cache, slot, kt_lo, kh, 0), kt_lo * PAGE, pos_last, tid);
+    load_page_tile<HD, 128>(vs, page_ptr(cache, slot, kt_lo, kh, 1), kt_lo * PAGE, pos_last, tid);
+    cp_async_commit();
+    cp_async_wait<0>();
+    __syncthreads();
+
+    uint32_t qf[HD / 16][4];
+#pragma unroll
+    for (int kk = 0; kk < HD / 16; ++kk) {
+        const int row = warp * 16 + (lane & 15), col = kk * 16 + ((lane >> 4) << 3);
+        ldsm_x4(qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3], qs + row * LD + col);
+    }
+    float o[HD / 8][4];
+#pragma unroll
+    for (int n = 0; n < HD / 8; ++n)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) o[n][i] = 0.f;
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    const int prow[2] = {pos_first + warp * 16 + (lane >> 2), pos_first + warp * 16 + (lane >> 2) + 8};
+
+    for (int kt = kt_lo; kt <= kt_hi; ++kt) {
+        const int buf = (kt - kt_lo) & 1;
+        if (kt + 1 <= kt_hi) {
+            load_page_tile<HD, 128>(ks + (buf ^ 1) * 64 * LD, page_ptr(cache, slot, kt + 1, kh, 0), (kt + 1) * PAGE, pos_last, tid);
+            load_page_tile<HD, 128>(vs + (buf ^ 1) * 64 * LD, page_ptr(cache, slot, kt + 1, kh, 1), (kt + 1) * PAGE, pos_last, tid);
+        }
+        cp_async_commit();
+        const bf16* kb = ks + buf * 64 * LD;
+        const bf16* vb = vs + buf * 64 * LD;
+        // A warp whose rows all lie before this tile's first key has nothing to do here.
+        const int warp_last = min(pos_last, pos_first + warp * 16 + 15);
+        if (kt * PAGE <= warp_last) {
+            float s[8][4];
+            qk_tile<HD, 8>(s, qf, kb, 0, lane);
+            const bool edge = (kt * PAGE + PAGE - 1 > pos_first + warp * 16) ||
+                              (a.window > 0 && kt * PAGE <= warp_last - a.window + 16);
+#pragma unroll
+            for (int n = 0; n < 8; ++n)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    float v = s[n][i] * a.scale_log2;
+                    if (edge) {
+                        const int j = kt * PAGE + n * 8 + ((lane & 3) << 1) + (i & 1);
+                        const int p = prow[i >> 1];
+                        if (j > p || p > pos_last || (a.window > 0 && j <= p - a.window)) v = -INFINITY;
+                    }
+                    s[n][i] = v;
+                }
+            softmax_update<HD, 8>(s, o, m, l);
+            pv_tile<HD, 8>(o, s, vb, 0, lane);
+        }
+        cp_async_wait<0>();
+        __syncthreads();
+    }
+    // write
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int r = warp * 16 + (lane >> 2) + 8 * h;
+        if (r < nrows) {
+            const float inv = 1.0f / l[h];
+            bf16* dst = a.out + (int64_t)(row0 + r) * q_dim + head * HD + ((lane & 3) << 1);
+#pragma unroll
+            for (int n = 0; n < HD / 8; ++n)
+                *reinterpret_cast<uint32_t*>(dst + n * 8) = pack_bf16(o[n][2 * h] * inv, o[n][2 * h + 1] * inv);
+        }
+    }
+}
+
+// ----------------------------------------------------------------------------------------
+// Decode: one query row per sequence.  grid (splits, kv_heads * group_chunks, sequences); a block
+// serves up to 16 q heads of one kv head (they are the 16 rows of the MMA tile) over its share of
+// the sequence's pages.  The 4 warps take 16 keys each of every 64-key page, each with its own
+// running (m, l, o); they are merged in shared memory at the end, and the blocks of one
+// (sequence, kv head) are merged by whichever of them finishes last, in the fixed order of the
+// splits (the last-arriver scheme of x0ne-core/kernels/cuda/attention.cu:439-455: nobody waits).
+// ----------------------------------------------------------------------------------------
+struct DecodeArgs {
+    const bf16* q;
+    bf16* out;
+    const int32_t* row_slot;
+    const int32_t* row_pos;
+    float* part_o;         // [rows * q_heads][splits][HD]
+    float* part_ml;        // [rows * q_heads][splits][2]
+    int32_t* counters;     // [rows * kv_heads * group_chunks], zero before the launch, zero after
+    int32_t q_heads;
+    int32_t window;
+    int32_t splits;
+    float scale_log2;
+};
+
+template <int HD, int STAGES>
+__global__ void __launch_bounds__(128) attention_decode_kernel(DecodeArgs a, PagedCache cache) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    constexpr int LD = HD + PADE;
+    bf16* qs = reinterpret_cast<bf16*>(smem_raw);   // [16][LD]
+    bf16* ks = qs + 16 * LD;                        // [STAGES][64][LD]
+    bf16* vs = ks + STAGES * 64 * LD;               // [STAGES][64][LD]
+    __shared__ int s_last;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int split = blockIdx.x, b = blockIdx.z;
+    const int G = a.q_heads / cache.kv_heads;
+    const int gchunks = (G + 15) / 16;
+    const int kh = blockIdx.y / gchunks, gc = blockIdx.y % gchunks;
+    const int head0 = kh * G + gc * 16;
+    const int nheads = min(16, G - gc * 16);
+    const int slot = a.row_slot[b], pos = a.row_pos[b];
+    const int q_dim = a.q_heads * HD;
+
+    constexpr int CH = HD / 8;
+    for (int c = tid; c < 16 * CH; c += 128) {
+        const int r = c / CH, k = c % CH;
+        bf16* d = qs + r * LD + k * 8;
+        if (r < nheads)
+            cp_async16(d, a.q + (int64_t)b * q_dim + (head0 + r) * HD + k * 8);
+        else
+            *reinterpret_cast<uint4*>(d) = make_uint4(0, 0, 0, 0);
+    }
+    const int j_lo = a.window > 0 ? max(0, pos - a.window + 1) : 0;
+    const int pg_first = j_lo / PAGE, pg_count = pos / PAGE - pg_first + 1;
+    const int p_lo = pg_first + (int)(((int64_t)pg_count * split) / a.splits);
+    const int p_hi = pg_first + (int)(((int64_t)pg_count * (split + 1)) / a.splits);   // exclusive
+    const int n_pages = p_hi - p_lo;
+
+    // prologue: up to STAGES - 1 pages in flight
+#pragma unroll
+    for (int s = 0; s < STAGES - 1; ++s) {
+        if (s < n_pages) {
+            load_page_tile<HD, 128>(ks + s * 64 * LD, page_ptr(cache, slot, p_lo + s, kh, 0), (p_lo + s) * PAGE, pos, tid);
+            load_page_tile<HD, 128>(vs + s * 64 * LD, page_ptr(cache, slot, p_lo + s, kh, 1), (p_lo + s) * PAGE, pos, tid);
+        }
+        cp_async_commit();
+    }
+    float o[HD / 8][4];
+#pragma unroll
+    for (int n = 0; n < HD / 8; ++n)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) o[n][i] = 0.f;
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    uint32_t qf[HD / 16][4];
+
+    for (int it = 0; it < n_pages; ++it) {
+        cp_async_wait<STAGES - 2>();
+        __syncthreads();
+        if (it == 0) {
+#pragma unroll
+            for (int kk = 0; kk < HD / 16; ++kk) {
+                const int row = lane & 15, col = kk * 16 + ((lane >> 4) << 3);
+                ldsm_x4(qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3], qs + row * LD + col);
+            }
+        }
+        {   // refill the stage that was consumed in the previous iteration
+            const int nx = it + STAGES - 1;
+            if (nx < n_pages) {
+                const int st = nx % STAGES;
+                load_page_tile<HD, 128>(ks + st * 64 * LD, page_ptr(cache, slot, p_lo + nx, kh, 0), (p_lo + nx) * PAGE, pos, tid);
+                load_page_tile<HD, 128>(vs + st * 64 * LD, page_ptr(cache, slot, p_lo + nx, kh, 1), (p_lo + nx) * PAGE, pos, tid);
+            }
+            cp_async_commit();
+        }
+        const int st = it % STAGES;
+        const int pg = p_lo + it;
+        const int key0 = warp * 16;
+        if (pg * PAGE + key0 <= pos) {
+            float s[2][4];
+            qk_tile<HD, 2>(s, qf, ks + st * 64 * LD, key0, lane);
+            const bool edge = (pg * PAGE + key0 + 15 > pos) || (a.window > 0 && pg * PAGE + key0 < j_lo);
+#pragma unroll
+            for (int n = 0; n < 2; ++n)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    float v = s[n][i] * a.scale_log2;
+                    if (edge) {
+                        const int j = pg * PAGE + key0 + n * 8 + ((lane & 3) << 1) + (i & 1);
+                        if (j > pos || j < j_lo) v = -INFINITY;
+                    }
+                    s[n][i] = v;
+                }
+            softmax_update<HD, 2>(s, o, m, l);
+            pv_tile<HD, 2>(o, s, vs + st * 64 * LD, key0, lane);
+        }
+    }
+    cp_async_wait<0>();
+    __syncthreads();
+
+    // merge the 4 warps through shared memory (the K/V stages are free now)
+    float* mo = reinterpret_cast<float*>(ks);            // [4][16][HD]
+    float* mml = mo + 4 * 16 * HD;                       // [4][16][2]
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int r = (lane >> 2) + 8 * h;
+#pragma unroll
+        for (int n = 0; n < HD / 8; ++n) {
+            float* d = mo + (warp * 16 + r) * HD + n * 8 + ((lane & 3) << 1);
+            d[0] = o[n][2 * h];
+            d[1] = o[n][2 * h + 1];
+        }
+        if ((lane & 3) == 0) {
+            mml[(warp * 16 + r) * 2] = m[h];
+            mml[(warp * 16 + r) * 2 + 1] = l[h];
+        }
+    }
+    __syncthreads();
+    const int64_t qrow0 = (int64_t)b * a.q_heads + head0;
+    for (int e = tid; e < nheads * HD; e += 128) {
+        const int r = e / HD, d = e % HD;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) M = fmaxf(M, mml[(w * 16 + r) * 2]);
+        float acc = 0.f, L = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float mw = mml[(w * 16 + r) * 2];
+            const float f = mw == -INFINITY ? 0.f : exp2f(mw - M);
+            acc += mo[(w * 16 + r) * HD + d] * f;
+            L += mml[(w * 16 + r) * 2 + 1] * f;
+        }
+        if (a.splits == 1) {
+            a.out[(qrow0 + r) * HD + d] = __float2bfloat16_rn(acc / L);
+        } else {
+            a.part_o[((qrow0 + r) * a.splits + split) * HD + d] = acc;
+            if (d == 0) {
+                a.part_ml[((qrow0 + r) * a.splits + split) * 2] = M;
+                a.part_ml[((qrow0 + r) * a.splits + split) * 2 + 1] = L;
+            }
+        }
+    }
+    if (a.splits == 1) return;
+
+    // last arriver merges the splits in their fixed order
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        int32_t* cnt = a.counters + ((int64_t)b * cache.kv_heads * gchunks + blockIdx.y);
+        const int prev = atomicAdd(cnt, 1);
+        s_last = prev == a.splits - 1;
+        if (s_last) *cnt = 0;
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    for (int e = tid; e < nheads * HD; e += 128) {
+        const int r = e / HD, d = e % HD;
+        const float* ml = a.part_ml + (qrow0 + r) * a.splits * 2;
+        const float* po = a.part_o + (qrow0 + r) * a.splits * HD;
+        float M = -INFINITY;
+        for (int s = 0; s < a.splits; ++s) M = fmaxf(M, __ldcg(ml + 2 * s));
+        float acc = 0.f, L = 0.f;
+        for (int s = 0; s < a.splits; ++s) {
+            const float ms = __ldcg(ml + 2 * s);
+            const float f = ms == -INFINITY ? 0.f : exp2f(ms - M);
+            acc += __ldcg(po + s * HD + d) * f;
+            L += __ldcg(ml + 2 * s + 1) * f;
+        }
+        a.out[(qrow0 + r) * HD + d] = __float2bfloat16_rn(acc / L);
+    }
+}
+
+// ----------------------------------------------------------------------------------------
+// host
+// ----------------------------------------------------------------------------------------
+template <int HD>
+static int launch_prefill(const PrefillArgs& a, const PagedCache& cache, int n_tiles, cudaStream_t stream) {
+    const size_t smem = (size_t)(64 + 4 * 64) * (HD + PADE) * sizeof(bf16);
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) {
+            x0ne_set_error("attention_prefill: cannot set %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
+            return (int)e;
+        }
+        configured = true;
+    }
+    dim3 grid(a.q_heads, n_tiles);
+    attention_prefill_kernel<HD><<<grid, 128, smem, stream>>>(a, cache);
+    X0NE_LAUNCH_CHECK();
+}
+
+#define DECODE_STAGES 3
+template <int HD>
+static int launch_decode(const DecodeArgs& a, const PagedCache& cache, int n_rows, cudaStream_t stream) {
+    size_t smem = (size_t)(16 + 2 * DECODE_STAGES * 64) * (HD + PADE) * sizeof(bf16);
+    const size_t merge = (size_t)(4 * 16 * HD + 4 * 16 * 2) * sizeof(float);
+    if (smem < 16 * (HD + PADE) * sizeof(bf16) + merge) smem = 16 * (HD + PADE) * sizeof(bf16) + merge;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<HD, DECODE_STAGES>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) {
+            x0ne_set_error("attention_decode: cannot set %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
+            return (int)e;
+        }
+        configured = true;
+    }
+    const int G = a.q_heads / cache.kv_heads;
+    dim3 grid(a.splits, cache.kv_heads * ((G + 15) / 16), n_rows);
+    attention_decode_kernel<HD, DECODE_STAGES><<<grid, 128, smem, stream>>>(a, cache);
+    X0NE_LAUNCH_CHECK();
+}
+
+#define DISPATCH_HD(HDV, CALL)                     \
+    switch (HDV) {                                 \
+        case 16: { constexpr int HD_ = 16; CALL; } \
+        case 32: { constexpr int HD_ = 32; CALL; } \
+        case 48: { constexpr int HD_ = 48; CALL; } \
+        case 64: { constexpr int HD_ = 64; CALL; } \
+        case 80: { constexpr int HD_ = 80; CALL; } \
+        case 96: { constexpr int HD_ = 96; CALL; } \
+        case 112: { constexpr int HD_ = 112; CALL; } \
+        case 128: { constexpr int HD_ = 128; CALL; } \
+        default: break;                            \
+    }
+
+static int check_common(const PagedCache& cache, int q_heads, const char* what) {
+    X0NE_REQUIRE(cache.page_size == PAGE, "%s: pages of %d positions, the kernel takes %d", what, cache.page_size, PAGE);
+    X0NE_REQUIRE(cache.head_dim % 16 == 0 && cache.head_dim >= 16 && cache.head_dim <= 128,
+                 "%s: head_dim %d is not a multiple of 16 between 16 and 128 (use the plain kernel)", what, cache.head_dim);
+    X0NE_REQUIRE(q_heads > 0 && cache.kv_heads > 0 && q_heads % cache.kv_heads == 0, "%s: %d q heads over %d kv heads",
+                 what, q_heads, cache.kv_heads);
+    return 0;
+}
+
+X0NE_API int x0ne_attention_prefill_bf16(const void* q, void* out, PagedCache cache, const int32_t* tile_seq,
+                                         const int32_t* tile_row0, int n_tiles, const int32_t* seq_first_row,
+                                         const int32_t* seq_slot, const int32_t* seq_pos0, int q_heads, float scale,
+                                         int window, cudaStream_t stream) {
+    if (int e = check_common(cache, q_heads, "attention_prefill")) return e;
+    X0NE_REQUIRE(n_tiles >= 0 && n_tiles <= 65535, "attention_prefill: %d tiles in one launch (limit 65535)", n_tiles);
+    X0NE_REQUIRE(window >= 0, "attention_prefill: negative window");
+    if (n_tiles == 0) return 0;
+    PrefillArgs a{(const bf16*)q, (bf16*)out, tile_seq, tile_row0, seq_first_row, seq_slot, seq_pos0, q_heads, window,
+                  scale * LOG2E};
+    DISPATCH_HD(cache.head_dim, return launch_prefill<HD_>(a, cache, n_tiles, stream));
+    X0NE_REQUIRE(false, "attention_prefill: head_dim %d not built", cache.head_dim);
+}
+
+// Scratch the decode kernel needs for `n_rows` sequences with `splits` splits, in bytes:
+// partial outputs, partial (m, l), and the arrival counters (which must start at zero).
+X0NE_API int64_t x0ne_attention_decode_scratch_bytes(int n_rows, int q_heads, int kv_heads, int head_dim, int splits) {
+    const int G = q_heads / kv_heads, gchunks = (G + 15) / 16;
+    const int64_t po = (int64_t)n_rows * q_heads * splits * head_dim * 4;
+    const int64_t ml = (int64_t)n_rows * q_heads * splits * 2 * 4;
+    const int64_t cn = (int64_t)n_rows * kv_heads * gchunks * 4;
+    return po + ml + ((cn + 255) / 256) * 256;
+}
+
+X0NE_API int x0ne_attention_decode_bf16(const void* q, void* out, PagedCache cache, const int32_t* row_slot,
+                                        const int32_t* row_pos, int n_rows, int q_heads, float scale, int window,
+                                        int splits, void* scratch, int64_t scratch_bytes, cudaStream_t stream) {
+    if (int e = check_common(cache, q_heads, "attention_decode")) return e;
+    X0NE_REQUIRE(n_rows >= 0 && n_rows <= 65535, "attention_decode: %d rows in one launch (limit 65535)", n_rows);
+    X0NE_REQUIRE(splits >= 1 && splits <= 1024, "attention_decode: %d splits", splits);
+    X0NE_REQUIRE(window >= 0, "attention_decode: negative window");
+    if (n_rows == 0) return 0;
+    DecodeArgs a{};
+    a.q = (const bf16*)q;
+    a.out = (bf16*)out;
+    a.row_slot = row_slot;
+    a.row_pos = row_pos;
+    a.q_heads = q_heads;
+    a.window = window;
+    a.splits = splits;
+    a.scale_log2 = scale * LOG2E;
+    if (splits > 1) {
+        const int64_t need = x0ne_attention_decode_scratch_bytes(n_rows, q_heads, cache.kv_heads, cache.head_dim, splits);
+        X0NE_REQUIRE(scratch != nullptr && scratch_bytes >= need, "attention_decode: scratch of %lld bytes, %lld needed",
+                     (long long)scratch_bytes, (long long)need);
+        const int G = q_heads / cache.kv_heads, gchunks = (G + 15) / 16;
+        const int64_t cn = (((int64_t)n_rows * cache.kv_heads * gchunks * 4 + 255) / 256) * 256;
+        a.counters = (int32_t*)scratch;
+        a.part_ml = (float*)((char*)scratch + cn);
+        a.part_o = a.part_ml + (int64_t)n_rows * q_heads * splits * 2;
+    }
+    DISPATCH_HD(cache.head_dim, return launch_decode<HD_>(a, cache, n_rows, stream));
+    X0NE_REQUIRE(false, "attention_decode: head_dim %d not built", cache.head_dim);
+}

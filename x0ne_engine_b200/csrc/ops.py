@@ -62,7 +62,12 @@ def loaded_libraries():
     return [lib._name for lib in _libs.values()]
 
 
+LAUNCHES = 0   # kernel entry points called by this process (one or a few launches each)
+
+
 def _check(lib, code: int, what: str) -> None:
+    global LAUNCHES
+    LAUNCHES += 1
     if code != 0:
         msg = lib.x0ne_last_error()
         raise KernelError(f"{what}: {msg.decode() if msg else 'error'} (code {code})")
@@ -215,3 +220,67 @@ def sample(logits: torch.Tensor, n_rows: int, out_token: torch.Tensor, *, temper
                      _ptr(stop_ids if n_stop else None), _ptr(finished), _ptr(budget), _ptr(out_token),
                      _ptr(next_token), _ptr(next_pos), logits.stride(0), logits.shape[1], n_stop)
     _check(lib, lib.x0ne_sample(io, c_int(n_rows), _stream()), "sample")
+
+
+# ---------------------------------------------------------------------------------------------
+# bfloat16 tensor-core attention (module `fast`)
+# ---------------------------------------------------------------------------------------------
+def fast_attention_takes(cache: PagedCacheArg, dtype: torch.dtype) -> bool:
+    """Whether the tensor-core attention kernels take this shape; otherwise the plain kernel does."""
+    return dtype == torch.bfloat16 and cache.page_size == 64 and cache.head_dim % 16 == 0 \
+        and 16 <= cache.head_dim <= 128
+
+
+def attention_prefill_bf16(q: torch.Tensor, out: torch.Tensor, cache: PagedCacheArg, tile_seq: torch.Tensor,
+                           tile_row0: torch.Tensor, n_tiles: int, seq_first_row: torch.Tensor,
+                           seq_slot: torch.Tensor, seq_pos0: torch.Tensor, q_heads: int, scale: float,
+                           window: int = 0) -> None:
+    """Causal flash attention of a pass whose sequences bring several rows; a tile is up to 64
+    consecutive rows of one sequence."""
+    lib = _lib("fast")
+    _need(q, torch.bfloat16, "q")
+    _need(out, torch.bfloat16, "attention output")
+    for t, what in ((tile_seq, "tile sequences"), (tile_row0, "tile rows"), (seq_first_row, "sequence rows"),
+                    (seq_slot, "sequence slots"), (seq_pos0, "sequence positions")):
+        _need(t, torch.int32, what)
+    if tile_seq.numel() < n_tiles or tile_row0.numel() < n_tiles:
+        raise KernelError("attention_prefill: tile tables shorter than the tiles asked for")
+    if q.shape[-1] != q_heads * cache.head_dim or out.shape[-1] != q.shape[-1]:
+        raise KernelError("attention_prefill: q or output width does not match the head counts")
+    for first in range(0, n_tiles, 65535):
+        n = min(65535, n_tiles - first)
+        _check(lib, lib.x0ne_attention_prefill_bf16(
+            _ptr(q), _ptr(out), cache, c_void_p(tile_seq.data_ptr() + 4 * first),
+            c_void_p(tile_row0.data_ptr() + 4 * first), c_int(n), _ptr(seq_first_row), _ptr(seq_slot), _ptr(seq_pos0),
+            c_int(q_heads), c_float(scale), c_int(window), _stream()), "attention_prefill_bf16")
+
+
+def attention_decode_scratch_bytes(n_rows: int, q_heads: int, kv_heads: int, head_dim: int, splits: int) -> int:
+    lib = _lib("fast")
+    lib.x0ne_attention_decode_scratch_bytes.restype = c_int64
+    return int(lib.x0ne_attention_decode_scratch_bytes(c_int(n_rows), c_int(q_heads), c_int(kv_heads),
+                                                       c_int(head_dim), c_int(splits)))
+
+
+def attention_decode_bf16(q: torch.Tensor, out: torch.Tensor, cache: PagedCacheArg, row_slot: torch.Tensor,
+                          row_pos: torch.Tensor, n_rows: int, q_heads: int, scale: float, window: int, splits: int,
+                          scratch: Optional[torch.Tensor]) -> None:
+    """Split-KV flash decoding: one query row per sequence.  `scratch` (uint8, zero when first
+    used; the kernel leaves its counters at zero) holds the partial results when splits > 1."""
+    lib = _lib("fast")
+    _need(q, torch.bfloat16, "q")
+    _need(out, torch.bfloat16, "attention output")
+    _need(row_slot, torch.int32, "row slots")
+    _need(row_pos, torch.int32, "row positions")
+    width = q_heads * cache.head_dim
+    if q.shape[-1] != width or out.shape[-1] != width or q.numel() < n_rows * width or out.numel() < n_rows * width:
+        raise KernelError("attention_decode: q or output do not match the head counts and rows")
+    if row_slot.numel() < n_rows or row_pos.numel() < n_rows:
+        raise KernelError("attention_decode: row tables shorter than the rows asked for")
+    nbytes = 0
+    if scratch is not None:
+        _need(scratch, torch.uint8, "decode scratch")
+        nbytes = scratch.numel()
+    _check(lib, lib.x0ne_attention_decode_bf16(
+        _ptr(q), _ptr(out), cache, _ptr(row_slot), _ptr(row_pos), c_int(n_rows), c_int(q_heads), c_float(scale),
+        c_int(window), c_int(splits), _ptr(scratch), c_int64(nbytes), _stream()), "attention_decode_bf16")

@@ -52,6 +52,7 @@ class DeviceBatch:
         self.rows: Sequence[Row] = ()
         self.live: List[int] = []
         self.graph_replays = 0
+        self.launches_per_step = 0      # calls of this library's kernel entry points in one decode step
         self.eager_steps = 0
         if engine.ws.max_rows < max_batch:
             raise ValueError("the engine's largest pass is smaller than the batch")
@@ -139,7 +140,7 @@ class DeviceBatch:
         ctx = StepContext(n_rows=n, tokens=self.tokens, row_slot=self.row_slot, row_pos=self.row_pos,
                           dtype=eng.dtype, ws=eng.ws, cache=eng.cache, decode=True, n_seqs=n, max_seq_rows=1,
                           max_context=eng.max_seq_len, seq_first_row=self.seq_first_row, seq_slot=self.row_slot,
-                          seq_pos0=self.row_pos)
+                          seq_pos0=self.row_pos, sm_count=eng.sm_count)
         eng.model.forward(ctx, self.want_rows, n, self.logits)
         self._sample(self.logits, n)
 
@@ -149,7 +150,9 @@ class DeviceBatch:
         saved = [t[:n].clone() for t in self._per_row]
         saved_out = self.out_token[:n].clone()
         torch.cuda.synchronize()
+        before = ops.LAUNCHES
         self._launch(n)            # lets libraries and the workspace finish their lazy set-up
+        self.launches_per_step = ops.LAUNCHES - before
         torch.cuda.synchronize()
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g):

@@ -52,6 +52,10 @@ class StepContext:
     seq_first_row: Optional[torch.Tensor] = None   # int32 [n_seqs + 1]
     seq_slot: Optional[torch.Tensor] = None        # int32 [n_seqs]
     seq_pos0: Optional[torch.Tensor] = None        # int32 [n_seqs]: position of the sequence's first row
+    n_tiles: int = 0                               # tiles of up to 64 consecutive rows of one sequence
+    tile_seq: Optional[torch.Tensor] = None        # int32 [n_tiles]
+    tile_row0: Optional[torch.Tensor] = None       # int32 [n_tiles]
+    sm_count: int = 148
 
 
 def require_gpu(device) -> torch.device:
@@ -82,12 +86,12 @@ class Engine:
         self.ws = Workspace(self.max_step_tokens, self.device)
         self.ws.max_want = self.max_step_tokens
         # pass metadata: tokens, slots, positions, wanted rows; a small ring of pinned staging buffers
-        self._meta_dev = torch.zeros((4, self.max_step_tokens), dtype=torch.int32, device=self.device)
-        self._stage = [torch.zeros((4, self.max_step_tokens), dtype=torch.int32).pin_memory() for _ in range(4)]
+        self._meta_dev = torch.zeros((6, self.max_step_tokens), dtype=torch.int32, device=self.device)
+        self._stage = [torch.zeros((6, self.max_step_tokens), dtype=torch.int32).pin_memory() for _ in range(4)]
         self._stage_events: List[Optional[torch.cuda.Event]] = [None] * len(self._stage)
         self._stage_at = 0
         self._seq_dev = torch.zeros((3, self.max_step_tokens + 1), dtype=torch.int32, device=self.device)
-        self.launch_count = 0
+        self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
 
     # ------------------------------------------------------------------ construction
     @classmethod
@@ -210,13 +214,20 @@ class Engine:
         nw = len(want_rows)
         if nw:
             stage[3, :nw] = torch.from_numpy(want_rows.astype(np.int32))
+        # sequence-level view of the pass (for kernels that work per sequence) and its row tiles
+        seq_ids = [i for i in range(len(slots)) if first_row[i] < r1 and first_row[i + 1] > r0]
+        sfirst = np.asarray([max(first_row[i], r0) - r0 for i in seq_ids] + [r1 - r0], dtype=np.int32)
+        counts = np.diff(sfirst)
+        tiles_per = (counts + 63) // 64
+        n_tiles = int(tiles_per.sum())
+        tile_seq = np.repeat(np.arange(len(seq_ids), dtype=np.int32), tiles_per)
+        tile_k = np.arange(n_tiles, dtype=np.int32) - np.repeat(np.cumsum(tiles_per) - tiles_per, tiles_per).astype(np.int32)
+        stage[4, :n_tiles] = torch.from_numpy(tile_seq)
+        stage[5, :n_tiles] = torch.from_numpy(sfirst[tile_seq] + 64 * tile_k)
         self._meta_dev.copy_(stage, non_blocking=True)
         ev = torch.cuda.Event()
         ev.record()
         self._stage_events[si] = ev
-        # sequence-level view of the pass (for kernels that work per sequence)
-        seq_ids = [i for i in range(len(slots)) if first_row[i] < r1 and first_row[i + 1] > r0]
-        sfirst = np.asarray([max(first_row[i], r0) - r0 for i in seq_ids] + [r1 - r0], dtype=np.int32)
         sslot = np.asarray([slots[i] for i in seq_ids], dtype=np.int32)
         spos0 = np.asarray([starts[i] + (max(first_row[i], r0) - first_row[i]) for i in seq_ids], dtype=np.int32)
         ns = len(seq_ids)
@@ -229,7 +240,8 @@ class Engine:
             n_rows=n, tokens=self._meta_dev[0], row_slot=self._meta_dev[1], row_pos=self._meta_dev[2],
             dtype=self.dtype, ws=self.ws, cache=self.cache, decode=decode, n_seqs=ns,
             max_seq_rows=int(np.max(np.diff(sfirst))), max_context=int(rpos.max()) + 1,
-            seq_first_row=self._seq_dev[0], seq_slot=self._seq_dev[1], seq_pos0=self._seq_dev[2])
+            seq_first_row=self._seq_dev[0], seq_slot=self._seq_dev[1], seq_pos0=self._seq_dev[2],
+            n_tiles=n_tiles, tile_seq=self._meta_dev[4], tile_row0=self._meta_dev[5], sm_count=self.sm_count)
         if nw == 0:
             self.model.forward(ctx, None, 0, None)
         elif nw == logits.shape[0] and np.array_equal(want_dest, np.arange(nw)):

@@ -31,5 +31,16 @@ class Workspace:
             self._bufs[name] = t
         return t[:n].view(shape)
 
+    def zeroed(self, name: str, nbytes: int) -> torch.Tensor:
+        """A uint8 buffer that is zero when first handed out and whose user leaves it zero where it
+        needs zeros (arrival counters); grown, and zeroed again, when a larger one is asked for."""
+        t = self._bufs.get(name)
+        if t is None or t.numel() < nbytes:
+            if self.frozen:
+                raise RuntimeError(f"workspace buffer {name!r} would be reallocated after the workspace was frozen")
+            t = torch.zeros(max(nbytes, 1), dtype=torch.uint8, device=self.device)
+            self._bufs[name] = t
+        return t
+
     def bytes(self) -> int:
         return sum(t.numel() * t.element_size() for t in self._bufs.values())

@@ -16,7 +16,28 @@ from .linear import Linear
 def run_attention(ctx, q, out, view, n_rows, q_heads, scale, window):
     """Chooses the attention kernel for this step: the tensor-core kernels where they take the
     shape, else the plain kernel (which is also the whole 32-bit path)."""
-    ops.attention_rows(q, out, view, ctx.row_slot, ctx.row_pos, n_rows, q_heads, scale, window)
+    if not ops.fast_attention_takes(view, q.dtype):
+        ops.attention_rows(q, out, view, ctx.row_slot, ctx.row_pos, n_rows, q_heads, scale, window)
+    elif ctx.decode:
+        splits = decode_splits(ctx, n_rows, view.kv_heads, q_heads)
+        scratch = None
+        if splits > 1:
+            need = ops.attention_decode_scratch_bytes(n_rows, q_heads, view.kv_heads, view.head_dim, splits)
+            scratch = ctx.ws.zeroed("attn.decode_scratch", need)
+        ops.attention_decode_bf16(q, out, view, ctx.row_slot, ctx.row_pos, n_rows, q_heads, scale, window, splits,
+                                  scratch)
+    else:
+        ops.attention_prefill_bf16(q, out, view, ctx.tile_seq, ctx.tile_row0, ctx.n_tiles, ctx.seq_first_row,
+                                   ctx.seq_slot, ctx.seq_pos0, q_heads, scale, window)
+
+
+def decode_splits(ctx, n_rows: int, kv_heads: int, q_heads: int) -> int:
+    """Into how many blocks each (sequence, kv head) of a decode pass is split: enough to give
+    every SM about two blocks, and no more than the longest context has pages."""
+    group_chunks = (q_heads // kv_heads + 15) // 16
+    blocks = max(1, n_rows * kv_heads * group_chunks)
+    pages = max(1, (ctx.max_context + 63) // 64)
+    return int(max(1, min(pages, (2 * ctx.sm_count + blocks - 1) // blocks, 64)))
 
 
 class GQAttention(Mixer):
