@@ -30,7 +30,7 @@ NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-Xcompil
 # module name -> sources.  `core` is all a 32-bit run needs; `fast` holds the bfloat16 kernels.
 MODULES: Dict[str, List[str]] = {
     "core": ["elementwise.cu", "attention_generic.cu", "gemm_f32.cu", "sampling.cu"],
-    "fast": ["attention_bf16.cu", "fast_common.cu"],
+    "fast": ["attention_bf16.cu", "gemm_bf16.cu", "fast_common.cu"],
 }
 HEADERS = ["common.cuh"]
 

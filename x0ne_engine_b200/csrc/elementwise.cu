@@ -82,10 +82,94 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const T* __restric
     for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = from_f32<T>(r[i] * scale * w[i]);
 }
 
+// The same, for hidden % 8 == 0 and hidden <= 8 * 1024 * VEC_IT: 16-byte accesses, and the row stays
+// in registers between the sum of squares and the scaling, so it is read once.
+#define VEC_IT 4
+__device__ __forceinline__ void load8(const float* p, float* v) {
+    const float4 a = reinterpret_cast<const float4*>(p)[0], b = reinterpret_cast<const float4*>(p)[1];
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+__device__ __forceinline__ void load8(const bf16* p, float* v) {
+    const uint4 u = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 f = __bfloat1622float2(h[i]);
+        v[2 * i] = f.x;
+        v[2 * i + 1] = f.y;
+    }
+}
+__device__ __forceinline__ void store8(float* p, const float* v) {
+    reinterpret_cast<float4*>(p)[0] = make_float4(v[0], v[1], v[2], v[3]);
+    reinterpret_cast<float4*>(p)[1] = make_float4(v[4], v[5], v[6], v[7]);
+}
+__device__ __forceinline__ void store8(bf16* p, const float* v) {
+    uint4 u;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+    *reinterpret_cast<uint4*>(p) = u;
+}
+
+template <typename T>
+__global__ void add_rmsnorm_vec_kernel(float* __restrict__ resid, const T* __restrict__ delta,
+                                       const float* __restrict__ w, T* __restrict__ out,
+                                       const int32_t* __restrict__ rows, int hidden, float eps) {
+    __shared__ float sh[32];
+    const int64_t src = rows ? rows[blockIdx.x] : blockIdx.x;
+    float* r = resid + src * hidden;
+    const T* d = delta ? delta + src * hidden : nullptr;
+    T* o = out + (int64_t)blockIdx.x * hidden;
+    float v[VEC_IT][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int it = 0; it < VEC_IT; ++it) {
+        const int i = (it * blockDim.x + threadIdx.x) * 8;
+        if (i < hidden) {
+            load8(r + i, v[it]);
+            if (d) {
+                float dv[8];
+                load8(d + i, dv);
+#pragma unroll
+                for (int k = 0; k < 8; ++k) v[it][k] = v[it][k] + dv[k];
+                store8(r + i, v[it]);
+            }
+#pragma unroll
+            for (int k = 0; k < 8; ++k) ss += v[it][k] * v[it][k];
+        }
+    }
+    const float total = block_sum(ss, sh);
+    const float scale = 1.0f / sqrtf(total / (float)hidden + eps);
+#pragma unroll
+    for (int it = 0; it < VEC_IT; ++it) {
+        const int i = (it * blockDim.x + threadIdx.x) * 8;
+        if (i < hidden) {
+            float wv[8], ov[8];
+            load8(w + i, wv);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) ov[k] = v[it][k] * scale * wv[k];
+            store8(o + i, ov);
+        }
+    }
+}
+
 X0NE_API int x0ne_add_rmsnorm(float* resid, const void* delta, const float* w, void* out, int dt,
                               const int32_t* rows, int n_rows, int hidden, float eps, cudaStream_t stream) {
     X0NE_REQUIRE(n_rows >= 0 && hidden > 0, "add_rmsnorm: rows %d hidden %d", n_rows, hidden);
     if (n_rows == 0) return 0;
+    if (hidden % 8 == 0 && hidden <= 8 * 1024 * VEC_IT &&
+        ((((uintptr_t)resid | (uintptr_t)delta | (uintptr_t)w | (uintptr_t)out) & 15) == 0)) {
+        int threads = (hidden / 8 + 31) / 32 * 32;
+        if (threads > 1024) threads = 1024;
+        if (hidden / 8 > 512 && hidden / 8 <= 1024) threads = 512;   // two sweeps of 512 rather than one of 1024
+        if (dt == X0NE_F32)
+            add_rmsnorm_vec_kernel<float><<<n_rows, threads, 0, stream>>>(resid, (const float*)delta, w, (float*)out, rows, hidden, eps);
+        else if (dt == X0NE_BF16)
+            add_rmsnorm_vec_kernel<bf16><<<n_rows, threads, 0, stream>>>(resid, (const bf16*)delta, w, (bf16*)out, rows, hidden, eps);
+        else
+            X0NE_REQUIRE(false, "add_rmsnorm: unknown dtype tag %d", dt);
+        X0NE_LAUNCH_CHECK();
+    }
     const int block = 256;
     if (dt == X0NE_F32)
         add_rmsnorm_kernel<float><<<n_rows, block, 0, stream>>>(resid, (const float*)delta, w, (float*)out, rows, hidden, eps);

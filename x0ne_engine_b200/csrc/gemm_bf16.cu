@@ -1,0 +1,150 @@
+// y[M,N] = x[M,K] W[N,K]^T for bfloat16 with a small M (decode): a weight-streaming kernel.
+//
+// A decode step multiplies a handful of rows by every weight matrix of the model, so the product
+// is bound by reading W once from HBM (the library engine gives these shapes to cublasGemmEx,
+// x0ne-core/runtime/src/gpu.rs:1098-1149).  Here W is the A operand of mma.sync m16n8k16: a warp
+// takes 16 weight rows and streams them along K with 16-byte loads that bypass L1, the M <= 8*MT
+// activation rows are the B operand (read through L1, where they stay), and the accumulators are
+// float32.  Because a dot product does not care about the order of its terms, each thread feeds
+// the 8 consecutive k values of its 16-byte load to the MMA slots directly (the same permutation on
+// both operands), so no shuffle or shared-memory staging is needed.  The 8 warps of a block split K
+// in interleaved 32-value chunks and are summed in a fixed order at the end.
+//
+// Variants: bfloat16 or float32 output (logits), and SwiGLU fused into the epilogue for the packed
+// [gate; up] weight (out[m][i] = silu(gate_i . x_m) * (up_i . x_m), in float32, rounded once:
+// x0ne-core/kernels/cuda/swiglu.cu:5-11 without the intermediate bfloat16 rounding of gate and up).
+// Needs K % 8 == 0; other shapes go to the library product.
+#include "common.cuh"
+
+__device__ __forceinline__ uint4 ld_stream16(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ void mma16816(float* c, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+#define SM_WARPS 8
+#define SM_UNROLL 4
+
+template <int MT, typename OutT, bool SWIGLU>
+__global__ void __launch_bounds__(SM_WARPS * 32) gemm_smallm_kernel(const bf16* __restrict__ W, const bf16* __restrict__ X,
+                                                                    OutT* __restrict__ Y, int M, int N, int K, int ldy,
+                                                                    int n_tiles) {
+    constexpr int SETS = SWIGLU ? 2 : 1;
+    __shared__ float part[SM_WARPS][SETS][MT][128];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
+    const int chunks = (K + 31) / 32;
+    const uint4 zero = make_uint4(0, 0, 0, 0);
+
+    for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+        const int n0 = tile * 16;
+        const bf16* wrow[SETS][2];
+        bool wok[SETS][2];
+#pragma unroll
+        for (int s = 0; s < SETS; ++s)
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const int n = n0 + g + 8 * h;
+                wok[s][h] = n < N;
+                wrow[s][h] = W + (int64_t)(s * N + (wok[s][h] ? n : 0)) * K;
+            }
+        float acc[SETS][MT][4];
+#pragma unroll
+        for (int s = 0; s < SETS; ++s)
+#pragma unroll
+            for (int j = 0; j < MT; ++j)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) acc[s][j][i] = 0.f;
+
+        for (int c0 = warp; c0 < chunks; c0 += SM_WARPS * SM_UNROLL) {
+            uint4 a[SM_UNROLL][SETS][2], b[SM_UNROLL][MT];
+#pragma unroll
+            for (int u = 0; u < SM_UNROLL; ++u) {
+                const int k = (c0 + u * SM_WARPS) * 32 + 8 * t;
+                const bool kok = k < K;
+#pragma unroll
+                for (int s = 0; s < SETS; ++s)
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) a[u][s][h] = (kok && wok[s][h]) ? ld_stream16(wrow[s][h] + k) : zero;
+#pragma unroll
+                for (int j = 0; j < MT; ++j) {
+                    const int m = 8 * j + g;
+                    b[u][j] = (kok && m < M) ? __ldg(reinterpret_cast<const uint4*>(X + (int64_t)m * K + k)) : zero;
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < SM_UNROLL; ++u)
+#pragma unroll
+                for (int s = 0; s < SETS; ++s)
+#pragma unroll
+                    for (int j = 0; j < MT; ++j) {
+                        mma16816(acc[s][j], a[u][s][0].x, a[u][s][1].x, a[u][s][0].y, a[u][s][1].y, b[u][j].x, b[u][j].y);
+                        mma16816(acc[s][j], a[u][s][0].z, a[u][s][1].z, a[u][s][0].w, a[u][s][1].w, b[u][j].z, b[u][j].w);
+                    }
+        }
+        // partials: part[warp][set][j][row * 8 + col], row = weight row in the tile, col = m in the tile
+#pragma unroll
+        for (int s = 0; s < SETS; ++s)
+#pragma unroll
+            for (int j = 0; j < MT; ++j) {
+                part[warp][s][j][g * 8 + 2 * t] = acc[s][j][0];
+                part[warp][s][j][g * 8 + 2 * t + 1] = acc[s][j][1];
+                part[warp][s][j][(g + 8) * 8 + 2 * t] = acc[s][j][2];
+                part[warp][s][j][(g + 8) * 8 + 2 * t + 1] = acc[s][j][3];
+            }
+        __syncthreads();
+        for (int e = threadIdx.x; e < MT * 128; e += SM_WARPS * 32) {
+            const int j = e / 128, r = e % 128;
+            const int row = r % 16, col = r / 16;      // consecutive threads -> consecutive n
+            const int n = n0 + row, m = 8 * j + col;
+            float v[SETS];
+#pragma unroll
+            for (int s = 0; s < SETS; ++s) {
+                float sum = 0.f;
+#pragma unroll
+                for (int w = 0; w < SM_WARPS; ++w) sum += part[w][s][j][row * 8 + col];
+                v[s] = sum;
+            }
+            if (n < N && m < M) {
+                float out = v[0];
+                if (SWIGLU) out = v[0] / (1.0f + expf(-v[0])) * v[SETS - 1];
+                Y[(int64_t)m * ldy + n] = from_f32<OutT>(out);
+            }
+        }
+        __syncthreads();
+    }
+}
+
+template <int MT, typename OutT, bool SWIGLU>
+static int launch_smallm(const bf16* W, const bf16* X, OutT* Y, int M, int N, int K, int ldy, int sms, cudaStream_t stream) {
+    const int n_tiles = (N + 15) / 16;
+    int grid = n_tiles < sms * 4 ? n_tiles : sms * 4;
+    gemm_smallm_kernel<MT, OutT, SWIGLU><<<grid, SM_WARPS * 32, 0, stream>>>(W, X, Y, M, N, K, ldy, n_tiles);
+    X0NE_LAUNCH_CHECK();
+}
+
+// out_kind: 0 = bfloat16, 1 = float32, 2 = bfloat16 with SwiGLU over the packed [gate; up] weight
+// (W then has 2*N rows and y has N columns).
+X0NE_API int x0ne_gemm_bf16_smallm(const void* W, const void* X, void* Y, int M, int N, int K, int ldy, int out_kind,
+                                   int sms, cudaStream_t stream) {
+    X0NE_REQUIRE(M >= 0 && M <= 32 && N > 0 && K > 0, "gemm_smallm: M %d (at most 32) N %d K %d", M, N, K);
+    X0NE_REQUIRE(K % 8 == 0, "gemm_smallm: K %d is not a multiple of 8", K);
+    X0NE_REQUIRE(ldy >= N && sms > 0 && out_kind >= 0 && out_kind <= 2, "gemm_smallm: ldy %d N %d kind %d", ldy, N, out_kind);
+    X0NE_REQUIRE((((uintptr_t)W | (uintptr_t)X) & 15) == 0, "gemm_smallm: operands are not 16-byte aligned");
+    if (M == 0) return 0;
+    const bf16* w = (const bf16*)W;
+    const bf16* x = (const bf16*)X;
+    const int mt = (M + 7) / 8;
+#define X0NE_SMALLM(MT)                                                                                        \
+    if (out_kind == 0) return launch_smallm<MT, bf16, false>(w, x, (bf16*)Y, M, N, K, ldy, sms, stream);       \
+    if (out_kind == 1) return launch_smallm<MT, float, false>(w, x, (float*)Y, M, N, K, ldy, sms, stream);     \
+    return launch_smallm<MT, bf16, true>(w, x, (bf16*)Y, M, N, K, ldy, sms, stream);
+    if (mt == 1) { X0NE_SMALLM(1) }
+    if (mt == 2) { X0NE_SMALLM(2) }
+    { X0NE_SMALLM(4) }
+#undef X0NE_SMALLM
+}

@@ -284,3 +284,43 @@ def attention_decode_bf16(q: torch.Tensor, out: torch.Tensor, cache: PagedCacheA
     _check(lib, lib.x0ne_attention_decode_bf16(
         _ptr(q), _ptr(out), cache, _ptr(row_slot), _ptr(row_pos), c_int(n_rows), c_int(q_heads), c_float(scale),
         c_int(window), c_int(splits), _ptr(scratch), c_int64(nbytes), _stream()), "attention_decode_bf16")
+
+
+# ---------------------------------------------------------------------------------------------
+# bfloat16 small-M weight-streaming product (module `fast`)
+# ---------------------------------------------------------------------------------------------
+SMALL_M_LIMIT = 16
+_sm_count = {}
+
+
+def _sms(device) -> int:
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    n = _sm_count.get(idx)
+    if n is None:
+        n = _sm_count[idx] = torch.cuda.get_device_properties(idx).multi_processor_count
+    return n
+
+
+def gemm_smallm_takes(w: torch.Tensor, m: int) -> bool:
+    return w.dtype == torch.bfloat16 and 0 < m <= SMALL_M_LIMIT and w.shape[1] % 8 == 0
+
+
+def gemm_bf16_smallm(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, m: int, swiglu: bool = False) -> None:
+    """y[:m] = x[:m] @ w.T for m <= 32 by streaming w once; y is bfloat16 or float32.  With
+    `swiglu`, w is the packed [gate; up] weight and y[:m] = silu(x gate^T) * (x up^T)."""
+    lib = _lib("fast")
+    _need(x, torch.bfloat16, "gemm input")
+    _need(w, torch.bfloat16, "gemm weight")
+    _need(y, y.dtype, "gemm output")
+    rows, k = w.shape
+    n = rows // 2 if swiglu else rows
+    if x.shape[-1] != k or y.shape[-1] != n or x.numel() < m * k or y.numel() < m * n or (swiglu and rows % 2):
+        raise KernelError(f"gemm_smallm: shapes x {tuple(x.shape)} w {tuple(w.shape)} y {tuple(y.shape)} m {m}")
+    if y.dtype == torch.float32 and not swiglu:
+        kind = 1
+    elif y.dtype == torch.bfloat16:
+        kind = 2 if swiglu else 0
+    else:
+        raise KernelError(f"gemm_smallm: no output kind for {y.dtype} (swiglu={swiglu})")
+    _check(lib, lib.x0ne_gemm_bf16_smallm(_ptr(w), _ptr(x), _ptr(y), c_int(m), c_int(n), c_int(k), c_int(n),
+                                          c_int(kind), c_int(_sms(w.device)), _stream()), "gemm_bf16_smallm")

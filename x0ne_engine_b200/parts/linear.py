@@ -29,6 +29,8 @@ class Linear:
         w = self.weight
         if w.dtype == torch.float32:
             ops.gemm_f32_nt(x, w, out, m)
+        elif ops.gemm_smallm_takes(w, m):
+            ops.gemm_bf16_smallm(x, w, out, m)
         elif w.dtype == torch.bfloat16:
             if m > 0:
                 if out.dtype == torch.bfloat16:

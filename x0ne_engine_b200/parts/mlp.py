@@ -42,8 +42,11 @@ class SwiGLU(FeedForward):
         gu = ctx.ws.buffer("ffn.gate_up", (ctx.ws.max_rows, 2 * self.inter), self.env.dtype)
         act = ctx.ws.buffer("ffn.act", (ctx.ws.max_rows, self.inter), self.env.dtype)
         out = ctx.ws.buffer("delta", (ctx.ws.max_rows, self.hidden), self.env.dtype)
-        self.gate_up(x, gu, n_rows)
-        ops.swiglu(gu, act, n_rows)
+        if ops.gemm_smallm_takes(self.gate_up.weight, n_rows):
+            ops.gemm_bf16_smallm(x, self.gate_up.weight, act, n_rows, swiglu=True)     # activation in the epilogue
+        else:
+            self.gate_up(x, gu, n_rows)
+            ops.swiglu(gu, act, n_rows)
         self.down(act, out, n_rows)
         return out
 
