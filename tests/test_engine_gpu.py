@@ -1,0 +1,315 @@
+"""The engine against the plain implementation, in float32 and bfloat16, under every cut of the work:
+each request alone and whole; its last 32 tokens one by one; batches of unequal lengths whose
+shorter requests end earlier, one batch after another so that slots are used again; long decoding;
+the first tokens of a sequence; greedy and sampled generation through the entry point."""
+import numpy as np
+import pytest
+import torch
+
+import plain_impl as P
+from helpers import (BF16_SELF_TOL, assert_close_bf16, assert_close_f32, first_difference, golden_folder, model_folder,
+                     plain_logits, plain_model, prompts_for)
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = ["float32", "bfloat16"]
+_engines = {}
+
+
+def engine(name, dtype, max_tokens=4096, **kw):
+    from x0ne_engine_b200 import Engine
+    key = (name, dtype, max_tokens, tuple(sorted(kw.items())))
+    if key not in _engines:
+        folder = golden_folder() if name == "G" else model_folder(name, "float32" if dtype == "float32" else "bfloat16")
+        _engines[key] = (Engine.from_folder(folder, dtype=dtype, max_tokens=max_tokens, **kw), folder)
+    return _engines[key]
+
+
+def check(dtype, got, want, what):
+    (assert_close_f32 if dtype == "float32" else assert_close_bf16)(got, want, what)
+
+
+def same_cut(dtype, got, base, what):
+    """Two cuts of the same work by the engine itself."""
+    got, base = np.asarray(got), np.asarray(base)
+    if dtype == "float32":
+        assert np.array_equal(got, base), f"{what}: first difference at {first_difference(got, base)}"
+    else:
+        err = np.max(np.abs(got - base) / (np.max(np.abs(base), axis=-1, keepdims=True) + 1e-30))
+        assert err <= BF16_SELF_TOL, f"{what}: {err:.3e}"
+
+
+def whole(eng, ids):
+    s = eng.new_sequence()
+    try:
+        return eng.step([s], [ids], [list(range(len(ids)))]).cpu().numpy()
+    finally:
+        eng.free_sequence(s)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name,lengths", [("A", [5, 11, 17, 100]), ("B", [1, 7, 30, 64, 200]), ("C", [3, 65, 129]),
+                                          ("G", [12, 1, 40])])
+def test_each_request_alone_and_whole(name, lengths, dtype):
+    eng, folder = engine(name, dtype)
+    cfg, _ = plain_model(folder)
+    for ids in prompts_for(cfg["vocab"], lengths, seed=1):
+        check(dtype, whole(eng, ids), plain_logits(folder, ids), f"{name} len {len(ids)}")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_the_reference_projects_fixture(dtype):
+    import json
+    import os
+    eng, folder = engine("G", dtype)
+    with open(os.path.join(folder, "reference.json")) as f:
+        ref = json.load(f)
+    want = np.array(ref["logits"]).reshape(12, 40)
+    check(dtype, whole(eng, ref["ids"]), want, "fixture logits")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name,n", [("A", 100), ("B", 150), ("C", 40)])
+def test_last_32_tokens_one_by_one(name, n, dtype):
+    eng, folder = engine(name, dtype)
+    cfg, _ = plain_model(folder)
+    (ids,) = prompts_for(cfg["vocab"], [n], seed=2)
+    base = whole(eng, ids)
+    s = eng.new_sequence()
+    head = n - 32
+    rows = [eng.step([s], [ids[:head]], [[head - 1]]).cpu().numpy()[0]]
+    for t in ids[head:]:
+        rows.append(eng.step([s], [[t]]).cpu().numpy()[0])
+    eng.free_sequence(s)
+    got = np.stack(rows)
+    same_cut(dtype, got, base[head - 1:], f"{name}: decode vs whole")
+    check(dtype, got, plain_logits(folder, ids)[head - 1:], f"{name}: decode vs plain")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_prompt_cut_into_pieces(name, dtype):
+    """Chunks of 1, 2, 63, 64, 65... tokens: every piece attends the cache the earlier ones left."""
+    eng, folder = engine(name, dtype)
+    cfg, _ = plain_model(folder)
+    n = min(cfg["max_pos"], 230)
+    (ids,) = prompts_for(cfg["vocab"], [n], seed=3)
+    base = whole(eng, ids)
+    s = eng.new_sequence()
+    rows, at = [], 0
+    for size in [1, 2, 61, 64, 1, 65, 7, 1000]:
+        piece = ids[at:at + size]
+        if not piece:
+            break
+        rows.append(eng.step([s], [piece], [list(range(len(piece)))]).cpu().numpy())
+        at += len(piece)
+    eng.free_sequence(s)
+    same_cut(dtype, np.concatenate(rows), base, f"{name}: pieces vs whole")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name,lengths,steps", [("A", [5, 11, 17], 8), ("B", [1, 7, 30, 64], 12), ("C", [70, 3, 129, 64, 65], 40)])
+def test_unequal_batches_one_after_another_reuse_slots(name, lengths, steps, dtype):
+    """Three batches in a row on a cache that only holds one of them: prompts in one step, then one
+    token each; request i leaves the batch after i+2 decode steps.  Every logit row must equal the
+    request's own whole-sequence run, whatever slot and pages it got."""
+    need = sum((n + steps + 63) // 64 * 64 for n in lengths)
+    eng, folder = engine(name, dtype, max_tokens=need)
+    cfg, _ = plain_model(folder)
+    for batch in range(3):
+        prompts = prompts_for(cfg["vocab"], lengths, seed=10 + batch)
+        conts = prompts_for(cfg["vocab"], [steps] * len(lengths), seed=20 + batch)
+        leave = [min(steps, i + 2) for i in range(len(lengths))]
+        slots = [eng.new_sequence() for _ in prompts]
+        got = [[] for _ in prompts]
+        out = eng.step(slots, prompts).cpu().numpy()
+        for i in range(len(prompts)):
+            got[i].append(out[i])
+        live = list(range(len(prompts)))
+        for k in range(steps):
+            live = [i for i in live if k < leave[i]]
+            if not live:
+                break
+            out = eng.step([slots[i] for i in live], [[conts[i][k]] for i in live]).cpu().numpy()
+            for j, i in enumerate(live):
+                got[i].append(out[j])
+            for i in live:
+                if k + 1 == leave[i]:
+                    eng.free_sequence(slots[i])          # shorter requests end earlier
+        assert eng.cache.slots.held() == 0
+        for i, p in enumerate(prompts):
+            full = p + conts[i][:leave[i]]
+            base = whole(eng, full)[len(p) - 1:]
+            same_cut(dtype, np.stack(got[i]), base, f"{name} batch {batch} request {i}")
+            check(dtype, np.stack(got[i]), plain_logits(folder, full)[len(p) - 1:], f"{name} batch {batch} request {i}")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_long_decoding(dtype):
+    """Hundreds of single-token steps across many pages, two sequences of different age."""
+    eng, folder = engine("C", dtype)
+    cfg, _ = plain_model(folder)
+    a, b = prompts_for(cfg["vocab"], [600, 450], seed=4)
+    sa, sb = eng.new_sequence(), eng.new_sequence()
+    eng.step([sa], [a[:150]], [[]])
+    rows_a, rows_b = [], []
+    for k in range(450):
+        out = eng.step([sa, sb], [[a[150 + k]], [b[k]]]).cpu().numpy()
+        rows_a.append(out[0])
+        rows_b.append(out[1])
+    eng.free_sequence(sa)
+    eng.free_sequence(sb)
+    pa, pb = plain_logits(folder, a), plain_logits(folder, b)
+    check(dtype, np.stack(rows_a[-40:]), pa[-40:], "long decode a")
+    check(dtype, np.stack(rows_b[-40:]), pb[-40:], "long decode b")
+    check(dtype, np.stack(rows_b[:40]), pb[:40], "first tokens of a sequence")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_first_tokens_of_a_sequence(dtype):
+    eng, folder = engine("B", dtype)
+    cfg, _ = plain_model(folder)
+    (ids,) = prompts_for(cfg["vocab"], [6], seed=5)
+    s = eng.new_sequence()
+    rows = [eng.step([s], [[t]]).cpu().numpy()[0] for t in ids]
+    eng.free_sequence(s)
+    check(dtype, np.stack(rows), plain_logits(folder, ids), "token by token from the first")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_a_far_key_among_hundreds_decides_the_logits(dtype):
+    """Random weights average far keys away, so a wrong page or a dropped tile could hide.  Here one
+    early token's key is made to dominate a late query (its embedding row is scaled up, and the late
+    token shares it), so the late logits depend on that one far key; they must match the plain run."""
+    import os
+    import tempfile
+    from x0ne_engine_b200 import Engine
+    from x0ne_engine_b200.weights import open_folder, write_file
+    src_folder = model_folder("C", "float32" if dtype == "float32" else "bfloat16", linear_std=0.05)
+    d = tempfile.mkdtemp(prefix="x0ne_far_")
+    src = open_folder(src_folder)
+    tensors = {n: src.tensor(n).clone() for n in src.names()}
+    src.close()
+    special = 7
+    tensors["model.embed_tokens.weight"][special] *= 6.0
+    write_file(os.path.join(d, "model.safetensors"), tensors)
+    with open(os.path.join(src_folder, "config.json")) as f, open(os.path.join(d, "config.json"), "w") as g:
+        g.write(f.read())
+    eng = Engine.from_folder(d, dtype=dtype, max_tokens=2048)
+    cfg, w = P.read_model(d)
+    rng = np.random.default_rng(6)
+    ids = [int(t) for t in rng.integers(8, cfg["vocab"], 700)]
+    ids[130] = special                    # in page 2
+    ids[-1] = special
+    want = P.forward(cfg, w, ids)[-3:]
+    other = list(ids)
+    other[130] = 9
+    assert np.abs(P.forward(cfg, w, other)[-1] - want[-1]).max() > 1e-3 * np.abs(want[-1]).max(), \
+        "the far key does not matter enough for this test to see it"
+    s = eng.new_sequence()
+    eng.step([s], [ids[:-3]], [[]])
+    got = np.stack([eng.step([s], [[t]]).cpu().numpy()[0] for t in ids[-3:]])
+    eng.free_sequence(s)
+    check(dtype, got, want, "far key")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name,lengths,n_new", [("A", [5, 11, 17], 8), ("B", [1, 7, 30, 64], 12)])
+@pytest.mark.parametrize("decode", ["graph", "eager"])
+def test_greedy_generation_through_the_entry_point(name, lengths, n_new, decode, dtype):
+    from x0ne_engine_b200 import Model
+    folder = model_folder(name, "float32" if dtype == "float32" else "bfloat16")
+    cfg, w = plain_model(folder)
+    prompts = prompts_for(cfg["vocab"], lengths, seed=7)
+    m = Model.from_folder(folder, dtype=dtype, max_batch=3, max_ctx=cfg["max_pos"], decode=decode)
+    out = m.generate(prompts, max_tokens=n_new, stop_token_ids=())
+    assert out.finish_reasons == ["length"] * len(prompts)
+    for p, got in zip(prompts, out.tokens):
+        if dtype == "float32":
+            assert got == P.greedy(cfg, w, p, n_new)
+        else:
+            # bfloat16: equal until the plain top-2 margin is within the logit tolerance
+            ids = list(p)
+            for t in got:
+                row = P.forward(cfg, w, ids)[-1]
+                top = np.sort(row)[-2:]
+                if t != int(np.argmax(row)):
+                    assert top[1] - top[0] <= 2 * 0.05 * np.abs(row).max(), "a bfloat16 token left a clear argmax"
+                    break
+                ids.append(t)
+    # a second call gives the same tokens (slots and graphs reused)
+    assert m.generate(prompts, max_tokens=n_new, stop_token_ids=()).tokens == out.tokens
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_stop_tokens_and_early_endings_in_generation(dtype):
+    from x0ne_engine_b200 import Model
+    folder = model_folder("A", "float32" if dtype == "float32" else "bfloat16")
+    cfg, w = plain_model(folder)
+    prompts = prompts_for(cfg["vocab"], [9, 4, 21, 6, 13], seed=8)
+    m = Model.from_folder(folder, dtype=dtype, max_batch=4, max_ctx=128)
+    free = m.generate(prompts, max_tokens=20, stop_token_ids=()).tokens
+    stop = free[0][3]                                         # a token the first request emits
+    out = m.generate(prompts, max_tokens=20, stop_token_ids=(stop,))
+    for f, got, why in zip(free, out.tokens, out.finish_reasons):
+        if stop in f:
+            assert got == f[:f.index(stop)] and why == "stop"
+        else:
+            assert got == f and why == "length"
+    assert m.engine.cache.slots.held() == 0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_sampled_generation_follows_seed_and_ignores_batch_mates(dtype):
+    from x0ne_engine_b200 import Model, SamplingParams
+    folder = model_folder("B", "float32" if dtype == "float32" else "bfloat16")
+    cfg, w = plain_model(folder)
+    prompts = prompts_for(cfg["vocab"], [1, 7, 30, 64], seed=9)
+    m = Model.from_folder(folder, dtype=dtype, max_batch=4, max_ctx=256)
+    params = [SamplingParams(max_tokens=12, temperature=0.7, seed=100 + i) for i in range(4)]
+    a = m.generate(prompts, params=params).tokens
+    assert m.generate(prompts, params=params).tokens == a
+    alone = [m.generate([p], params=[q]).tokens[0] for p, q in zip(prompts, params)]
+    if dtype == "float32":
+        assert alone == a                                     # bit-identical logits, same draws
+    b = m.generate(prompts, params=[SamplingParams(max_tokens=12, temperature=0.7, seed=200 + i) for i in range(4)]).tokens
+    assert a != b
+    # every drawn token lies inside the interval the plain CDF gives for the request's uniform
+    for p, toks, q in zip(prompts, a, params):
+        ids = list(p)
+        for k, t in enumerate(toks[:4]):
+            row = P.forward(cfg, w, ids)[-1]
+            lo, hi = P.draw_interval(row, 0.7, 1.0, t)
+            u = P.uniform_of(q.seed, k)
+            slack = 1e-4 if dtype == "float32" else 0.05
+            assert lo - slack <= u <= hi + slack
+            ids.append(t)
+
+
+def test_refused_steps_change_nothing():
+    from x0ne_engine_b200 import StepError
+    eng, folder = engine("A", "float32", max_tokens=128)
+    s = eng.new_sequence()
+    eng.step([s], [[1, 2, 3]])
+    for bad in (dict(slots=[s], tokens=[[256]]), dict(slots=[s], tokens=[[]]), dict(slots=[s, s], tokens=[[1], [2]]),
+                dict(slots=[s], tokens=[[1]], want=[[1]]), dict(slots=[99], tokens=[[1]]),
+                dict(slots=[s], tokens=[[1] * 126])):
+        with pytest.raises(StepError):
+            eng.step(**bad)
+    assert eng.length(s) == 3
+    t = eng.new_sequence()
+    with pytest.raises(StepError, match="no room"):
+        eng.step([t], [[1] * 100])                            # 2 pages, 1 free
+    assert eng.length(t) == 0
+    eng.free_sequence(s)
+    eng.free_sequence(t)
+
+
+def test_library_is_loaded_and_there_is_no_cpu_path():
+    from x0ne_engine_b200 import Engine
+    from x0ne_engine_b200.csrc import ops
+    engine("A", "bfloat16")
+    libs = ops.loaded_libraries()
+    assert any("libx0ne_core" in p for p in libs) and any("libx0ne_fast" in p for p in libs)
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        Engine.from_folder(model_folder("A"), dtype="float32", device="cpu")

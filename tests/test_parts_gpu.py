@@ -1,0 +1,246 @@
+"""Each part of a layer alone against its plain function, and a toy mixer with state of its own that is
+registered, built and stepped without a change to the library's files."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_impl as P
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def make_ctx(engine_dtype, n_rows, slots, positions, cache, decode=False):
+    from x0ne_engine_b200.engine import StepContext, Workspace
+    ws = Workspace(max(64, n_rows), DEV)
+    ws.max_want = ws.max_rows
+    mk = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)   # noqa: E731
+    return StepContext(n_rows=n_rows, tokens=mk([0] * n_rows), row_slot=mk(slots), row_pos=mk(positions),
+                       dtype=engine_dtype, ws=ws, cache=cache, decode=decode, n_seqs=1, max_seq_rows=n_rows,
+                       max_context=max(positions) + 1, seq_first_row=mk([0, n_rows]), seq_slot=mk(slots[:1]),
+                       seq_pos0=mk(positions[:1]), n_tiles=(n_rows + 63) // 64,
+                       tile_seq=mk([0] * ((n_rows + 63) // 64)), tile_row0=mk(list(range(0, n_rows, 64))))
+
+
+def rnd(shape, seed, scale=1.0):
+    return torch.randn(shape, generator=torch.Generator().manual_seed(seed)) * scale
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_rmsnorm_part(dtype):
+    from x0ne_engine_b200.config import PartSpec
+    from x0ne_engine_b200.parts import NORMS, BuildEnv
+    spec = PartSpec("rmsnorm", dict(size=120, eps=3e-6, names=dict(weight="w")))
+    part = NORMS.get("rmsnorm")(spec, BuildEnv(dtype, torch.device(DEV)))
+    assert [(n.name, n.shape, n.role) for n in part.tensor_needs(spec)] == [("w", (120,), "vector")]
+    w = 1 + 0.1 * rnd((120,), 1)
+    part.bind({"w": w.to(DEV)})
+    resid, delta = rnd((4, 120), 2).to(DEV), rnd((4, 120), 3).to(dtype).to(DEV)
+    out = torch.empty((4, 120), dtype=dtype, device=DEV)
+    want = P.rmsnorm((resid.double() + delta.double()).cpu().numpy(), w.double().numpy(), 3e-6)
+    part.add_norm(None, resid, delta, out, 4)
+    tol = 2e-5 if dtype == torch.float32 else 2 ** -7
+    assert np.abs(out.double().cpu().numpy() - want).max() / np.abs(want).max() < tol
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_swiglu_part(dtype):
+    from x0ne_engine_b200.config import PartSpec
+    from x0ne_engine_b200.parts import FEED_FORWARDS, BuildEnv
+    h, inter, n = 96, 200, 5
+    spec = PartSpec("swiglu", dict(hidden_size=h, intermediate_size=inter, names=dict(gate="g", up="u", down="d")))
+    part = FEED_FORWARDS.get("swiglu")(spec, BuildEnv(dtype, torch.device(DEV)))
+    w = {"g": rnd((inter, h), 1, 0.1).to(dtype), "u": rnd((inter, h), 2, 0.1).to(dtype), "d": rnd((h, inter), 3, 0.1).to(dtype)}
+    part.bind({k: v.to(DEV) for k, v in w.items()})
+    x = rnd((n, h), 4).to(dtype)
+    ctx = make_ctx(dtype, n, [0] * n, list(range(n)), None)
+    xb = ctx.ws.buffer("x", (ctx.ws.max_rows, h), dtype)
+    xb[:n] = x.to(DEV)
+    out = part.forward(ctx, xb, n)[:n]
+    want = P.swiglu_mlp(x.double().numpy(), {"p.gate_proj.weight": w["g"].double().numpy(),
+                                             "p.up_proj.weight": w["u"].double().numpy(),
+                                             "p.down_proj.weight": w["d"].double().numpy()}, "p.")
+    tol = 2e-5 if dtype == torch.float32 else 3 * 2 ** -7
+    assert np.abs(out.double().cpu().numpy() - want).max() / np.abs(want).max() < tol
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("window", [None, 5])
+def test_attention_part_whole_then_token_by_token(dtype, window):
+    """The mixer alone over its own cache group: a 70-token sequence whole, then continued one
+    token at a time, against the plain attention block; with and without a window."""
+    from x0ne_engine_b200.cache import SequenceCache
+    from x0ne_engine_b200.config import PartSpec
+    from x0ne_engine_b200.parts import MIXERS, POSITIONS, BuildEnv
+    h, qh, kvh, hd, n = 72, 6, 2, 16, 75
+    env = BuildEnv(dtype, torch.device(DEV))
+    env.positions["p"] = POSITIONS.get("rope")(PartSpec("rope", dict(head_dim=hd, rotary_dim=hd, theta=1e4)), env)
+    names = dict(q="a.q_proj.weight", k="a.k_proj.weight", v="a.v_proj.weight", o="a.o_proj.weight",
+                 q_norm="a.q_norm.weight", k_norm="a.k_norm.weight")
+    spec = PartSpec("gqa_attention", dict(hidden_size=h, q_heads=qh, kv_heads=kvh, head_dim=hd, qk_norm_eps=1e-5,
+                                          window=window, position="p", scale=None, names=names))
+    cls = MIXERS.get("gqa_attention")
+    part = cls(spec, env)
+    w = {"a.q_proj.weight": rnd((qh * hd, h), 1, 0.2), "a.k_proj.weight": rnd((kvh * hd, h), 2, 0.2),
+         "a.v_proj.weight": rnd((kvh * hd, h), 3, 0.2), "a.o_proj.weight": rnd((h, qh * hd), 4, 0.2),
+         "a.q_norm.weight": 1 + 0.1 * rnd((hd,), 5), "a.k_norm.weight": 1 + 0.1 * rnd((hd,), 6)}
+    w = {k: (v.to(dtype).float() if v.dim() == 2 else v) for k, v in w.items()}
+    part.bind({k: (v.to(dtype) if v.dim() == 2 else v).to(DEV) for k, v in w.items()})
+    need = cls.cache_need(spec)
+    assert (need.kind, need.kv_heads, need.head_dim, need.window) == ("kv", kvh, hd, window)
+    cache = SequenceCache([need], [None], 256, 256, dtype, DEV)
+    slot = cache.acquire(n)
+    x = rnd((n, h), 7).to(dtype)
+    cfg = dict(q_heads=qh, kv_heads=kvh, head_dim=hd, eps=1e-5, theta=1e4)
+    want = P.attention_block(x.double().numpy(), {k: v.double().numpy() for k, v in w.items()}, "a.", cfg,
+                             np.arange(n), window=window)
+    head = 70
+    ctx = make_ctx(dtype, head, [slot] * head, list(range(head)), cache)
+    xb = ctx.ws.buffer("x", (ctx.ws.max_rows, h), dtype)
+    xb[:head] = x[:head].to(DEV)
+    got = [part.forward(ctx, 0, xb, head)[:head].double().cpu().numpy()]
+    for p in range(head, n):
+        ctx = make_ctx(dtype, 1, [slot], [p], cache, decode=True)
+        xb = ctx.ws.buffer("x", (ctx.ws.max_rows, h), dtype)
+        xb[:1] = x[p:p + 1].to(DEV)
+        got.append(part.forward(ctx, 0, xb, 1)[:1].double().cpu().numpy())
+    got = np.concatenate(got)
+    tol = 2e-5 if dtype == torch.float32 else 4 * 2 ** -7
+    assert np.abs(got - want).max() / np.abs(want).max() < tol
+
+
+def test_a_toy_mixer_with_state_of_its_own_is_registered_built_and_stepped():
+    """A mixer defined here keeps a running, decayed sum of its inputs per sequence (a fixed-size
+    state, no keys or values).  With a toy architecture around it the engine must build it, give it a
+    zeroed state per slot, and produce the same logits whole, token by token, and after slot reuse."""
+    from x0ne_engine_b200 import Engine
+    from x0ne_engine_b200.config import LayerSpec, ModelSpec, PartSpec, RunEntry
+    from x0ne_engine_b200.engine import tensor_needs_of_spec
+    from x0ne_engine_b200.parts import MIXERS, CacheNeed, Mixer
+    from x0ne_engine_b200.weights import RandomInit, TensorNeed, make_tensor
+
+    class DecayMixer(Mixer):
+        """state_t = decay * state_{t-1} + x_t ;  out_t = state_t @ W^T"""
+
+        def __init__(self, spec, env):
+            super().__init__(spec, env)
+            self.h, self.decay = int(spec["hidden_size"]), float(spec["decay"])
+
+        @staticmethod
+        def cache_need(spec):
+            return CacheNeed("state", state_shape=(int(spec["hidden_size"]),))
+
+        @staticmethod
+        def tensor_needs(spec):
+            return [TensorNeed(spec["names"]["w"], (int(spec["hidden_size"]),) * 2)]
+
+        def bind(self, tensors):
+            self.w = tensors[self.spec["names"]["w"]]
+
+        def forward(self, ctx, entry, x, n_rows, cache_entry=None, write_cache=True):
+            state = ctx.cache.state(entry)
+            out = ctx.ws.buffer("delta", (ctx.ws.max_rows, self.h), self.env.dtype)
+            slots = ctx.row_slot[:n_rows].tolist()
+            for r in range(n_rows):                      # a toy: rows in order, one at a time
+                s = slots[r]
+                state[s] = self.decay * state[s] + x[r].float()
+                out[r] = (state[s] @ self.w.float().T).to(self.env.dtype)
+            return out
+
+    MIXERS.register("toy_decay", DecayMixer)
+    try:
+        h, vocab = 32, 50
+        norm = lambda name: PartSpec("rmsnorm", dict(size=h, eps=1e-6, names=dict(weight=name)))   # noqa: E731
+        layers = []
+        for l in range(2):
+            layers.append(LayerSpec(
+                block="prenorm", mixer_norm=norm(f"l{l}.n1"),
+                mixer=PartSpec("toy_decay", dict(hidden_size=h, decay=0.5 + 0.2 * l, names=dict(w=f"l{l}.mix"))),
+                ffn_norm=norm(f"l{l}.n2"),
+                ffn=PartSpec("swiglu", dict(hidden_size=h, intermediate_size=48,
+                                            names=dict(gate=f"l{l}.g", up=f"l{l}.u", down=f"l{l}.d")))))
+        spec = ModelSpec(architecture="ToyForCausalLM", vocab_size=vocab, hidden_size=h, max_position_embeddings=64,
+                         embedding=PartSpec("token_embedding", dict(vocab_size=vocab, hidden_size=h, names=dict(weight="emb"))),
+                         positions={}, layers=tuple(layers), run_order=(RunEntry(0), RunEntry(1), RunEntry(0)),
+                         final_norm=norm("fn"),
+                         head=PartSpec("lm_head", dict(vocab_size=vocab, hidden_size=h, tied=True, names=dict(weight="emb"))))
+        needs = tensor_needs_of_spec(spec)
+        assert "l1.mix" in [n.name for n in needs]
+        init = RandomInit(seed=3, linear_std=0.3, norm_jitter=0.1)
+        cpu = {n.name: make_tensor(n, init, torch.float32, "cpu") for n in needs}
+        eng = Engine(spec, {k: v.to(DEV) for k, v in cpu.items()}, "float32", DEV, max_tokens=256)
+        # layer 0 runs twice (entries 0 and 2), each entry with a state of its own
+        assert sorted(eng.cache.states) == [0, 1, 2] and eng.cache.state(0).data_ptr() != eng.cache.state(2).data_ptr()
+
+        def plain(ids):
+            w = {k: v.double().numpy() for k, v in cpu.items()}
+            x = w["emb"][ids]
+            for (l, decay) in ((0, 0.5), (1, 0.7), (0, 0.5)):
+                nx = P.rmsnorm(x, w[f"l{l}.n1"], 1e-6)
+                st, outs = np.zeros(h), []
+                for t in range(len(ids)):
+                    st = decay * st + nx[t]
+                    outs.append(st @ w[f"l{l}.mix"].T)
+                x = x + np.stack(outs)
+                nx = P.rmsnorm(x, w[f"l{l}.n2"], 1e-6)
+                x = x + P.swiglu_mlp(nx, {"p.gate_proj.weight": w[f"l{l}.g"], "p.up_proj.weight": w[f"l{l}.u"],
+                                          "p.down_proj.weight": w[f"l{l}.d"]}, "p.")
+            return P.rmsnorm(x, w["fn"], 1e-6) @ w["emb"].T
+
+        ids = [3, 14, 15, 9, 2, 6, 5, 35, 8, 9]
+        want = plain(ids)
+        for round_ in range(2):                           # the second round reuses the slot: state must start at zero
+            s = eng.new_sequence()
+            got = eng.step([s], [ids], [list(range(len(ids)))]).cpu().numpy()
+            eng.free_sequence(s)
+            assert np.abs(got - want).max() / np.abs(want).max() < 1e-4
+        s = eng.new_sequence()
+        rows = [eng.step([s], [ids[:4]], [[3]]).cpu().numpy()[0]]
+        rows += [eng.step([s], [[t]]).cpu().numpy()[0] for t in ids[4:]]
+        eng.free_sequence(s)
+        assert np.abs(np.stack(rows) - want[3:]).max() / np.abs(want).max() < 1e-4
+    finally:
+        MIXERS.unregister("toy_decay")
+
+
+def test_a_layer_can_read_another_layers_cache():
+    """Run order entry 1 runs layer 1 on the keys and values entry 0 wrote (it writes none)."""
+    from x0ne_engine_b200 import Engine, Qwen3Config
+    from x0ne_engine_b200.config import ModelSpec, RunEntry
+    from x0ne_engine_b200.engine import tensor_needs_of_spec
+    from x0ne_engine_b200.weights import RandomInit, make_tensor
+    import dataclasses
+    cfg = Qwen3Config(hidden_size=64, intermediate_size=96, num_hidden_layers=2, num_attention_heads=4,
+                      num_key_value_heads=2, head_dim=16, vocab_size=80, max_position_embeddings=128,
+                      rms_norm_eps=1e-6, rope_theta=1e4, tie_word_embeddings=True, dtype="float32")
+    spec = dataclasses.replace(cfg.to_spec(), run_order=(RunEntry(0), RunEntry(1, reads_cache_of=0)))
+    init = RandomInit(seed=9, linear_std=0.1, norm_jitter=0.1)
+    cpu = {n.name: make_tensor(n, init, torch.float32, "cpu") for n in tensor_needs_of_spec(spec)}
+    eng = Engine(spec, {k: v.to(DEV) for k, v in cpu.items()}, "float32", DEV, max_tokens=256)
+    assert len(eng.cache.groups) == 1 and eng.cache.groups[0].entries == [0]
+    w = {k: v.double().numpy() for k, v in cpu.items()}
+    pc = dict(q_heads=4, kv_heads=2, head_dim=16, eps=1e-6, theta=1e4)
+    ids = [5, 9, 33, 2, 71, 8, 8, 40]
+    n = len(ids)
+    pos = np.arange(n)
+    x = w["model.embed_tokens.weight"][ids]
+    # layer 0 as usual
+    nx = P.rmsnorm(x, w["model.layers.0.input_layernorm.weight"], 1e-6)
+    x = x + P.attention_block(nx, w, "model.layers.0.self_attn.", pc, pos)
+    k0 = P.rope(P.rmsnorm((nx @ w["model.layers.0.self_attn.k_proj.weight"].T).reshape(n, 2, 16),
+                          w["model.layers.0.self_attn.k_norm.weight"], 1e-6), pos, P.inv_freq(16, 1e4))
+    v0 = (nx @ w["model.layers.0.self_attn.v_proj.weight"].T).reshape(n, 2, 16)
+    x = x + P.swiglu_mlp(P.rmsnorm(x, w["model.layers.0.post_attention_layernorm.weight"], 1e-6), w, "model.layers.0.mlp.")
+    # layer 1: its own q, layer 0's keys and values
+    nx = P.rmsnorm(x, w["model.layers.1.input_layernorm.weight"], 1e-6)
+    q1 = P.rope(P.rmsnorm((nx @ w["model.layers.1.self_attn.q_proj.weight"].T).reshape(n, 4, 16),
+                          w["model.layers.1.self_attn.q_norm.weight"], 1e-6), pos, P.inv_freq(16, 1e4))
+    x = x + P.attention(q1, k0, v0).reshape(n, 64) @ w["model.layers.1.self_attn.o_proj.weight"].T
+    x = x + P.swiglu_mlp(P.rmsnorm(x, w["model.layers.1.post_attention_layernorm.weight"], 1e-6), w, "model.layers.1.mlp.")
+    want = P.rmsnorm(x, w["model.norm.weight"], 1e-6) @ w["model.embed_tokens.weight"].T
+    s = eng.new_sequence()
+    got = eng.step([s], [ids[:5]], [list(range(5))]).cpu().numpy()
+    got = np.concatenate([got] + [eng.step([s], [[t]]).cpu().numpy() for t in ids[5:]])
+    assert np.abs(got - want).max() / np.abs(want).max() < 1e-4

@@ -1,0 +1,335 @@
+"""Command line of the library: `python -m x0ne_engine_b200 <command> ...`.
+
+Commands and their options follow the reference's own programs where it has them:
+
+  core-bench <model dir> [--lengths short,1k,4k] [--decode N] [--reps N] [--batch B] [--dtype D]
+      time to first token, prefill and decode rates per prompt length, one line
+      `x0ne-bench-result: <JSON>` (x0ne-core/oracle/examples/core-bench.rs:6-16,420-436).
+  roofline --config config.json --gpu <GB/s> --prompt P --generated N [--tok-s X] [--batch B]
+      places a decode rate against the bandwidth ceiling
+      (x0ne-core/runtime/src/bin/x0ne-core-roofline.rs:4-5, x0ne-core/runtime/src/roofline.rs:55-102).
+  generate <model dir> --prompt-ids 1,2,3 [--prompt-ids ...] [--max-tokens N] [--temperature T]
+      [--top-p P] [--seed S] [--stop-token-ids a,b] [--dtype D] [--decode graph|eager]
+  replay ...            the trace replay program (same as bin/trace_run)
+  init <config.json> <out dir> [--seed S] [--linear-std X] [--norm-jitter X]
+      writes a model folder with random weights
+  kernel-bench --kernel NAME [sizes]   times one kernel alone with CUDA events
+      (the reference's per-kernel timing entry: x0ne-core/runtime/src/ops.rs:579-681)
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import statistics
+import sys
+import time
+
+
+def _ids(text: str):
+    return [int(t) for t in text.split(",") if t.strip() != ""]
+
+
+def synthetic_ids(n: int, vocab: int, seed: int = 0x0C0E5EED):
+    """splitmix64 ids (x0ne-core/oracle/examples/core-bench.rs:26-43)."""
+    m = (1 << 64) - 1
+    s, out = seed, []
+    for _ in range(n):
+        s = (s + 0x9E3779B97F4A7C15) & m
+        z = s
+        z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & m
+        z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & m
+        out.append(int((z ^ (z >> 31)) % vocab))
+    return out
+
+
+def _stats(v):
+    if not v:
+        return None
+    s = sorted(v)
+    return {"median": statistics.median(s), "min": s[0], "max": s[-1], "mean": statistics.fmean(s),
+            "stddev": statistics.stdev(s) if len(s) > 1 else 0.0, "n": len(s)}
+
+
+def _length_tokens(name: str, limit: int) -> int:
+    if name == "short":
+        return 20
+    if name == "max":
+        return limit - 1
+    if name.endswith("k"):
+        return int(name[:-1]) * 1024
+    return int(name)
+
+
+def cmd_generate(a) -> int:
+    from . import Model
+    m = Model.from_folder(a.model, dtype=a.dtype, max_batch=max(1, len(a.prompt_ids)), max_ctx=a.max_ctx,
+                          decode=a.decode)
+    stop = None if a.stop_token_ids is None else tuple(_ids(a.stop_token_ids))
+    out = m.generate([_ids(p) for p in a.prompt_ids], max_tokens=a.max_tokens, temperature=a.temperature,
+                     top_p=a.top_p, seed=a.seed, stop_token_ids=stop)
+    for toks, why in zip(out.tokens, out.finish_reasons):
+        print(json.dumps({"tokens": toks, "finish_reason": why}))
+    return 0
+
+
+def cmd_core_bench(a) -> int:
+    import torch
+    from . import Model
+    from .config import config_from_folder
+    from .engine.generate import GenerationStats
+    cfg = config_from_folder(a.model)
+    names = [n.strip() for n in a.lengths.split(",")]
+    if any(not n for n in names) or a.decode < 2 or a.reps < 1:
+        print("usage: core-bench <model directory> [--lengths a,b,...] [--decode N>=2] [--reps N>=1]", file=sys.stderr)
+        return 2
+    lens = [_length_tokens(n, cfg.max_position_embeddings - a.decode) for n in names]
+    max_ctx = min(cfg.max_position_embeddings, max(lens) + a.decode)
+    t0 = time.time()
+    m = Model.from_folder(a.model, dtype=a.dtype, max_batch=a.batch, max_ctx=max_ctx)
+    torch.cuda.synchronize()
+    load_s = time.time() - t0
+    results = []
+    for name, n in zip(names, lens):
+        prompts = [synthetic_ids(n, cfg.vocab_size, 0x0C0E5EED + i) for i in range(a.batch)]
+        ttft, prefill, decode, tokens = [], [], [], []
+        first = None
+        for rep in range(a.reps + 1):
+            m._generator.stats = st = GenerationStats()
+            out = m.generate(prompts, max_tokens=a.decode, stop_token_ids=())
+            rates = (st.prefill_seconds, st.prefill_tokens / st.prefill_seconds,
+                     st.decode_tokens / st.decode_seconds if st.decode_seconds else 0.0)
+            if rep == 0:
+                first = rates
+            else:
+                ttft.append(rates[0]); prefill.append(rates[1]); decode.append(rates[2]); tokens.append(out.tokens)
+        same = all(t == tokens[0] for t in tokens)
+        results.append({"name": name, "tokens": n, "source": "synthetic", "status": "ok", "same_tokens": same,
+                        "first": {"ttft_s": first[0], "prefill_tok_s": first[1], "decode_tok_s": first[2]},
+                        "ttft_s": _stats(ttft), "prefill_tok_s": _stats(prefill), "decode_tok_s": _stats(decode)})
+    free, total = torch.cuda.mem_get_info()
+    print("x0ne-bench-result: " + json.dumps({
+        "schema": 1, "kind": "core", "model": a.model, "max_ctx": max_ctx, "decode_tokens": a.decode, "reps": a.reps,
+        "batch": a.batch, "engine": m.engine.describe(),
+        "config": {"model_type": "qwen3", "layers": cfg.num_hidden_layers, "hidden_size": cfg.hidden_size,
+                   "vocab_size": cfg.vocab_size, "max_position_embeddings": cfg.max_position_embeddings},
+        "load": {"cold_s": load_s}, "memory": {"device_total_bytes": total, "free_after_bytes": free},
+        "lengths": results}))
+    return 0
+
+
+def cmd_roofline(a) -> int:
+    from .config import config_from_folder
+    import os
+    cfg = config_from_folder(os.path.dirname(os.path.abspath(a.config)))
+    h = cfg.hidden_size
+    per_layer = cfg.linear_params_per_layer + 2 * h + 2 * cfg.head_dim
+    weights = (cfg.num_hidden_layers * per_layer + h + cfg.vocab_size * h + h) * 2
+    ctx = a.prompt + a.generated / 2.0
+    kv = cfg.kv_bytes_per_position * ctx * a.batch
+    ceiling = a.gpu * 1e9 / (weights + kv) * a.batch
+    row = {"prompt_tokens": a.prompt, "generated": a.generated, "batch": a.batch, "mean_ctx": ctx,
+           "weight_bytes": weights, "kv_bytes": kv, "bandwidth_gb_s": a.gpu, "ceiling_tok_s": ceiling}
+    if a.tok_s is not None:
+        row.update(tok_s=a.tok_s, share=a.tok_s / ceiling)
+    print(json.dumps(row))
+    return 0
+
+
+def cmd_init(a) -> int:
+    from .config import config_from_dict
+    from .weights import RandomInit, write_model_folder
+    with open(a.config) as f:
+        cfg = config_from_dict(json.load(f))
+    write_model_folder(a.out, cfg, RandomInit(a.seed, a.linear_std, a.norm_jitter))
+    print(f"wrote {a.out}")
+    return 0
+
+
+def cmd_replay(a, rest) -> int:
+    from .engine.replay import main
+    return main(rest)
+
+
+def cmd_kernel_bench(a) -> int:
+    """Times one kernel alone: inputs larger than L2 are cycled so every launch reads cold data."""
+    import math
+    import torch
+    from .csrc import ops
+    dev = "cuda:0"
+    torch.manual_seed(0)
+
+    def timed(fn, bytes_per_launch, flops_per_launch=0.0):
+        """The launches are captured into one CUDA graph, so the time is the device's, not the host's."""
+        for _ in range(a.warmup):
+            fn()
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for _ in range(a.iters):
+                fn()
+        g.replay()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        s.record()
+        g.replay()
+        e.record()
+        torch.cuda.synchronize()
+        us = s.elapsed_time(e) * 1e3 / a.iters
+        print(json.dumps({"kernel": a.kernel, "m": a.m, "n": a.n, "k": a.k, "batch": a.batch, "context": a.context,
+                          "us": us, "gb_s": bytes_per_launch / us / 1e3, "tflops": flops_per_launch / us / 1e6,
+                          "copies": copies}))
+
+    if a.kernel in ("gemm_smallm", "gemm_smallm_swiglu", "gemm_library"):
+        swiglu = a.kernel == "gemm_smallm_swiglu"
+        rows = 2 * a.n if swiglu else a.n
+        wbytes = rows * a.k * 2
+        copies = max(2, int(math.ceil(256e6 / wbytes)) + 1)          # cycle through > 2 x L2 of weights
+        ws = [torch.randn(rows, a.k, device=dev).mul_(0.02).bfloat16() for _ in range(copies)]
+        x = torch.randn(max(a.m, 1), a.k, device=dev).bfloat16()
+        y = torch.empty(max(a.m, 1), a.n, device=dev, dtype=torch.bfloat16)
+        i = [0]
+
+        def fn():
+            w = ws[i[0] % copies]
+            i[0] += 1
+            if a.kernel == "gemm_library":
+                torch.mm(x[:a.m], w.t(), out=y[:a.m])
+            else:
+                ops.gemm_bf16_smallm(x, w, y, a.m, swiglu=swiglu)
+        timed(fn, wbytes, 2.0 * a.m * rows * a.k)
+        return 0
+
+    if a.kernel == "attention_decode":
+        from .parts.attention import decode_splits
+        hd, kvh, qh, B, ctx = a.head_dim, a.kv_heads, a.q_heads, a.batch, a.context
+        pages_per = (ctx + 63) // 64
+        kv_bytes = B * pages_per * 2 * kvh * 64 * hd * 2
+        copies = max(2, int(math.ceil(256e6 / kv_bytes)) + 1)
+        n_pages = B * pages_per
+        stores = [torch.randn(n_pages, 2, kvh, 64, hd, device=dev).bfloat16() for _ in range(copies)]
+        table = torch.arange(n_pages, dtype=torch.int32, device=dev).reshape(B, pages_per).contiguous()
+        views = [ops.PagedCacheArg(s.data_ptr(), table.data_ptr(), 2 * kvh * 64 * hd, pages_per, pages_per, 64, kvh, hd,
+                                   n_pages) for s in stores]
+        q = torch.randn(B, qh * hd, device=dev).bfloat16()
+        out = torch.empty_like(q)
+        slots = torch.arange(B, dtype=torch.int32, device=dev)
+        pos = torch.full((B,), ctx - 1, dtype=torch.int32, device=dev)
+
+        class Ctx:
+            max_context = ctx
+            sm_count = torch.cuda.get_device_properties(0).multi_processor_count
+        splits = a.splits or decode_splits(Ctx, B, kvh, qh)
+        scratch = torch.zeros(max(1, ops.attention_decode_scratch_bytes(B, qh, kvh, hd, splits)), dtype=torch.uint8,
+                              device=dev)
+        i = [0]
+
+        def fn():
+            v = views[i[0] % copies]
+            i[0] += 1
+            ops.attention_decode_bf16(q, out, v, slots, pos, B, qh, 1 / math.sqrt(hd), 0, splits, scratch)
+        print(f"splits {splits}", file=sys.stderr)
+        timed(fn, B * ctx * 2 * kvh * hd * 2, 4.0 * B * qh * hd * ctx)
+        return 0
+
+    if a.kernel == "attention_prefill":
+        hd, kvh, qh, T = a.head_dim, a.kv_heads, a.q_heads, a.context
+        pages_per = (T + 63) // 64
+        store = torch.randn(pages_per, 2, kvh, 64, hd, device=dev).bfloat16()
+        table = torch.arange(pages_per, dtype=torch.int32, device=dev).reshape(1, pages_per).contiguous()
+        view = ops.PagedCacheArg(store.data_ptr(), table.data_ptr(), 2 * kvh * 64 * hd, pages_per, pages_per, 64, kvh,
+                                 hd, pages_per)
+        q = torch.randn(T, qh * hd, device=dev).bfloat16()
+        out = torch.empty_like(q)
+        mk = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)   # noqa: E731
+        n_tiles = (T + 63) // 64
+        tile_seq, tile_row0 = mk([0] * n_tiles), mk(list(range(0, T, 64)))
+        first, sslot, spos0 = mk([0, T]), mk([0]), mk([0])
+        copies = 1
+
+        def fn():
+            ops.attention_prefill_bf16(q, out, view, tile_seq, tile_row0, n_tiles, first, sslot, spos0, qh,
+                                       1 / math.sqrt(hd), 0)
+        timed(fn, 2 * T * qh * hd * 2 + 2 * T * kvh * hd * 2, 4.0 * qh * hd * T * (T + 1) / 2)
+        return 0
+
+    if a.kernel == "add_rmsnorm":
+        rows, h = a.m, a.n
+        resid = torch.randn(rows, h, device=dev)
+        delta = torch.randn(rows, h, device=dev).bfloat16()
+        w = torch.ones(h, device=dev)
+        out = torch.empty_like(delta)
+        copies = 1
+        timed(lambda: ops.add_rmsnorm(resid, delta, w, out, rows, 1e-6), rows * h * (4 + 4 + 2 + 2))
+        return 0
+    print(f"unknown kernel {a.kernel!r}", file=sys.stderr)
+    return 2
+
+
+def main(argv=None) -> int:
+    argv = list(sys.argv[1:] if argv is None else argv)
+    if argv and argv[0] == "replay":
+        return cmd_replay(None, argv[1:])
+    ap = argparse.ArgumentParser(prog="x0ne_engine_b200", description=__doc__,
+                                 formatter_class=argparse.RawDescriptionHelpFormatter)
+    sub = ap.add_subparsers(dest="command", required=True)
+
+    g = sub.add_parser("generate")
+    g.add_argument("model")
+    g.add_argument("--prompt-ids", action="append", required=True, help="comma-separated token ids; repeat per prompt")
+    g.add_argument("--max-tokens", type=int, default=16)
+    g.add_argument("--temperature", type=float, default=0.0)
+    g.add_argument("--top-p", type=float, default=1.0)
+    g.add_argument("--seed", type=int, default=None)
+    g.add_argument("--stop-token-ids", default=None)
+    g.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
+    g.add_argument("--decode", default="graph", choices=["graph", "eager"])
+    g.add_argument("--max-ctx", type=int, default=None)
+    g.set_defaults(fn=cmd_generate)
+
+    b = sub.add_parser("core-bench")
+    b.add_argument("model")
+    b.add_argument("--lengths", default="short,1k,4k")
+    b.add_argument("--decode", type=int, default=256)
+    b.add_argument("--reps", type=int, default=5)
+    b.add_argument("--batch", type=int, default=1)
+    b.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
+    b.set_defaults(fn=cmd_core_bench)
+
+    r = sub.add_parser("roofline")
+    r.add_argument("--config", required=True)
+    r.add_argument("--gpu", type=float, required=True, help="memory bandwidth in GB/s")
+    r.add_argument("--prompt", type=int, required=True)
+    r.add_argument("--generated", type=int, required=True)
+    r.add_argument("--tok-s", type=float, default=None)
+    r.add_argument("--batch", type=int, default=1)
+    r.set_defaults(fn=cmd_roofline)
+
+    i = sub.add_parser("init")
+    i.add_argument("config")
+    i.add_argument("out")
+    i.add_argument("--seed", type=int, default=0)
+    i.add_argument("--linear-std", type=float, default=0.02)
+    i.add_argument("--norm-jitter", type=float, default=0.0)
+    i.set_defaults(fn=cmd_init)
+
+    k = sub.add_parser("kernel-bench")
+    k.add_argument("--kernel", required=True)
+    k.add_argument("--m", type=int, default=8)
+    k.add_argument("--n", type=int, default=4096)
+    k.add_argument("--k", type=int, default=4096)
+    k.add_argument("--batch", type=int, default=8)
+    k.add_argument("--context", type=int, default=3072)
+    k.add_argument("--q-heads", type=int, default=32)
+    k.add_argument("--kv-heads", type=int, default=8)
+    k.add_argument("--head-dim", type=int, default=128)
+    k.add_argument("--splits", type=int, default=0)
+    k.add_argument("--iters", type=int, default=50)
+    k.add_argument("--warmup", type=int, default=5)
+    k.set_defaults(fn=cmd_kernel_bench)
+
+    a = ap.parse_args(argv)
+    return a.fn(a)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

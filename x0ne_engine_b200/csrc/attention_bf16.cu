@@ -282,6 +282,8 @@ struct DecodeArgs {
     float scale_log2;
 };
 
+#define DEC_MAX_PAGES 128
+
 template <int HD, int STAGES>
 __global__ void __launch_bounds__(128) attention_decode_kernel(DecodeArgs a, PagedCache cache) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -315,12 +317,34 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(DecodeArgs a, Pag
     const int p_hi = pg_first + (int)(((int64_t)pg_count * (split + 1)) / a.splits);   // exclusive
     const int n_pages = p_hi - p_lo;
 
+    // The page numbers of this block's range, read once (a lookup inside the loop would put a
+    // dependent global load in front of every copy).
+    __shared__ int s_page[DEC_MAX_PAGES];
+    for (int i = tid; i < n_pages && i < DEC_MAX_PAGES; i += 128) {
+        const int pg = cache.page_table[(int64_t)slot * cache.table_stride + ((p_lo + i) % cache.ring_pages)];
+        s_page[i] = (pg >= 0 && pg < cache.n_pages) ? pg : -1;
+    }
+    __syncthreads();
+    const int64_t head_off = (int64_t)kh * cache.page_size * cache.head_dim;
+    const int64_t v_off = (int64_t)cache.kv_heads * cache.page_size * cache.head_dim;
+    auto tile_ptr = [&](int i) -> const bf16* {
+        int pg;
+        if (i < DEC_MAX_PAGES) {
+            pg = s_page[i];
+        } else {
+            pg = cache.page_table[(int64_t)slot * cache.table_stride + ((p_lo + i) % cache.ring_pages)];
+            if (pg >= cache.n_pages) pg = -1;
+        }
+        return pg < 0 ? nullptr : (const bf16*)cache.base + (int64_t)pg * cache.page_stride + head_off;
+    };
+
     // prologue: up to STAGES - 1 pages in flight
 #pragma unroll
     for (int s = 0; s < STAGES - 1; ++s) {
         if (s < n_pages) {
-            load_page_tile<HD, 128>(ks + s * 64 * LD, page_ptr(cache, slot, p_lo + s, kh, 0), (p_lo + s) * PAGE, pos, tid);
-            load_page_tile<HD, 128>(vs + s * 64 * LD, page_ptr(cache, slot, p_lo + s, kh, 1), (p_lo + s) * PAGE, pos, tid);
+            const bf16* kp = tile_ptr(s);
+            load_page_tile<HD, 128>(ks + s * 64 * LD, kp, (p_lo + s) * PAGE, pos, tid);
+            load_page_tile<HD, 128>(vs + s * 64 * LD, kp ? kp + v_off : nullptr, (p_lo + s) * PAGE, pos, tid);
         }
         cp_async_commit();
     }
@@ -346,8 +370,9 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(DecodeArgs a, Pag
             const int nx = it + STAGES - 1;
             if (nx < n_pages) {
                 const int st = nx % STAGES;
-                load_page_tile<HD, 128>(ks + st * 64 * LD, page_ptr(cache, slot, p_lo + nx, kh, 0), (p_lo + nx) * PAGE, pos, tid);
-                load_page_tile<HD, 128>(vs + st * 64 * LD, page_ptr(cache, slot, p_lo + nx, kh, 1), (p_lo + nx) * PAGE, pos, tid);
+                const bf16* kp = tile_ptr(nx);
+                load_page_tile<HD, 128>(ks + st * 64 * LD, kp, (p_lo + nx) * PAGE, pos, tid);
+                load_page_tile<HD, 128>(vs + st * 64 * LD, kp ? kp + v_off : nullptr, (p_lo + nx) * PAGE, pos, tid);
             }
             cp_async_commit();
         }
@@ -432,20 +457,41 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(DecodeArgs a, Pag
     __syncthreads();
     if (!s_last) return;
     __threadfence();
-    for (int e = tid; e < nheads * HD; e += 128) {
-        const int r = e / HD, d = e % HD;
-        const float* ml = a.part_ml + (qrow0 + r) * a.splits * 2;
-        const float* po = a.part_o + (qrow0 + r) * a.splits * HD;
+    // Per (head, split) weights first, all loads in parallel, then every thread sums four
+    // consecutive output values over the splits in their order.
+    float* wgt = reinterpret_cast<float*>(ks);           // [16][splits]: exp2(m_s - M); then [16]: 1 / L
+    float* inv_l = wgt + 16 * a.splits;
+    for (int e = tid; e < nheads * a.splits; e += 128) {
+        const int r = e / a.splits, sp = e % a.splits;
+        wgt[r * a.splits + sp] = __ldcg(a.part_ml + ((qrow0 + r) * a.splits + sp) * 2);
+    }
+    __syncthreads();
+    if (tid < nheads) {
         float M = -INFINITY;
-        for (int s = 0; s < a.splits; ++s) M = fmaxf(M, __ldcg(ml + 2 * s));
-        float acc = 0.f, L = 0.f;
-        for (int s = 0; s < a.splits; ++s) {
-            const float ms = __ldcg(ml + 2 * s);
+        for (int sp = 0; sp < a.splits; ++sp) M = fmaxf(M, wgt[tid * a.splits + sp]);
+        float L = 0.f;
+        for (int sp = 0; sp < a.splits; ++sp) {
+            const float ms = wgt[tid * a.splits + sp];
             const float f = ms == -INFINITY ? 0.f : exp2f(ms - M);
-            acc += __ldcg(po + s * HD + d) * f;
-            L += __ldcg(ml + 2 * s + 1) * f;
+            wgt[tid * a.splits + sp] = f;
+            L += __ldcg(a.part_ml + ((qrow0 + tid) * a.splits + sp) * 2 + 1) * f;
         }
-        a.out[(qrow0 + r) * HD + d] = __float2bfloat16_rn(acc / L);
+        inv_l[tid] = 1.0f / L;
+    }
+    __syncthreads();
+    for (int e = tid; e < nheads * (HD / 4); e += 128) {
+        const int r = e / (HD / 4), d = (e % (HD / 4)) * 4;
+        const float* po = a.part_o + (qrow0 + r) * a.splits * HD + d;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 8
+        for (int sp = 0; sp < a.splits; ++sp) {
+            const float4 v = __ldcg(reinterpret_cast<const float4*>(po + sp * HD));
+            const float f = wgt[r * a.splits + sp];
+            acc.x += v.x * f; acc.y += v.y * f; acc.z += v.z * f; acc.w += v.w * f;
+        }
+        const float il = inv_l[r];
+        bf16* dst = a.out + (qrow0 + r) * HD + d;
+        *reinterpret_cast<uint2*>(dst) = make_uint2(pack_bf16(acc.x * il, acc.y * il), pack_bf16(acc.z * il, acc.w * il));
     }
 }
 
@@ -457,6 +503,7 @@ static int launch_prefill(const PrefillArgs& a, const PagedCache& cache, int n_t
     const size_t smem = (size_t)(64 + 4 * 64) * (HD + PADE) * sizeof(bf16);
     static bool configured = false;
     if (!configured) {
+        cudaFuncSetAttribute(attention_prefill_kernel<HD>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
         cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) {
             x0ne_set_error("attention_prefill: cannot set %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
@@ -477,6 +524,7 @@ static int launch_decode(const DecodeArgs& a, const PagedCache& cache, int n_row
     if (smem < 16 * (HD + PADE) * sizeof(bf16) + merge) smem = 16 * (HD + PADE) * sizeof(bf16) + merge;
     static bool configured = false;
     if (!configured) {
+        cudaFuncSetAttribute(attention_decode_kernel<HD, DECODE_STAGES>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
         cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<HD, DECODE_STAGES>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) {
@@ -542,7 +590,7 @@ X0NE_API int x0ne_attention_decode_bf16(const void* q, void* out, PagedCache cac
                                         int splits, void* scratch, int64_t scratch_bytes, cudaStream_t stream) {
     if (int e = check_common(cache, q_heads, "attention_decode")) return e;
     X0NE_REQUIRE(n_rows >= 0 && n_rows <= 65535, "attention_decode: %d rows in one launch (limit 65535)", n_rows);
-    X0NE_REQUIRE(splits >= 1 && splits <= 1024, "attention_decode: %d splits", splits);
+    X0NE_REQUIRE(splits >= 1 && splits <= 64, "attention_decode: %d splits (1 to 64)", splits);
     X0NE_REQUIRE(window >= 0, "attention_decode: negative window");
     if (n_rows == 0) return 0;
     DecodeArgs a{};
@@ -561,8 +609,9 @@ X0NE_API int x0ne_attention_decode_bf16(const void* q, void* out, PagedCache cac
         const int G = q_heads / cache.kv_heads, gchunks = (G + 15) / 16;
         const int64_t cn = (((int64_t)n_rows * cache.kv_heads * gchunks * 4 + 255) / 256) * 256;
         a.counters = (int32_t*)scratch;
-        a.part_ml = (float*)((char*)scratch + cn);
-        a.part_o = a.part_ml + (int64_t)n_rows * q_heads * splits * 2;
+        a.part_o = (float*)((char*)scratch + cn);            // 256-byte aligned: read back as float4
+        a.part_ml = a.part_o + (int64_t)n_rows * q_heads * splits * cache.head_dim;
+        X0NE_REQUIRE(((uintptr_t)scratch & 15) == 0, "attention_decode: scratch is not 16-byte aligned");
     }
     DISPATCH_HD(cache.head_dim, return launch_decode<HD_>(a, cache, n_rows, stream));
     X0NE_REQUIRE(false, "attention_decode: head_dim %d not built", cache.head_dim);

@@ -38,7 +38,7 @@ def decode_splits(ctx, n_rows: int, kv_heads: int, q_heads: int) -> int:
     group_chunks = (q_heads // kv_heads + 15) // 16
     blocks = max(1, n_rows * kv_heads * group_chunks)
     pages = max(1, (ctx.max_context + 63) // 64)
-    return int(max(1, min(pages, (2 * ctx.sm_count) // blocks, 64)))
+    return int(max(1, min(pages, (2 * ctx.sm_count) // blocks, 32)))
 
 
 class GQAttention(Mixer):
