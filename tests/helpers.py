@@ -68,14 +68,20 @@ def golden_folder():
 _plain = {}
 
 
-def plain_model(folder):
-    if folder not in _plain:
-        _plain[folder] = P.read_model(folder)
-    return _plain[folder]
+def plain_model(folder, bf16_matrices=False):
+    """(config, tensors).  With `bf16_matrices` every matrix is rounded to bfloat16 first: what a
+    bfloat16 engine holds when the checkpoint stores float32 (vectors stay in 32-bit)."""
+    key = (folder, bf16_matrices)
+    if key not in _plain:
+        cfg, w = P.read_model(folder)
+        if bf16_matrices:
+            w = {k: (P.round_bf16(v) if v.ndim == 2 else v) for k, v in w.items()}
+        _plain[key] = (cfg, w)
+    return _plain[key]
 
 
-def plain_logits(folder, ids):
-    cfg, w = plain_model(folder)
+def plain_logits(folder, ids, bf16_matrices=False):
+    cfg, w = plain_model(folder, bf16_matrices)
     return P.forward(cfg, w, ids)
 
 
