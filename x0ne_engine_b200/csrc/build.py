@@ -31,8 +31,11 @@ NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-Xcompil
 MODULES: Dict[str, List[str]] = {
     "core": ["elementwise.cu", "attention_generic.cu", "gemm_f32.cu", "sampling.cu"],
     "fast": ["attention_bf16.cu", "gemm_bf16.cu", "fast_common.cu"],
+    "noalloc": ["attention_decode_noalloc.cu"],
 }
 HEADERS = ["common.cuh"]
+# files a module's sources include besides the headers (they change its hash too)
+INCLUDED = {"noalloc": ["attention_bf16.cu", "fast_common.cu", "x0ne_noalloc.h"]}
 
 _loaded: Dict[str, ctypes.CDLL] = {}
 _lock = threading.Lock()
@@ -57,7 +60,7 @@ def find_nvcc() -> str:
 def _module_hash(name: str) -> str:
     h = hashlib.sha256()
     h.update(" ".join(ARCH_FLAGS + NVCC_FLAGS).encode())
-    for f in HEADERS + MODULES[name]:
+    for f in HEADERS + MODULES[name] + INCLUDED.get(name, []):
         with open(os.path.join(HERE, f), "rb") as fh:
             h.update(f.encode())
             h.update(fh.read())
