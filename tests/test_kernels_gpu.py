@@ -261,8 +261,9 @@ def test_plain_attention_finds_one_far_key_among_hundreds():
 def tiles_for(first_rows):
     """Host tables of the prefill kernel for sequences whose rows start at first_rows (last = end)."""
     tile_seq, tile_row0 = [], []
+    tr = ops().attention_prefill_tile_rows()
     for s in range(len(first_rows) - 1):
-        for r0 in range(first_rows[s], first_rows[s + 1], 64):
+        for r0 in range(first_rows[s], first_rows[s + 1], tr):
             tile_seq.append(s)
             tile_row0.append(r0)
     mk = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)   # noqa: E731
@@ -277,7 +278,7 @@ def test_prefill_attention_bf16_equals_plain_kernel(q_heads, kv_heads, hd, windo
     o = ops()
     storage, table, view = make_cache(kv_heads, hd, 16, 3, torch.bfloat16, 5)
     fill_cache(storage, torch.bfloat16, 40)
-    lens, pos0, seq_slots = [65, 1, 130], [0, 7, 70], [2, 0, 1]
+    lens, pos0, seq_slots = [65, 1, 130], [0, 7, 70], [2, 0, 1]     # 130 rows: a full tile and a short one
     first = [0, 65, 66, 196]
     n = first[-1]
     slots = torch.tensor(sum(([s] * l for s, l in zip(seq_slots, lens)), []), dtype=torch.int32, device=DEV)

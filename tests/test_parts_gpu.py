@@ -14,14 +14,16 @@ DEV = "cuda:0"
 
 def make_ctx(engine_dtype, n_rows, slots, positions, cache, decode=False):
     from x0ne_engine_b200.engine import StepContext, Workspace
+    from x0ne_engine_b200.csrc import ops
     ws = Workspace(max(64, n_rows), DEV)
     ws.max_want = ws.max_rows
     mk = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)   # noqa: E731
+    tr = ops.attention_prefill_tile_rows()
     return StepContext(n_rows=n_rows, tokens=mk([0] * n_rows), row_slot=mk(slots), row_pos=mk(positions),
                        dtype=engine_dtype, ws=ws, cache=cache, decode=decode, n_seqs=1, max_seq_rows=n_rows,
                        max_context=max(positions) + 1, seq_first_row=mk([0, n_rows]), seq_slot=mk(slots[:1]),
-                       seq_pos0=mk(positions[:1]), n_tiles=(n_rows + 63) // 64,
-                       tile_seq=mk([0] * ((n_rows + 63) // 64)), tile_row0=mk(list(range(0, n_rows, 64))))
+                       seq_pos0=mk(positions[:1]), n_tiles=(n_rows + tr - 1) // tr,
+                       tile_seq=mk([0] * ((n_rows + tr - 1) // tr)), tile_row0=mk(list(range(0, n_rows, tr))))
 
 
 def rnd(shape, seed, scale=1.0):

@@ -241,8 +241,9 @@ def cmd_kernel_bench(a) -> int:
         q = torch.randn(T, qh * hd, device=dev).bfloat16()
         out = torch.empty_like(q)
         mk = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)   # noqa: E731
-        n_tiles = (T + 63) // 64
-        tile_seq, tile_row0 = mk([0] * n_tiles), mk(list(range(0, T, 64)))
+        tr = ops.attention_prefill_tile_rows()
+        n_tiles = (T + tr - 1) // tr
+        tile_seq, tile_row0 = mk([0] * n_tiles), mk(list(range(0, T, tr)))
         first, sslot, spos0 = mk([0, T]), mk([0]), mk([0])
         copies = 1
 

@@ -51,6 +51,7 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 template <int HD, int THREADS>
 __device__ __forceinline__ void load_page_tile(bf16* dst, const bf16* src, int first_pos, int last_pos, int tid) {
     constexpr int CH = HD / 8;  // 16-byte chunks per row
+#pragma unroll
     for (int c = tid; c < PAGE * CH; c += THREADS) {
         const int r = c / CH, k = c % CH;
         bf16* d = dst + r * (HD + PADE) + k * 8;
@@ -145,8 +146,9 @@ __device__ __forceinline__ void softmax_update(float (*s)[4], float (*o)[4], flo
 }
 
 // ----------------------------------------------------------------------------------------
-// Prefill: grid (q_heads, tiles); a tile is up to 64 consecutive rows of one sequence.
-// 4 warps, 16 query rows each.
+// Prefill: grid (q_heads, tiles); a tile is up to 64 * MT consecutive rows of one sequence.
+// 4 warps, 16 * MT query rows each: with MT = 2 every K and V fragment read from shared memory
+// feeds two MMAs, which is what the shared-memory bandwidth needs.  Q stays in shared memory.
 // ----------------------------------------------------------------------------------------
 struct PrefillArgs {
     const bf16* q;
@@ -161,19 +163,22 @@ struct PrefillArgs {
     float scale_log2;
 };
 
-template <int HD>
+template <int HD, int MT>
 __global__ void __launch_bounds__(128) attention_prefill_kernel(PrefillArgs a, PagedCache cache) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     constexpr int LD = HD + PADE;
-    bf16* qs = reinterpret_cast<bf16*>(smem_raw);   // [64][LD]
-    bf16* ks = qs + 64 * LD;                        // [2][64][LD]
+    constexpr int ROWS = 64 * MT;                   // query rows of a tile; a warp owns 16 * MT of them
+    bf16* qs = reinterpret_cast<bf16*>(smem_raw);   // [ROWS][LD]
+    bf16* ks = qs + ROWS * LD;                      // [2][64][LD]
     bf16* vs = ks + 2 * 64 * LD;                    // [2][64][LD]
+    pdl_prologue();
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int head = blockIdx.x, tile = blockIdx.y;
+    // the longest contexts (the last tiles of a sequence) are scheduled first
+    const int head = blockIdx.x, tile = gridDim.y - 1 - blockIdx.y;
     const int kh = head / (a.q_heads / cache.kv_heads);
     const int seq = a.tile_seq[tile], row0 = a.tile_row0[tile];
     const int seq_end = a.seq_first_row[seq + 1];
-    const int nrows = min(64, seq_end - row0);
+    const int nrows = min(ROWS, seq_end - row0);
     const int slot = a.seq_slot[seq];
     const int pos_first = a.seq_pos0[seq] + (row0 - a.seq_first_row[seq]);
     const int pos_last = pos_first + nrows - 1;
@@ -181,7 +186,7 @@ __global__ void __launch_bounds__(128) attention_prefill_kernel(PrefillArgs a, P
 
     // Q tile -> shared (rows past the tile's end are zero)
     constexpr int CH = HD / 8;
-    for (int c = tid; c < 64 * CH; c += 128) {
+    for (int c = tid; c < ROWS * CH; c += 128) {
         const int r = c / CH, k = c % CH;
         bf16* d = qs + r * LD + k * 8;
         if (r < nrows)
@@ -198,19 +203,20 @@ __global__ void __launch_bounds__(128) attention_prefill_kernel(PrefillArgs a, P
     cp_async_wait<0>();
     __syncthreads();
 
-    uint32_t qf[HD / 16][4];
+    const int wrow0 = warp * 16 * MT;               // this warp's first row in the tile
+    float o[MT][HD / 8][4];
+    float m[MT][2], l[MT][2];
 #pragma unroll
-    for (int kk = 0; kk < HD / 16; ++kk) {
-        const int row = warp * 16 + (lane & 15), col = kk * 16 + ((lane >> 4) << 3);
-        ldsm_x4(qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3], qs + row * LD + col);
+    for (int t = 0; t < MT; ++t) {
+#pragma unroll
+        for (int n = 0; n < HD / 8; ++n)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) o[t][n][i] = 0.f;
+        m[t][0] = m[t][1] = -INFINITY;
+        l[t][0] = l[t][1] = 0.f;
     }
-    float o[HD / 8][4];
-#pragma unroll
-    for (int n = 0; n < HD / 8; ++n)
-#pragma unroll
-        for (int i = 0; i < 4; ++i) o[n][i] = 0.f;
-    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
-    const int prow[2] = {pos_first + warp * 16 + (lane >> 2), pos_first + warp * 16 + (lane >> 2) + 8};
+    const int warp_first = pos_first + wrow0;
+    const int warp_last = min(pos_last, warp_first + 16 * MT - 1);
 
     for (int kt = kt_lo; kt <= kt_hi; ++kt) {
         const int buf = (kt - kt_lo) & 1;
@@ -222,42 +228,95 @@ __global__ void __launch_bounds__(128) attention_prefill_kernel(PrefillArgs a, P
         const bf16* kb = ks + buf * 64 * LD;
         const bf16* vb = vs + buf * 64 * LD;
         // A warp whose rows all lie before this tile's first key has nothing to do here.
-        const int warp_last = min(pos_last, pos_first + warp * 16 + 15);
         if (kt * PAGE <= warp_last) {
-            float s[8][4];
-            qk_tile<HD, 8>(s, qf, kb, 0, lane);
-            const bool edge = (kt * PAGE + PAGE - 1 > pos_first + warp * 16) ||
-                              (a.window > 0 && kt * PAGE <= warp_last - a.window + 16);
+            float s[MT][8][4];
 #pragma unroll
-            for (int n = 0; n < 8; ++n)
+            for (int t = 0; t < MT; ++t)
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    float v = s[n][i] * a.scale_log2;
-                    if (edge) {
-                        const int j = kt * PAGE + n * 8 + ((lane & 3) << 1) + (i & 1);
-                        const int p = prow[i >> 1];
-                        if (j > p || p > pos_last || (a.window > 0 && j <= p - a.window)) v = -INFINITY;
-                    }
-                    s[n][i] = v;
+                for (int n = 0; n < 8; ++n)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) s[t][n][i] = 0.f;
+#pragma unroll
+            for (int kk = 0; kk < HD / 16; ++kk) {
+                uint32_t kf[4][4];
+#pragma unroll
+                for (int n2 = 0; n2 < 4; ++n2) {
+                    const int row = n2 * 16 + (lane & 7) + ((lane >> 4) << 3);
+                    const int col = kk * 16 + (((lane >> 3) & 1) << 3);
+                    ldsm_x4(kf[n2][0], kf[n2][1], kf[n2][2], kf[n2][3], kb + row * LD + col);
                 }
-            softmax_update<HD, 8>(s, o, m, l);
-            pv_tile<HD, 8>(o, s, vb, 0, lane);
+#pragma unroll
+                for (int t = 0; t < MT; ++t) {
+                    uint32_t qf[4];
+                    const int row = wrow0 + t * 16 + (lane & 15), col = kk * 16 + ((lane >> 4) << 3);
+                    ldsm_x4(qf[0], qf[1], qf[2], qf[3], qs + row * LD + col);
+#pragma unroll
+                    for (int n2 = 0; n2 < 4; ++n2) {
+                        mma_bf16(s[t][2 * n2], qf, kf[n2][0], kf[n2][1]);
+                        mma_bf16(s[t][2 * n2 + 1], qf, kf[n2][2], kf[n2][3]);
+                    }
+                }
+            }
+            const bool edge = (kt * PAGE + PAGE - 1 > warp_first) ||
+                              (a.window > 0 && kt * PAGE <= warp_last - a.window + 16 * MT);
+#pragma unroll
+            for (int t = 0; t < MT; ++t) {
+                const int p0 = warp_first + t * 16 + (lane >> 2);
+#pragma unroll
+                for (int n = 0; n < 8; ++n)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        float v = s[t][n][i] * a.scale_log2;
+                        if (edge) {
+                            const int j = kt * PAGE + n * 8 + ((lane & 3) << 1) + (i & 1);
+                            const int p = p0 + ((i >> 1) << 3);
+                            if (j > p || (a.window > 0 && j <= p - a.window)) v = -INFINITY;
+                        }
+                        s[t][n][i] = v;
+                    }
+                softmax_update<HD, 8>(s[t], o[t], m[t], l[t]);
+            }
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk) {
+                uint32_t pa[MT][4];
+#pragma unroll
+                for (int t = 0; t < MT; ++t) {
+                    pa[t][0] = pack_bf16(s[t][2 * kk][0], s[t][2 * kk][1]);
+                    pa[t][1] = pack_bf16(s[t][2 * kk][2], s[t][2 * kk][3]);
+                    pa[t][2] = pack_bf16(s[t][2 * kk + 1][0], s[t][2 * kk + 1][1]);
+                    pa[t][3] = pack_bf16(s[t][2 * kk + 1][2], s[t][2 * kk + 1][3]);
+                }
+#pragma unroll
+                for (int n2 = 0; n2 < HD / 16; ++n2) {
+                    uint32_t b0, b1, b2, b3;
+                    const int row = kk * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
+                    const int col = n2 * 16 + ((lane >> 4) << 3);
+                    ldsm_x4_t(b0, b1, b2, b3, vb + row * LD + col);
+#pragma unroll
+                    for (int t = 0; t < MT; ++t) {
+                        mma_bf16(o[t][2 * n2], pa[t], b0, b1);
+                        mma_bf16(o[t][2 * n2 + 1], pa[t], b2, b3);
+                    }
+                }
+            }
         }
         cp_async_wait<0>();
         __syncthreads();
     }
     // write
 #pragma unroll
-    for (int h = 0; h < 2; ++h) {
-        const int r = warp * 16 + (lane >> 2) + 8 * h;
-        if (r < nrows) {
-            const float inv = 1.0f / l[h];
-            bf16* dst = a.out + (int64_t)(row0 + r) * q_dim + head * HD + ((lane & 3) << 1);
+    for (int t = 0; t < MT; ++t)
 #pragma unroll
-            for (int n = 0; n < HD / 8; ++n)
-                *reinterpret_cast<uint32_t*>(dst + n * 8) = pack_bf16(o[n][2 * h] * inv, o[n][2 * h + 1] * inv);
+        for (int h = 0; h < 2; ++h) {
+            const int r = wrow0 + t * 16 + (lane >> 2) + 8 * h;
+            if (r < nrows) {
+                const float inv = 1.0f / l[t][h];
+                bf16* dst = a.out + (int64_t)(row0 + r) * q_dim + head * HD + ((lane & 3) << 1);
+#pragma unroll
+                for (int n = 0; n < HD / 8; ++n)
+                    *reinterpret_cast<uint32_t*>(dst + n * 8) = pack_bf16(o[t][n][2 * h] * inv, o[t][n][2 * h + 1] * inv);
+            }
         }
-    }
 }
 
 // ----------------------------------------------------------------------------------------
@@ -292,6 +351,7 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(DecodeArgs a, Pag
     bf16* ks = qs + 16 * LD;                        // [STAGES][64][LD]
     bf16* vs = ks + STAGES * 64 * LD;               // [STAGES][64][LD]
     __shared__ int s_last;
+    pdl_prologue();
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int split = blockIdx.x, b = blockIdx.z;
     const int G = a.q_heads / cache.kv_heads;
@@ -498,13 +558,14 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(DecodeArgs a, Pag
 // ----------------------------------------------------------------------------------------
 // host
 // ----------------------------------------------------------------------------------------
+#define PREFILL_MT 2
 template <int HD>
 static int launch_prefill(const PrefillArgs& a, const PagedCache& cache, int n_tiles, cudaStream_t stream) {
-    const size_t smem = (size_t)(64 + 4 * 64) * (HD + PADE) * sizeof(bf16);
+    const size_t smem = (size_t)(64 * PREFILL_MT + 4 * 64) * (HD + PADE) * sizeof(bf16);
     static bool configured = false;
     if (!configured) {
-        cudaFuncSetAttribute(attention_prefill_kernel<HD>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
-        cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaFuncSetAttribute(attention_prefill_kernel<HD, PREFILL_MT>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
+        cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel<HD, PREFILL_MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) {
             x0ne_set_error("attention_prefill: cannot set %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
             return (int)e;
@@ -512,11 +573,11 @@ static int launch_prefill(const PrefillArgs& a, const PagedCache& cache, int n_t
         configured = true;
     }
     dim3 grid(a.q_heads, n_tiles);
-    attention_prefill_kernel<HD><<<grid, 128, smem, stream>>>(a, cache);
+    x0ne_launch(attention_prefill_kernel<HD, PREFILL_MT>, dim3(grid), dim3(128), smem, stream, a, cache);
     X0NE_LAUNCH_CHECK();
 }
 
-#define DECODE_STAGES 3
+#define DECODE_STAGES 2
 template <int HD>
 static int launch_decode(const DecodeArgs& a, const PagedCache& cache, int n_rows, cudaStream_t stream) {
     size_t smem = (size_t)(16 + 2 * DECODE_STAGES * 64) * (HD + PADE) * sizeof(bf16);
@@ -535,7 +596,7 @@ static int launch_decode(const DecodeArgs& a, const PagedCache& cache, int n_row
     }
     const int G = a.q_heads / cache.kv_heads;
     dim3 grid(a.splits, cache.kv_heads * ((G + 15) / 16), n_rows);
-    attention_decode_kernel<HD, DECODE_STAGES><<<grid, 128, smem, stream>>>(a, cache);
+    x0ne_launch(attention_decode_kernel<HD, DECODE_STAGES>, dim3(grid), dim3(128), smem, stream, a, cache);
     X0NE_LAUNCH_CHECK();
 }
 
@@ -574,6 +635,13 @@ X0NE_API int x0ne_attention_prefill_bf16(const void* q, void* out, PagedCache ca
     DISPATCH_HD(cache.head_dim, return launch_prefill<HD_>(a, cache, n_tiles, stream));
     X0NE_REQUIRE(false, "attention_prefill: head_dim %d not built", cache.head_dim);
 }
+
+// Rows of one tile of the prefill kernel: callers build their tile tables with it.
+X0NE_API int x0ne_attention_prefill_tile_rows() { return 64 * PREFILL_MT; }
+
+// Blocks of the decode kernel that fit on one SM at head_dim 128 (shared memory decides): callers
+// size `splits` so that a launch is one wave.
+X0NE_API int x0ne_attention_decode_blocks_per_sm() { return DECODE_STAGES == 2 ? 3 : 2; }
 
 // Scratch the decode kernel needs for `n_rows` sequences with `splits` splits, in bytes:
 // partial outputs, partial (m, l), and the arrival counters (which must start at zero).

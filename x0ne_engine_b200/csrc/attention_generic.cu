@@ -22,6 +22,7 @@ __global__ void attention_rows_kernel(const T* __restrict__ q, T* __restrict__ o
                                       const int32_t* __restrict__ row_slot, const int32_t* __restrict__ row_pos,
                                       int n_rows, int q_heads, float scale, int window) {
     extern __shared__ float smem[];
+    pdl_prologue();
     const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
     const int hd = cache.head_dim;
     const int64_t item = (int64_t)blockIdx.x * (blockDim.x >> 5) + w;
@@ -99,10 +100,10 @@ X0NE_API int x0ne_attention_rows(const void* q, void* out, int dt, PagedCache ca
     const unsigned grid = (unsigned)((items + warps - 1) / warps);
     const size_t smem = (size_t)warps * cache.head_dim * sizeof(float);
     if (dt == X0NE_F32)
-        attention_rows_kernel<float><<<grid, warps * 32, smem, stream>>>((const float*)q, (float*)out, cache, row_slot,
+        x0ne_launch(attention_rows_kernel<float>, dim3(grid), dim3(warps * 32), smem, stream, (const float*)q, (float*)out, cache, row_slot,
                                                                        row_pos, n_rows, q_heads, scale, window);
     else if (dt == X0NE_BF16)
-        attention_rows_kernel<bf16><<<grid, warps * 32, smem, stream>>>((const bf16*)q, (bf16*)out, cache, row_slot,
+        x0ne_launch(attention_rows_kernel<bf16>, dim3(grid), dim3(warps * 32), smem, stream, (const bf16*)q, (bf16*)out, cache, row_slot,
                                                                       row_pos, n_rows, q_heads, scale, window);
     else
         X0NE_REQUIRE(false, "attention: unknown dtype tag %d", dt);

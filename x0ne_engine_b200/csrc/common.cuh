@@ -43,6 +43,38 @@ void x0ne_set_error(const char* fmt, ...);
         return 0;                                                    \
     } while (0)
 
+// Programmatic dependent launch.  Every kernel of this library is launched so that it may start
+// while the kernel before it in the stream is still running (its blocks are scheduled and run
+// their prologue early); `pdl_wait` then blocks until that kernel has finished and its writes
+// are visible.  A kernel calls `pdl_launch_dependents` at once, to let its own successor start
+// early in turn, and `pdl_wait` before it touches anything an earlier kernel may have written,
+// and before its own first write.  Only reads of weights may come before the wait.
+// Set X0NE_PDL=0 in the environment to launch everything fully serialized.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_prologue() {
+    pdl_launch_dependents();
+    pdl_wait();
+}
+
+bool x0ne_pdl_enabled();
+
+template <typename... KArgs, typename... Args>
+static inline cudaError_t x0ne_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                      Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = x0ne_pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 __device__ __forceinline__ float to_f32(float x) { return x; }
 __device__ __forceinline__ float to_f32(bf16 x) { return __bfloat162float(x); }
 template <typename T> __device__ __forceinline__ T from_f32(float x);

@@ -3,6 +3,7 @@
 // the serving path); per-channel weights are always float32.
 #include <stdarg.h>
 #include <stdio.h>
+#include <stdlib.h>
 
 #include "common.cuh"
 
@@ -17,6 +18,16 @@ void x0ne_set_error(const char* fmt, ...) {
 
 X0NE_API const char* x0ne_last_error() { return g_error; }
 
+bool x0ne_pdl_enabled() {
+    static int on = -1;
+    if (on < 0) {
+        const char* e = getenv("X0NE_PDL");
+        on = (e != nullptr && e[0] == '0') ? 0 : 1;
+    }
+    return on == 1;
+}
+
+
 // ----------------------------------------------------------------------------------------
 // Embedding: resid[r] = f32(table[tokens[r]]); an id outside the table gives a zero row
 // (x0ne-core/kernels/cuda/embedding.cu:5-17).  The engine there copies the row and lets the
@@ -26,6 +37,7 @@ X0NE_API const char* x0ne_last_error() { return g_error; }
 template <typename T>
 __global__ void embedding_kernel(const T* __restrict__ table, const int32_t* __restrict__ tokens,
                                  float* __restrict__ resid, int hidden, int vocab) {
+    pdl_prologue();
     const int row = blockIdx.x;
     const int t = tokens[row];
     float* dst = resid + (int64_t)row * hidden;
@@ -43,9 +55,9 @@ X0NE_API int x0ne_embedding(const void* table, int dt, const int32_t* tokens, fl
     if (n_rows == 0) return 0;
     const int block = hidden >= 1024 ? 256 : 128;
     if (dt == X0NE_F32)
-        embedding_kernel<float><<<n_rows, block, 0, stream>>>((const float*)table, tokens, resid, hidden, vocab);
+        x0ne_launch(embedding_kernel<float>, dim3(n_rows), dim3(block), 0, stream, (const float*)table, tokens, resid, hidden, vocab);
     else if (dt == X0NE_BF16)
-        embedding_kernel<bf16><<<n_rows, block, 0, stream>>>((const bf16*)table, tokens, resid, hidden, vocab);
+        x0ne_launch(embedding_kernel<bf16>, dim3(n_rows), dim3(block), 0, stream, (const bf16*)table, tokens, resid, hidden, vocab);
     else
         X0NE_REQUIRE(false, "embedding: unknown dtype tag %d", dt);
     X0NE_LAUNCH_CHECK();
@@ -64,6 +76,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const T* __restric
                                    const float* __restrict__ w, T* __restrict__ out,
                                    const int32_t* __restrict__ rows, int hidden, float eps) {
     __shared__ float sh[32];
+    pdl_prologue();
     const int64_t src = rows ? rows[blockIdx.x] : blockIdx.x;
     float* r = resid + src * hidden;
     const T* d = delta ? delta + src * hidden : nullptr;
@@ -111,11 +124,27 @@ __device__ __forceinline__ void store8(bf16* p, const float* v) {
     *reinterpret_cast<uint4*>(p) = u;
 }
 
+__device__ __forceinline__ void load2(const float* p, float* v) {
+    const float2 a = *reinterpret_cast<const float2*>(p);
+    v[0] = a.x; v[1] = a.y;
+}
+__device__ __forceinline__ void load2(const bf16* p, float* v) {
+    const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p));
+    v[0] = f.x; v[1] = f.y;
+}
+__device__ __forceinline__ void store2(float* p, const float* v) { *reinterpret_cast<float2*>(p) = make_float2(v[0], v[1]); }
+__device__ __forceinline__ void store2(bf16* p, const float* v) {
+    *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(v[0], v[1]);
+}
+__device__ __forceinline__ void copy2(float* d, const float* s) { *reinterpret_cast<float2*>(d) = *reinterpret_cast<const float2*>(s); }
+__device__ __forceinline__ void copy2(bf16* d, const bf16* s) { *reinterpret_cast<uint32_t*>(d) = *reinterpret_cast<const uint32_t*>(s); }
+
 template <typename T>
 __global__ void add_rmsnorm_vec_kernel(float* __restrict__ resid, const T* __restrict__ delta,
                                        const float* __restrict__ w, T* __restrict__ out,
                                        const int32_t* __restrict__ rows, int hidden, float eps) {
     __shared__ float sh[32];
+    pdl_prologue();
     const int64_t src = rows ? rows[blockIdx.x] : blockIdx.x;
     float* r = resid + src * hidden;
     const T* d = delta ? delta + src * hidden : nullptr;
@@ -163,18 +192,18 @@ X0NE_API int x0ne_add_rmsnorm(float* resid, const void* delta, const float* w, v
         if (threads > 1024) threads = 1024;
         if (hidden / 8 > 512 && hidden / 8 <= 1024) threads = 512;   // two sweeps of 512 rather than one of 1024
         if (dt == X0NE_F32)
-            add_rmsnorm_vec_kernel<float><<<n_rows, threads, 0, stream>>>(resid, (const float*)delta, w, (float*)out, rows, hidden, eps);
+            x0ne_launch(add_rmsnorm_vec_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, resid, (const float*)delta, w, (float*)out, rows, hidden, eps);
         else if (dt == X0NE_BF16)
-            add_rmsnorm_vec_kernel<bf16><<<n_rows, threads, 0, stream>>>(resid, (const bf16*)delta, w, (bf16*)out, rows, hidden, eps);
+            x0ne_launch(add_rmsnorm_vec_kernel<bf16>, dim3(n_rows), dim3(threads), 0, stream, resid, (const bf16*)delta, w, (bf16*)out, rows, hidden, eps);
         else
             X0NE_REQUIRE(false, "add_rmsnorm: unknown dtype tag %d", dt);
         X0NE_LAUNCH_CHECK();
     }
     const int block = 256;
     if (dt == X0NE_F32)
-        add_rmsnorm_kernel<float><<<n_rows, block, 0, stream>>>(resid, (const float*)delta, w, (float*)out, rows, hidden, eps);
+        x0ne_launch(add_rmsnorm_kernel<float>, dim3(n_rows), dim3(block), 0, stream, resid, (const float*)delta, w, (float*)out, rows, hidden, eps);
     else if (dt == X0NE_BF16)
-        add_rmsnorm_kernel<bf16><<<n_rows, block, 0, stream>>>(resid, (const bf16*)delta, w, (bf16*)out, rows, hidden, eps);
+        x0ne_launch(add_rmsnorm_kernel<bf16>, dim3(n_rows), dim3(block), 0, stream, resid, (const bf16*)delta, w, (bf16*)out, rows, hidden, eps);
     else
         X0NE_REQUIRE(false, "add_rmsnorm: unknown dtype tag %d", dt);
     X0NE_LAUNCH_CHECK();
@@ -182,7 +211,8 @@ X0NE_API int x0ne_add_rmsnorm(float* resid, const void* delta, const float* w, v
 
 // ----------------------------------------------------------------------------------------
 // Per-head RMSNorm of q and k (optional), rotate-half RoPE, and the K/V write into the
-// paged cache (x0ne-core/kernels/cuda/rope.cu:7-47).  One warp per (row, head); heads
+// paged cache (x0ne-core/kernels/cuda/rope.cu:7-47).  One block per row: the row's sines and cosines
+// are computed once into shared memory, then one warp per head; heads
 // 0..q_heads-1 are q heads, the rest k heads, whose warps also copy the v head.
 //   scale = rsqrt(mean(x^2 over head_dim) + eps); n = x * scale * w
 //   angle = (float)pos * inv_freq[i]; (a, b) = (n[i], n[i + rot/2])
@@ -191,17 +221,12 @@ X0NE_API int x0ne_add_rmsnorm(float* resid, const void* delta, const float* w, v
 // A row whose position has no page writes nothing into the cache.
 // ----------------------------------------------------------------------------------------
 template <typename T>
-__global__ void qk_norm_rope_kv_write_kernel(const T* __restrict__ qkv, const float* __restrict__ norm_q,
-                                             const float* __restrict__ norm_k,
-                                             const float* __restrict__ inv_freq, int rot, T* __restrict__ q_out,
-                                             PagedCache cache, const int32_t* __restrict__ row_slot,
-                                             const int32_t* __restrict__ row_pos, int n_rows, int q_heads,
-                                             float eps, int write_kv) {
+__device__ __forceinline__ void rope_one_head(const T* __restrict__ qkv, const float* __restrict__ norm_q,
+                                              const float* __restrict__ norm_k, int rot, T* __restrict__ q_out,
+                                              const PagedCache& cache, const int32_t* __restrict__ row_slot, int row, int pos,
+                                              int head, int q_heads, float eps, int write_kv,
+                                              const float* __restrict__ cs_tab, const float* __restrict__ sn_tab) {
     const int lane = threadIdx.x & 31;
-    const int heads = q_heads + cache.kv_heads;
-    const int64_t item = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (item >= (int64_t)n_rows * heads) return;
-    const int row = (int)(item / heads), head = (int)(item % heads);
     const int hd = cache.head_dim, half = rot >> 1;
     const int q_dim = q_heads * hd, kv_dim = cache.kv_heads * hd;
     const bool is_q = head < q_heads;
@@ -209,7 +234,63 @@ __global__ void qk_norm_rope_kv_write_kernel(const T* __restrict__ qkv, const fl
     if (!is_q && !write_kv) return;
     const T* src = qkv + (int64_t)row * (q_dim + 2 * kv_dim) + (is_q ? head * hd : q_dim + kh * hd);
     const float* nw = is_q ? norm_q : norm_k;
-    const int pos = row_pos[row];
+
+    T* dst;
+    if (is_q) {
+        dst = q_out + (int64_t)row * q_dim + head * hd;
+    } else {
+        const int64_t off = cache_row_offset(cache, row_slot[row], pos, kh, 0);
+        if (off < 0) return;
+        dst = (T*)cache.base + off;
+    }
+
+    // The common shape (whole head rotated, head_dim a multiple of 4 up to 256): each lane owns the
+    // pairs (i, i + half) for i = 2 lane, 2 lane + 1 (+ 64 ...), keeps them in registers between the
+    // sum of squares and the rotation, and moves two values per access.
+    if (rot == hd && (hd & 3) == 0 && hd <= 256) {
+        float a[2][2], b[2][2];
+        float ss = 0.f;
+#pragma unroll
+        for (int it = 0; it < 2; ++it) {
+            const int i = 2 * lane + 64 * it;
+            if (i < half) {
+                load2(src + i, a[it]);
+                load2(src + i + half, b[it]);
+                ss += a[it][0] * a[it][0] + a[it][1] * a[it][1] + b[it][0] * b[it][0] + b[it][1] * b[it][1];
+            }
+        }
+        float scale = 1.f;
+        if (nw) {
+            ss = warp_sum(ss);
+            scale = 1.0f / sqrtf(ss / (float)hd + eps);
+        }
+#pragma unroll
+        for (int it = 0; it < 2; ++it) {
+            const int i = 2 * lane + 64 * it;
+            if (i < half) {
+                float ra[2], rb[2];
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    float x = a[it][e], y = b[it][e];
+                    if (nw) {
+                        x = x * scale * nw[i + e];
+                        y = y * scale * nw[i + e + half];
+                    }
+                    const float sn = sn_tab[i + e], cs = cs_tab[i + e];
+                    ra[e] = x * cs - y * sn;
+                    rb[e] = y * cs + x * sn;
+                }
+                store2(dst + i, ra);
+                store2(dst + i + half, rb);
+            }
+        }
+        if (!is_q) {
+            const T* vs = src + kv_dim;
+            T* vd = dst + (int64_t)cache.kv_heads * cache.page_size * hd;
+            for (int i = 2 * lane; i < hd; i += 64) copy2(vd + i, vs + i);
+        }
+        return;
+    }
 
     float scale = 1.f;
     if (nw) {
@@ -221,23 +302,13 @@ __global__ void qk_norm_rope_kv_write_kernel(const T* __restrict__ qkv, const fl
         ss = warp_sum(ss);
         scale = 1.0f / sqrtf(ss / (float)hd + eps);
     }
-
-    T* dst;
-    if (is_q) {
-        dst = q_out + (int64_t)row * q_dim + head * hd;
-    } else {
-        const int64_t off = cache_row_offset(cache, row_slot[row], pos, kh, 0);
-        if (off < 0) return;
-        dst = (T*)cache.base + off;
-    }
     for (int i = lane; i < half; i += 32) {
         float a = to_f32(src[i]), b = to_f32(src[i + half]);
         if (nw) {
             a = a * scale * nw[i];
             b = b * scale * nw[i + half];
         }
-        float s, c;
-        sincosf((float)pos * inv_freq[i], &s, &c);
+        const float s = sn_tab[i], c = cs_tab[i];
         dst[i] = from_f32<T>(a * c - b * s);
         dst[i + half] = from_f32<T>(b * c + a * s);
     }
@@ -253,6 +324,30 @@ __global__ void qk_norm_rope_kv_write_kernel(const T* __restrict__ qkv, const fl
     }
 }
 
+
+template <typename T>
+__global__ void qk_norm_rope_kv_write_kernel(const T* __restrict__ qkv, const float* __restrict__ norm_q,
+                                             const float* __restrict__ norm_k,
+                                             const float* __restrict__ inv_freq, int rot, T* __restrict__ q_out,
+                                             PagedCache cache, const int32_t* __restrict__ row_slot,
+                                             const int32_t* __restrict__ row_pos, int n_rows, int q_heads,
+                                             float eps, int write_kv) {
+    extern __shared__ float rope_cs[];          // [half] cosines, then [half] sines of this row's angles
+    pdl_prologue();
+    const int lane = threadIdx.x & 31;
+    const int heads = q_heads + cache.kv_heads;
+    const int row = blockIdx.x;
+    const int hd = cache.head_dim, half = rot >> 1;
+    const int q_dim = q_heads * hd, kv_dim = cache.kv_heads * hd;
+    const int pos = row_pos[row];
+    float* cs_tab = rope_cs;
+    float* sn_tab = rope_cs + half;
+    for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf((float)pos * inv_freq[i], &sn_tab[i], &cs_tab[i]);
+    __syncthreads();
+    for (int head = threadIdx.x >> 5; head < heads; head += blockDim.x >> 5)
+        rope_one_head<T>(qkv, norm_q, norm_k, rot, q_out, cache, row_slot, row, pos, head, q_heads, eps, write_kv, cs_tab, sn_tab);
+}
+
 X0NE_API int x0ne_qk_norm_rope_kv_write(const void* qkv, int dt, const float* norm_q, const float* norm_k,
                                         const float* inv_freq, int rotary_dim, void* q_out, PagedCache cache,
                                         const int32_t* row_slot, const int32_t* row_pos, int n_rows, int q_heads,
@@ -262,15 +357,18 @@ X0NE_API int x0ne_qk_norm_rope_kv_write(const void* qkv, int dt, const float* no
                  "rope: rotary_dim %d must be even and at most head_dim %d", rotary_dim, cache.head_dim);
     X0NE_REQUIRE(rotary_dim == 0 || inv_freq != nullptr, "rope: no inv_freq table");
     if (n_rows == 0) return 0;
-    const int warps = 4;
-    const int64_t items = (int64_t)n_rows * (q_heads + cache.kv_heads);
-    const unsigned grid = (unsigned)((items + warps - 1) / warps);
+    // one block per row; few rows (decode): as many warps as heads, so no warp loops
+    const int heads = q_heads + cache.kv_heads;
+    int warps = n_rows >= 64 ? 8 : (heads < 32 ? heads : 32);
+    X0NE_REQUIRE(n_rows <= 0x7fffffff, "rope: too many rows");
+    const unsigned grid = (unsigned)n_rows;
+    const size_t smem = (size_t)rotary_dim * sizeof(float);
     if (dt == X0NE_F32)
-        qk_norm_rope_kv_write_kernel<float><<<grid, warps * 32, 0, stream>>>(
+        x0ne_launch(qk_norm_rope_kv_write_kernel<float>, dim3(grid), dim3(warps * 32), smem, stream, 
             (const float*)qkv, norm_q, norm_k, inv_freq, rotary_dim, (float*)q_out, cache, row_slot, row_pos, n_rows,
             q_heads, eps, write_kv);
     else if (dt == X0NE_BF16)
-        qk_norm_rope_kv_write_kernel<bf16><<<grid, warps * 32, 0, stream>>>(
+        x0ne_launch(qk_norm_rope_kv_write_kernel<bf16>, dim3(grid), dim3(warps * 32), smem, stream, 
             (const bf16*)qkv, norm_q, norm_k, inv_freq, rotary_dim, (bf16*)q_out, cache, row_slot, row_pos, n_rows,
             q_heads, eps, write_kv);
     else
@@ -284,6 +382,7 @@ X0NE_API int x0ne_qk_norm_rope_kv_write(const void* qkv, int dt, const float* no
 // ----------------------------------------------------------------------------------------
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter) {
+    pdl_prologue();
     const int i = blockIdx.x * blockDim.x + threadIdx.x, r = blockIdx.y;
     if (i >= inter) return;
     const T* row = gate_up + (int64_t)r * 2 * inter;
@@ -291,19 +390,50 @@ __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out
     out[(int64_t)r * inter + i] = from_f32<T>(g / (1.0f + expf(-g)) * u);
 }
 
+// 8 values per thread with 16-byte accesses (inter % 8 == 0 and aligned rows).
+template <typename T>
+__global__ void swiglu_vec_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter, int64_t total8) {
+    pdl_prologue();
+    const int per_row = inter / 8;
+    for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < total8; e += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = e / per_row;
+        const int i = (int)(e % per_row) * 8;
+        const T* row = gate_up + r * 2 * inter;
+        float g[8], u[8], o[8];
+        load8(row + i, g);
+        load8(row + inter + i, u);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) o[k] = g[k] / (1.0f + expf(-g[k])) * u[k];
+        store8(out + r * inter + i, o);
+    }
+}
+
 X0NE_API int x0ne_swiglu(const void* gate_up, void* out, int dt, int n_rows, int inter, cudaStream_t stream) {
     X0NE_REQUIRE(n_rows >= 0 && inter > 0, "swiglu: rows %d inter %d", n_rows, inter);
     if (n_rows == 0) return 0;
     X0NE_REQUIRE(n_rows <= 65535 * 1024, "swiglu: too many rows for one launch");
+    const int esize = dt == X0NE_F32 ? 4 : 2;
+    if (inter % 8 == 0 && (((uintptr_t)gate_up | (uintptr_t)out) & 15) == 0 && ((int64_t)inter * esize) % 16 == 0) {
+        const int64_t total8 = (int64_t)n_rows * (inter / 8);
+        int64_t blocks = (total8 + 255) / 256;
+        if (blocks > 148 * 16) blocks = 148 * 16;
+        if (dt == X0NE_F32)
+            x0ne_launch(swiglu_vec_kernel<float>, dim3((unsigned)blocks), dim3(256), 0, stream, (const float*)gate_up, (float*)out, inter, total8);
+        else if (dt == X0NE_BF16)
+            x0ne_launch(swiglu_vec_kernel<bf16>, dim3((unsigned)blocks), dim3(256), 0, stream, (const bf16*)gate_up, (bf16*)out, inter, total8);
+        else
+            X0NE_REQUIRE(false, "swiglu: unknown dtype tag %d", dt);
+        X0NE_LAUNCH_CHECK();
+    }
     for (int r0 = 0; r0 < n_rows; r0 += 65535) {
         const int nr = n_rows - r0 < 65535 ? n_rows - r0 : 65535;
         dim3 grid((inter + 255) / 256, nr);
         if (dt == X0NE_F32)
-            swiglu_kernel<float><<<grid, 256, 0, stream>>>((const float*)gate_up + (int64_t)r0 * 2 * inter,
-                                                           (float*)out + (int64_t)r0 * inter, inter);
+            x0ne_launch(swiglu_kernel<float>, dim3(grid), dim3(256), 0, stream, (const float*)gate_up + (int64_t)r0 * 2 * inter,
+                        (float*)out + (int64_t)r0 * inter, inter);
         else if (dt == X0NE_BF16)
-            swiglu_kernel<bf16><<<grid, 256, 0, stream>>>((const bf16*)gate_up + (int64_t)r0 * 2 * inter,
-                                                          (bf16*)out + (int64_t)r0 * inter, inter);
+            x0ne_launch(swiglu_kernel<bf16>, dim3(grid), dim3(256), 0, stream, (const bf16*)gate_up + (int64_t)r0 * 2 * inter,
+                        (bf16*)out + (int64_t)r0 * inter, inter);
         else
             X0NE_REQUIRE(false, "swiglu: unknown dtype tag %d", dt);
     }

@@ -1,6 +1,7 @@
 // Error reporting of the `fast` module (each module is a library of its own).
 #include <stdarg.h>
 #include <stdio.h>
+#include <stdlib.h>
 
 #include "common.cuh"
 
@@ -14,3 +15,13 @@ void x0ne_set_error(const char* fmt, ...) {
 }
 
 X0NE_API const char* x0ne_last_error() { return g_error; }
+
+bool x0ne_pdl_enabled() {
+    static int on = -1;
+    if (on < 0) {
+        const char* e = getenv("X0NE_PDL");
+        on = (e != nullptr && e[0] == '0') ? 0 : 1;
+    }
+    return on == 1;
+}
+

@@ -3,9 +3,9 @@
 // A decode step multiplies a handful of rows by every weight matrix of the model, so the product
 // is bound by reading W once from HBM (the library engine gives these shapes to cublasGemmEx,
 // x0ne-core/runtime/src/gpu.rs:1098-1149).  Here W is the A operand of mma.sync m16n8k16: a warp
-// takes 16 weight rows and streams them along K with 16-byte loads that bypass L1, the M <= 8*MT
-// activation rows are the B operand (read through L1, where they stay), and the accumulators are
-// float32.  Because a dot product does not care about the order of its terms, each thread feeds
+// takes 16 weight rows and streams them along K with 16-byte asynchronous copies (cp.async.cg,
+// which bypasses L1), the M <= 8*MT activation rows are the B operand (copied the same way, from
+// L2), and the accumulators are float32.  Because a dot product does not care about the order of its terms, each thread feeds
 // the 8 consecutive k values of its 16-byte load to the MMA slots directly (the same permutation on
 // both operands), so no shuffle or shared-memory staging is needed.  The 8 warps of a block split K
 // in interleaved 32-value chunks and are summed in a fixed order at the end.
@@ -28,18 +28,37 @@ __device__ __forceinline__ void mma16816(float* c, uint32_t a0, uint32_t a1, uin
 }
 
 #define SM_WARPS 8
-#define SM_UNROLL 4
 
-template <int MT, typename OutT, bool SWIGLU>
+// 16 bytes global -> shared, asynchronously; `bytes` = 0 writes zeros instead (out-of-range rows or k).
+__device__ __forceinline__ void cp_async16_zfill(void* dst, const void* src, int bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src),
+                 "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ void cp_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
+
+// Each thread streams its 16-byte pieces of W through a private ring of DEPTH slots in shared
+// memory with cp.async: DEPTH chunks (2 rows x 16 bytes each, per weight set) are in flight per
+// thread whatever the register allocator does, which is what hides the memory latency.  A thread
+// reads back only what it copied itself, so no barrier is needed inside the k loop.
+template <int MT, typename OutT, bool SWIGLU, int DEPTH>
 __global__ void __launch_bounds__(SM_WARPS * 32) gemm_smallm_kernel(const bf16* __restrict__ W, const bf16* __restrict__ X,
                                                                     OutT* __restrict__ Y, int M, int N, int K, int ldy,
                                                                     int n_tiles) {
     constexpr int SETS = SWIGLU ? 2 : 1;
-    __shared__ float part[SM_WARPS][SETS][MT][128];
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    constexpr int SLOTS = SETS * 2 + MT;     // 16-byte pieces per chunk and thread: weight rows, then activation rows
+    uint4* ring = reinterpret_cast<uint4*>(smem_raw);                        // [DEPTH][SLOTS][threads]
+    float* part = reinterpret_cast<float*>(ring + DEPTH * SLOTS * SM_WARPS * 32);      // [warps][SETS][MT][128]
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
     const int chunks = (K + 31) / 32;
-    const uint4 zero = make_uint4(0, 0, 0, 0);
+    const int my_chunks = chunks > warp ? (chunks - warp + SM_WARPS - 1) / SM_WARPS : 0;   // chunks warp, warp + 8, ...
+    auto slot = [&](int d, int s, int h) -> uint4* { return ring + (d * SLOTS + s * 2 + h) * (SM_WARPS * 32) + tid; };
+    auto xslot = [&](int d, int j) -> uint4* { return ring + (d * SLOTS + SETS * 2 + j) * (SM_WARPS * 32) + tid; };
 
+    pdl_launch_dependents();
+    bool first_tile = true;
     for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
         const int n0 = tile * 16;
         const bf16* wrow[SETS][2];
@@ -52,6 +71,33 @@ __global__ void __launch_bounds__(SM_WARPS * 32) gemm_smallm_kernel(const bf16* 
                 wok[s][h] = n < N;
                 wrow[s][h] = W + (int64_t)(s * N + (wok[s][h] ? n : 0)) * K;
             }
+        auto issue_w = [&](int i) {
+            if (i < my_chunks) {
+                const int k = (warp + i * SM_WARPS) * 32 + 8 * t;
+                const bool kok = k < K;
+#pragma unroll
+                for (int s = 0; s < SETS; ++s)
+#pragma unroll
+                    for (int h = 0; h < 2; ++h)
+                        cp_async16_zfill(slot(i % DEPTH, s, h), wrow[s][h] + (kok ? k : 0), (kok && wok[s][h]) ? 16 : 0);
+            }
+        };
+        auto issue_x = [&](int i) {
+            if (i < my_chunks) {
+                const int k = (warp + i * SM_WARPS) * 32 + 8 * t;
+#pragma unroll
+                for (int j = 0; j < MT; ++j) {
+                    const int m = 8 * j + g;
+                    const bool ok = k < K && m < M;
+                    cp_async16_zfill(xslot(i % DEPTH, j), X + (ok ? (int64_t)m * K + k : 0), ok ? 16 : 0);
+                }
+            }
+            cp_commit();
+        };
+        auto issue = [&](int i) {
+            issue_w(i);
+            issue_x(i);
+        };
         float acc[SETS][MT][4];
 #pragma unroll
         for (int s = 0; s < SETS; ++s)
@@ -60,44 +106,47 @@ __global__ void __launch_bounds__(SM_WARPS * 32) gemm_smallm_kernel(const bf16* 
 #pragma unroll
                 for (int i = 0; i < 4; ++i) acc[s][j][i] = 0.f;
 
-        for (int c0 = warp; c0 < chunks; c0 += SM_WARPS * SM_UNROLL) {
-            uint4 a[SM_UNROLL][SETS][2], b[SM_UNROLL][MT];
+        // The weights do not depend on the kernel before this one: the first chunks of the first
+        // tile are requested before waiting for it (their copies then all belong to the first
+        // commit group, which is harmless: that group is waited for first).
 #pragma unroll
-            for (int u = 0; u < SM_UNROLL; ++u) {
-                const int k = (c0 + u * SM_WARPS) * 32 + 8 * t;
-                const bool kok = k < K;
+        for (int i = 0; i < DEPTH - 1; ++i) issue_w(i);
+        if (first_tile) {
+            pdl_wait();
+            first_tile = false;
+        }
 #pragma unroll
-                for (int s = 0; s < SETS; ++s)
+        for (int i = 0; i < DEPTH - 1; ++i) issue_x(i);
+        for (int i = 0; i < my_chunks; ++i) {
+            issue(i + DEPTH - 1);
+            cp_wait<DEPTH - 1>();
+            uint4 b[MT];
 #pragma unroll
-                    for (int h = 0; h < 2; ++h) a[u][s][h] = (kok && wok[s][h]) ? ld_stream16(wrow[s][h] + k) : zero;
+            for (int j = 0; j < MT; ++j) b[j] = *xslot(i % DEPTH, j);
+#pragma unroll
+            for (int s = 0; s < SETS; ++s) {
+                const uint4 a0 = *slot(i % DEPTH, s, 0), a1 = *slot(i % DEPTH, s, 1);
 #pragma unroll
                 for (int j = 0; j < MT; ++j) {
-                    const int m = 8 * j + g;
-                    b[u][j] = (kok && m < M) ? __ldg(reinterpret_cast<const uint4*>(X + (int64_t)m * K + k)) : zero;
+                    mma16816(acc[s][j], a0.x, a1.x, a0.y, a1.y, b[j].x, b[j].y);
+                    mma16816(acc[s][j], a0.z, a1.z, a0.w, a1.w, b[j].z, b[j].w);
                 }
             }
-#pragma unroll
-            for (int u = 0; u < SM_UNROLL; ++u)
-#pragma unroll
-                for (int s = 0; s < SETS; ++s)
-#pragma unroll
-                    for (int j = 0; j < MT; ++j) {
-                        mma16816(acc[s][j], a[u][s][0].x, a[u][s][1].x, a[u][s][0].y, a[u][s][1].y, b[u][j].x, b[u][j].y);
-                        mma16816(acc[s][j], a[u][s][0].z, a[u][s][1].z, a[u][s][0].w, a[u][s][1].w, b[u][j].z, b[u][j].w);
-                    }
         }
+        cp_wait<0>();
         // partials: part[warp][set][j][row * 8 + col], row = weight row in the tile, col = m in the tile
 #pragma unroll
         for (int s = 0; s < SETS; ++s)
 #pragma unroll
             for (int j = 0; j < MT; ++j) {
-                part[warp][s][j][g * 8 + 2 * t] = acc[s][j][0];
-                part[warp][s][j][g * 8 + 2 * t + 1] = acc[s][j][1];
-                part[warp][s][j][(g + 8) * 8 + 2 * t] = acc[s][j][2];
-                part[warp][s][j][(g + 8) * 8 + 2 * t + 1] = acc[s][j][3];
+                float* p = part + ((warp * SETS + s) * MT + j) * 128;
+                p[g * 8 + 2 * t] = acc[s][j][0];
+                p[g * 8 + 2 * t + 1] = acc[s][j][1];
+                p[(g + 8) * 8 + 2 * t] = acc[s][j][2];
+                p[(g + 8) * 8 + 2 * t + 1] = acc[s][j][3];
             }
         __syncthreads();
-        for (int e = threadIdx.x; e < MT * 128; e += SM_WARPS * 32) {
+        for (int e = tid; e < MT * 128; e += SM_WARPS * 32) {
             const int j = e / 128, r = e % 128;
             const int row = r % 16, col = r / 16;      // consecutive threads -> consecutive n
             const int n = n0 + row, m = 8 * j + col;
@@ -106,7 +155,7 @@ __global__ void __launch_bounds__(SM_WARPS * 32) gemm_smallm_kernel(const bf16* 
             for (int s = 0; s < SETS; ++s) {
                 float sum = 0.f;
 #pragma unroll
-                for (int w = 0; w < SM_WARPS; ++w) sum += part[w][s][j][row * 8 + col];
+                for (int w = 0; w < SM_WARPS; ++w) sum += part[((w * SETS + s) * MT + j) * 128 + row * 8 + col];
                 v[s] = sum;
             }
             if (n < N && m < M) {
@@ -121,9 +170,28 @@ __global__ void __launch_bounds__(SM_WARPS * 32) gemm_smallm_kernel(const bf16* 
 
 template <int MT, typename OutT, bool SWIGLU>
 static int launch_smallm(const bf16* W, const bf16* X, OutT* Y, int M, int N, int K, int ldy, int sms, cudaStream_t stream) {
+    constexpr int SETS = SWIGLU ? 2 : 1;
+    constexpr int SLOTS = SETS * 2 + MT;
+    constexpr int DEPTH = SWIGLU ? 5 : (MT == 1 ? 6 : 4);
+    constexpr int SMEM = DEPTH * SLOTS * SM_WARPS * 32 * 16 + SM_WARPS * SETS * MT * 128 * 4;
     const int n_tiles = (N + 15) / 16;
-    int grid = n_tiles < sms * 4 ? n_tiles : sms * 4;
-    gemm_smallm_kernel<MT, OutT, SWIGLU><<<grid, SM_WARPS * 32, 0, stream>>>(W, X, Y, M, N, K, ldy, n_tiles);
+    static int per_sm = 0;     // blocks of this variant that fit on one SM
+    if (per_sm == 0) {
+        auto kernel = gemm_smallm_kernel<MT, OutT, SWIGLU, DEPTH>;
+        cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+        if (e != cudaSuccess) {
+            x0ne_set_error("gemm_smallm: cannot set %d bytes of shared memory: %s", SMEM, cudaGetErrorString(e));
+            return (int)e;
+        }
+        int n = 0;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, SM_WARPS * 32, SMEM) != cudaSuccess || n < 1) n = 1;
+        per_sm = n;
+    }
+    const int resident = sms * per_sm;
+    // All tiles at once if they fit; else one block per resident slot, each walking its share of tiles.
+    const int grid = n_tiles < resident ? n_tiles : resident;
+    x0ne_launch(gemm_smallm_kernel<MT, OutT, SWIGLU, DEPTH>, dim3(grid), dim3(SM_WARPS * 32), SMEM, stream, W, X, Y, M, N, K, ldy, n_tiles);
     X0NE_LAUNCH_CHECK();
 }
 

@@ -22,6 +22,7 @@ __global__ void __launch_bounds__(256) gemm_f32_nt_kernel(const float* __restric
                                                            int ldw, int ldc) {
     __shared__ float As[BK][BM + 4];
     __shared__ float Ws[BK][BN + 4];
+    pdl_prologue();
     const int tid = threadIdx.x;
     const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
     const int tx = tid % 16, ty = tid / 16;  // tx: 16 column groups of 4, ty: 16 row groups of 8
@@ -82,6 +83,6 @@ X0NE_API int x0ne_gemm_f32_nt(const float* A, const float* W, float* C, int M, i
     if (M == 0) return 0;
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
     X0NE_REQUIRE(grid.y <= 65535, "gemm_f32: M %d needs more than 65535 row tiles", M);
-    gemm_f32_nt_kernel<<<grid, 256, 0, stream>>>(A, W, C, M, N, K, lda, ldw, ldc);
+    x0ne_launch(gemm_f32_nt_kernel, dim3(grid), dim3(256), 0, stream, A, W, C, M, N, K, lda, ldw, ldc);
     X0NE_LAUNCH_CHECK();
 }

@@ -235,8 +235,8 @@ def attention_prefill_bf16(q: torch.Tensor, out: torch.Tensor, cache: PagedCache
                            tile_row0: torch.Tensor, n_tiles: int, seq_first_row: torch.Tensor,
                            seq_slot: torch.Tensor, seq_pos0: torch.Tensor, q_heads: int, scale: float,
                            window: int = 0) -> None:
-    """Causal flash attention of a pass whose sequences bring several rows; a tile is up to 64
-    consecutive rows of one sequence."""
+    """Causal flash attention of a pass whose sequences bring several rows; a tile is up to
+    `attention_prefill_tile_rows()` consecutive rows of one sequence."""
     lib = _lib("fast")
     _need(q, torch.bfloat16, "q")
     _need(out, torch.bfloat16, "attention output")
@@ -253,6 +253,15 @@ def attention_prefill_bf16(q: torch.Tensor, out: torch.Tensor, cache: PagedCache
             _ptr(q), _ptr(out), cache, c_void_p(tile_seq.data_ptr() + 4 * first),
             c_void_p(tile_row0.data_ptr() + 4 * first), c_int(n), _ptr(seq_first_row), _ptr(seq_slot), _ptr(seq_pos0),
             c_int(q_heads), c_float(scale), c_int(window), _stream()), "attention_prefill_bf16")
+
+
+def attention_prefill_tile_rows() -> int:
+    """Rows of one tile of the prefill attention kernel (callers build their tile tables with it)."""
+    return int(_lib("fast").x0ne_attention_prefill_tile_rows())
+
+
+def attention_decode_blocks_per_sm() -> int:
+    return int(_lib("fast").x0ne_attention_decode_blocks_per_sm())
 
 
 def attention_decode_scratch_bytes(n_rows: int, q_heads: int, kv_heads: int, head_dim: int, splits: int) -> int:

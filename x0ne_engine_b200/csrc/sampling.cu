@@ -113,6 +113,7 @@ __global__ void __launch_bounds__(SB) sample_kernel(SampleIO io) {
     __shared__ int s_bi[32];
     __shared__ int s_pick;
     const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    pdl_prologue();
     if (io.finished && io.finished[row]) {
         if (tid == 0) io.out_token[row] = -2;
         return;
@@ -297,6 +298,6 @@ X0NE_API int x0ne_sample(SampleIO io, int n_rows, cudaStream_t stream) {
     X0NE_REQUIRE(io.logits && io.out_token, "sample: null logits or output");
     X0NE_REQUIRE(io.n_stop == 0 || io.stop_ids, "sample: %d stop ids but no list", io.n_stop);
     if (n_rows == 0) return 0;
-    sample_kernel<<<n_rows, SB, 0, stream>>>(io);
+    x0ne_launch(sample_kernel, dim3(n_rows), dim3(SB), 0, stream, io);
     X0NE_LAUNCH_CHECK();
 }

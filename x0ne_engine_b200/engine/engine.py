@@ -52,7 +52,7 @@ class StepContext:
     seq_first_row: Optional[torch.Tensor] = None   # int32 [n_seqs + 1]
     seq_slot: Optional[torch.Tensor] = None        # int32 [n_seqs]
     seq_pos0: Optional[torch.Tensor] = None        # int32 [n_seqs]: position of the sequence's first row
-    n_tiles: int = 0                               # tiles of up to 64 consecutive rows of one sequence
+    n_tiles: int = 0                               # tiles of consecutive rows of one sequence (prefill attention)
     tile_seq: Optional[torch.Tensor] = None        # int32 [n_tiles]
     tile_row0: Optional[torch.Tensor] = None       # int32 [n_tiles]
     sm_count: int = 148
@@ -92,6 +92,11 @@ class Engine:
         self._stage_at = 0
         self._seq_dev = torch.zeros((3, self.max_step_tokens + 1), dtype=torch.int32, device=self.device)
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
+        if self.dtype == torch.bfloat16:
+            from ..csrc import ops
+            self._tile_rows = ops.attention_prefill_tile_rows()
+        else:
+            self._tile_rows = 64
 
     # ------------------------------------------------------------------ construction
     @classmethod
@@ -218,12 +223,13 @@ class Engine:
         seq_ids = [i for i in range(len(slots)) if first_row[i] < r1 and first_row[i + 1] > r0]
         sfirst = np.asarray([max(first_row[i], r0) - r0 for i in seq_ids] + [r1 - r0], dtype=np.int32)
         counts = np.diff(sfirst)
-        tiles_per = (counts + 63) // 64
+        tr = self._tile_rows
+        tiles_per = (counts + tr - 1) // tr
         n_tiles = int(tiles_per.sum())
         tile_seq = np.repeat(np.arange(len(seq_ids), dtype=np.int32), tiles_per)
         tile_k = np.arange(n_tiles, dtype=np.int32) - np.repeat(np.cumsum(tiles_per) - tiles_per, tiles_per).astype(np.int32)
         stage[4, :n_tiles] = torch.from_numpy(tile_seq)
-        stage[5, :n_tiles] = torch.from_numpy(sfirst[tile_seq] + 64 * tile_k)
+        stage[5, :n_tiles] = torch.from_numpy(sfirst[tile_seq] + tr * tile_k)
         self._meta_dev.copy_(stage, non_blocking=True)
         ev = torch.cuda.Event()
         ev.record()

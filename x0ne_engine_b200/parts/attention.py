@@ -33,12 +33,11 @@ def run_attention(ctx, q, out, view, n_rows, q_heads, scale, window):
 
 def decode_splits(ctx, n_rows: int, kv_heads: int, q_heads: int) -> int:
     """Into how many blocks each (sequence, kv head) of a decode pass is split: as many as fit on
-    the GPU at once (two blocks per SM), so that the launch is one wave, and no more than the
-    longest context has pages."""
+    the GPU at once, so that the launch is one wave, and no more than the longest context has pages."""
     group_chunks = (q_heads // kv_heads + 15) // 16
     blocks = max(1, n_rows * kv_heads * group_chunks)
     pages = max(1, (ctx.max_context + 63) // 64)
-    return int(max(1, min(pages, (2 * ctx.sm_count) // blocks, 32)))
+    return int(max(1, min(pages, (ops.attention_decode_blocks_per_sm() * ctx.sm_count) // blocks, 32)))
 
 
 class GQAttention(Mixer):
