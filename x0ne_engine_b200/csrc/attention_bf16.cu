@@ -323,7 +323,8 @@ __global__ void __launch_bounds__(128) attention_prefill_kernel(PrefillArgs a, P
 // Decode: one query row per sequence.  grid (splits, kv_heads * group_chunks, sequences); a block
 // serves up to 16 q heads of one kv head (they are the 16 rows of the MMA tile) over its share of
 // the sequence's pages.  The 4 warps take 16 keys each of every 64-key page, each with its own
-// running (m, l, o); they are merged in shared memory at the end, and the blocks of one
+// running (m, l, o) and its own cp.async ring (no block barrier in the loop); they are merged in
+// shared memory at the end, and the blocks of one
 // (sequence, kv head) are merged by whichever of them finishes last, in the fixed order of the
 // splits (the last-arriver scheme of x0ne-core/kernels/cuda/attention.cu:439-455: nobody waits).
 // ----------------------------------------------------------------------------------------
@@ -348,10 +349,12 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(DecodeArgs a, Pag
     extern __shared__ __align__(16) unsigned char smem_raw[];
     constexpr int LD = HD + PADE;
     bf16* qs = reinterpret_cast<bf16*>(smem_raw);   // [16][LD]
-    bf16* ks = qs + 16 * LD;                        // [STAGES][64][LD]
-    bf16* vs = ks + STAGES * 64 * LD;               // [STAGES][64][LD]
+    bf16* ks = qs + 16 * LD;                        // [4 warps][STAGES][K, V][16][LD]: each warp's own ring
     __shared__ int s_last;
-    pdl_prologue();
+    // What the kernel before this one (the q/k-norm + RoPE + cache write of this step) produced is q
+    // and the newest row of the cache.  Positions, slots, the page table and all older rows are
+    // older than that, so the first slices are requested before waiting for it.
+    pdl_launch_dependents();
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int split = blockIdx.x, b = blockIdx.z;
     const int G = a.q_heads / cache.kv_heads;
@@ -363,14 +366,6 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(DecodeArgs a, Pag
     const int q_dim = a.q_heads * HD;
 
     constexpr int CH = HD / 8;
-    for (int c = tid; c < 16 * CH; c += 128) {
-        const int r = c / CH, k = c % CH;
-        bf16* d = qs + r * LD + k * 8;
-        if (r < nheads)
-            cp_async16(d, a.q + (int64_t)b * q_dim + (head0 + r) * HD + k * 8);
-        else
-            *reinterpret_cast<uint4*>(d) = make_uint4(0, 0, 0, 0);
-    }
     const int j_lo = a.window > 0 ? max(0, pos - a.window + 1) : 0;
     const int pg_first = j_lo / PAGE, pg_count = pos / PAGE - pg_first + 1;
     const int p_lo = pg_first + (int)(((int64_t)pg_count * split) / a.splits);
@@ -398,16 +393,49 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(DecodeArgs a, Pag
         return pg < 0 ? nullptr : (const bf16*)cache.base + (int64_t)pg * cache.page_stride + head_off;
     };
 
-    // prologue: up to STAGES - 1 pages in flight
+    // Each warp streams its own 16 keys of every page (K and V rows 16 w .. 16 w + 15) through a
+    // private ring of STAGES slots: no block-wide barrier inside the loop, STAGES - 1 slices in flight.
+    bf16* wring = ks + warp * STAGES * 2 * 16 * LD;
+    auto load_slice = [&](int st, int i) {
+        const bf16* kp = tile_ptr(i);
+        bf16* kd = wring + (st * 2) * 16 * LD;
+        bf16* vd = kd + 16 * LD;
+        const int first_pos = (p_lo + i) * PAGE + warp * 16;
+#pragma unroll
+        for (int c = lane; c < 16 * CH; c += 32) {
+            const int r = c / CH, k = c % CH;
+            if (kp != nullptr && first_pos + r <= pos) {
+                const bf16* src = kp + (warp * 16 + r) * HD + k * 8;
+                cp_async16(kd + r * LD + k * 8, src);
+                cp_async16(vd + r * LD + k * 8, src + v_off);
+            } else {
+                *reinterpret_cast<uint4*>(kd + r * LD + k * 8) = make_uint4(0, 0, 0, 0);
+                *reinterpret_cast<uint4*>(vd + r * LD + k * 8) = make_uint4(0, 0, 0, 0);
+            }
+        }
+    };
+    bool waited = false;
 #pragma unroll
     for (int s = 0; s < STAGES - 1; ++s) {
         if (s < n_pages) {
-            const bf16* kp = tile_ptr(s);
-            load_page_tile<HD, 128>(ks + s * 64 * LD, kp, (p_lo + s) * PAGE, pos, tid);
-            load_page_tile<HD, 128>(vs + s * 64 * LD, kp ? kp + v_off : nullptr, (p_lo + s) * PAGE, pos, tid);
+            if (!waited && (p_lo + s + 1) * PAGE > pos) {    // the page that holds the newest row
+                pdl_wait();
+                waited = true;
+            }
+            load_slice(s, s);
         }
         cp_async_commit();
     }
+    if (!waited) pdl_wait();
+    for (int c = tid; c < 16 * CH; c += 128) {
+        const int r = c / CH, k = c % CH;
+        bf16* d = qs + r * LD + k * 8;
+        if (r < nheads)
+            cp_async16(d, a.q + (int64_t)b * q_dim + (head0 + r) * HD + k * 8);
+        else
+            *reinterpret_cast<uint4*>(d) = make_uint4(0, 0, 0, 0);
+    }
+    cp_async_commit();
     float o[HD / 8][4];
 #pragma unroll
     for (int n = 0; n < HD / 8; ++n)
@@ -417,45 +445,43 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(DecodeArgs a, Pag
     uint32_t qf[HD / 16][4];
 
     for (int it = 0; it < n_pages; ++it) {
-        cp_async_wait<STAGES - 2>();
-        __syncthreads();
         if (it == 0) {
+            cp_async_wait<0>();  // the first slice and q (q is the last group of the prologue)
+            __syncthreads();     // q was copied by all warps
 #pragma unroll
             for (int kk = 0; kk < HD / 16; ++kk) {
                 const int row = lane & 15, col = kk * 16 + ((lane >> 4) << 3);
                 ldsm_x4(qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3], qs + row * LD + col);
             }
+        } else {
+            cp_async_wait<STAGES - 2>();
+            __syncwarp();        // the slice was copied by all lanes of this warp; all have left the last one
         }
-        {   // refill the stage that was consumed in the previous iteration
+        {   // refill the slot that was consumed in the previous iteration
             const int nx = it + STAGES - 1;
-            if (nx < n_pages) {
-                const int st = nx % STAGES;
-                const bf16* kp = tile_ptr(nx);
-                load_page_tile<HD, 128>(ks + st * 64 * LD, kp, (p_lo + nx) * PAGE, pos, tid);
-                load_page_tile<HD, 128>(vs + st * 64 * LD, kp ? kp + v_off : nullptr, (p_lo + nx) * PAGE, pos, tid);
-            }
+            if (nx < n_pages) load_slice(nx % STAGES, nx);
             cp_async_commit();
         }
-        const int st = it % STAGES;
-        const int pg = p_lo + it;
-        const int key0 = warp * 16;
-        if (pg * PAGE + key0 <= pos) {
+        const bf16* kb = wring + ((it % STAGES) * 2) * 16 * LD;
+        const bf16* vb = kb + 16 * LD;
+        const int first_pos = (p_lo + it) * PAGE + warp * 16;
+        if (first_pos <= pos) {
             float s[2][4];
-            qk_tile<HD, 2>(s, qf, ks + st * 64 * LD, key0, lane);
-            const bool edge = (pg * PAGE + key0 + 15 > pos) || (a.window > 0 && pg * PAGE + key0 < j_lo);
+            qk_tile<HD, 2>(s, qf, kb, 0, lane);
+            const bool edge = (first_pos + 15 > pos) || (a.window > 0 && first_pos < j_lo);
 #pragma unroll
             for (int n = 0; n < 2; ++n)
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                     float v = s[n][i] * a.scale_log2;
                     if (edge) {
-                        const int j = pg * PAGE + key0 + n * 8 + ((lane & 3) << 1) + (i & 1);
+                        const int j = first_pos + n * 8 + ((lane & 3) << 1) + (i & 1);
                         if (j > pos || j < j_lo) v = -INFINITY;
                     }
                     s[n][i] = v;
                 }
             softmax_update<HD, 2>(s, o, m, l);
-            pv_tile<HD, 2>(o, s, vs + st * 64 * LD, key0, lane);
+            pv_tile<HD, 2>(o, s, vb, 0, lane);
         }
     }
     cp_async_wait<0>();
@@ -577,10 +603,10 @@ static int launch_prefill(const PrefillArgs& a, const PagedCache& cache, int n_t
     X0NE_LAUNCH_CHECK();
 }
 
-#define DECODE_STAGES 2
+#define DECODE_STAGES 3
 template <int HD>
 static int launch_decode(const DecodeArgs& a, const PagedCache& cache, int n_rows, cudaStream_t stream) {
-    size_t smem = (size_t)(16 + 2 * DECODE_STAGES * 64) * (HD + PADE) * sizeof(bf16);
+    size_t smem = (size_t)(16 + 4 * DECODE_STAGES * 2 * 16) * (HD + PADE) * sizeof(bf16);
     const size_t merge = (size_t)(4 * 16 * HD + 4 * 16 * 2) * sizeof(float);
     if (smem < 16 * (HD + PADE) * sizeof(bf16) + merge) smem = 16 * (HD + PADE) * sizeof(bf16) + merge;
     static bool configured = false;
@@ -641,7 +667,7 @@ X0NE_API int x0ne_attention_prefill_tile_rows() { return 64 * PREFILL_MT; }
 
 // Blocks of the decode kernel that fit on one SM at head_dim 128 (shared memory decides): callers
 // size `splits` so that a launch is one wave.
-X0NE_API int x0ne_attention_decode_blocks_per_sm() { return DECODE_STAGES == 2 ? 3 : 2; }
+X0NE_API int x0ne_attention_decode_blocks_per_sm() { return DECODE_STAGES <= 2 ? 3 : (DECODE_STAGES == 3 ? 2 : 1); }
 
 // Scratch the decode kernel needs for `n_rows` sequences with `splits` splits, in bytes:
 // partial outputs, partial (m, l), and the arrival counters (which must start at zero).
