@@ -125,6 +125,14 @@ def build(name: str, verbose: bool = True) -> str:
     if r.returncode != 0:
         raise BuildError(f"link of module '{name}' failed:\n{r.stdout}\n{r.stderr}")
     os.replace(tmp, out)
+    # libraries of older versions of this module's sources are of no use any more
+    prefix = f"libx0ne_{name}-"
+    for f in os.listdir(bdir):
+        if f.startswith(prefix) and f.endswith(".so") and os.path.join(bdir, f) != out:
+            try:
+                os.remove(os.path.join(bdir, f))
+            except OSError:
+                pass
     if verbose:
         _say(f"module '{name}' built in {time.time() - t0:.0f} s -> {out}")
     return out

@@ -331,7 +331,8 @@ __global__ void qk_norm_rope_kv_write_kernel(const T* __restrict__ qkv, const fl
                                              const float* __restrict__ inv_freq, int rot, T* __restrict__ q_out,
                                              PagedCache cache, const int32_t* __restrict__ row_slot,
                                              const int32_t* __restrict__ row_pos, int n_rows, int q_heads,
-                                             float eps, int write_kv) {
+                                             float eps, int write_kv, const float* __restrict__ rope_table,
+                                             int table_positions) {
     extern __shared__ float rope_cs[];          // [half] cosines, then [half] sines of this row's angles
     pdl_prologue();
     const int lane = threadIdx.x & 31;
@@ -340,37 +341,54 @@ __global__ void qk_norm_rope_kv_write_kernel(const T* __restrict__ qkv, const fl
     const int hd = cache.head_dim, half = rot >> 1;
     const int q_dim = q_heads * hd, kv_dim = cache.kv_heads * hd;
     const int pos = row_pos[row];
-    float* cs_tab = rope_cs;
-    float* sn_tab = rope_cs + half;
-    for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf((float)pos * inv_freq[i], &sn_tab[i], &cs_tab[i]);
-    __syncthreads();
-    for (int head = threadIdx.x >> 5; head < heads; head += blockDim.x >> 5)
+    // The row's cosines and sines: from the table the position encoding made at start-up
+    // ([position][cos..., sin...]) when it covers the position, else computed here.
+    const float* cs_tab;
+    const float* sn_tab;
+    if (rope_table != nullptr && pos >= 0 && pos < table_positions) {
+        cs_tab = rope_table + (int64_t)pos * rot;
+        sn_tab = cs_tab + half;
+    } else {
+        float* c = rope_cs;
+        float* sn = rope_cs + half;
+        for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf((float)pos * inv_freq[i], &sn[i], &c[i]);
+        __syncthreads();
+        cs_tab = c;
+        sn_tab = sn;
+    }
+    // blockIdx.y picks this block's share of the heads (one share when there are many rows)
+    const int per_block = (heads + gridDim.y - 1) / gridDim.y;
+    const int h_lo = blockIdx.y * per_block, h_hi = min(heads, h_lo + per_block);
+    for (int head = h_lo + (threadIdx.x >> 5); head < h_hi; head += blockDim.x >> 5)
         rope_one_head<T>(qkv, norm_q, norm_k, rot, q_out, cache, row_slot, row, pos, head, q_heads, eps, write_kv, cs_tab, sn_tab);
 }
 
 X0NE_API int x0ne_qk_norm_rope_kv_write(const void* qkv, int dt, const float* norm_q, const float* norm_k,
                                         const float* inv_freq, int rotary_dim, void* q_out, PagedCache cache,
                                         const int32_t* row_slot, const int32_t* row_pos, int n_rows, int q_heads,
-                                        float eps, int write_kv, cudaStream_t stream) {
+                                        float eps, int write_kv, const float* rope_table, int table_positions,
+                                        cudaStream_t stream) {
     X0NE_REQUIRE(n_rows >= 0 && q_heads > 0 && cache.kv_heads > 0 && cache.head_dim > 0, "rope: bad sizes");
     X0NE_REQUIRE(rotary_dim >= 0 && rotary_dim % 2 == 0 && rotary_dim <= cache.head_dim,
                  "rope: rotary_dim %d must be even and at most head_dim %d", rotary_dim, cache.head_dim);
     X0NE_REQUIRE(rotary_dim == 0 || inv_freq != nullptr, "rope: no inv_freq table");
     if (n_rows == 0) return 0;
-    // one block per row; few rows (decode): as many warps as heads, so no warp loops
+    // One block of 8 warps per row when there are many rows; with few rows (decode) the heads of a
+    // row are spread over several blocks of 4 warps, each of which computes the row's table itself.
     const int heads = q_heads + cache.kv_heads;
-    int warps = n_rows >= 64 ? 8 : (heads < 32 ? heads : 32);
-    X0NE_REQUIRE(n_rows <= 0x7fffffff, "rope: too many rows");
-    const unsigned grid = (unsigned)n_rows;
+    const int warps = n_rows >= 64 ? 8 : 4;
+    const int shares = n_rows >= 64 ? 1 : (heads + warps - 1) / warps;
+    X0NE_REQUIRE(n_rows <= 0x7fffffff && shares <= 65535, "rope: too many rows or heads");
+    const dim3 grid((unsigned)n_rows, (unsigned)shares);
     const size_t smem = (size_t)rotary_dim * sizeof(float);
     if (dt == X0NE_F32)
         x0ne_launch(qk_norm_rope_kv_write_kernel<float>, dim3(grid), dim3(warps * 32), smem, stream, 
             (const float*)qkv, norm_q, norm_k, inv_freq, rotary_dim, (float*)q_out, cache, row_slot, row_pos, n_rows,
-            q_heads, eps, write_kv);
+            q_heads, eps, write_kv, rope_table, table_positions);
     else if (dt == X0NE_BF16)
         x0ne_launch(qk_norm_rope_kv_write_kernel<bf16>, dim3(grid), dim3(warps * 32), smem, stream, 
             (const bf16*)qkv, norm_q, norm_k, inv_freq, rotary_dim, (bf16*)q_out, cache, row_slot, row_pos, n_rows,
-            q_heads, eps, write_kv);
+            q_heads, eps, write_kv, rope_table, table_positions);
     else
         X0NE_REQUIRE(false, "rope: unknown dtype tag %d", dt);
     X0NE_LAUNCH_CHECK();

@@ -130,7 +130,11 @@ def add_rmsnorm(resid: torch.Tensor, delta: Optional[torch.Tensor], weight: torc
 def qk_norm_rope_kv_write(qkv: torch.Tensor, q_norm: Optional[torch.Tensor], k_norm: Optional[torch.Tensor],
                           inv_freq: Optional[torch.Tensor], rotary_dim: int, q_out: torch.Tensor,
                           cache: PagedCacheArg, row_slot: torch.Tensor, row_pos: torch.Tensor, n_rows: int,
-                          q_heads: int, eps: float, write_kv: bool = True) -> None:
+                          q_heads: int, eps: float, write_kv: bool = True,
+                          rope_table: Optional[torch.Tensor] = None) -> None:
+    """q/k head norm, rotation and cache write.  `rope_table` (float32 [positions, rotary_dim]: each
+    row the cosines then the sines of position * inv_freq) replaces the on-the-fly sines and cosines
+    for the positions it covers."""
     lib = _lib("core")
     _need(qkv, qkv.dtype, "qkv")
     _need(q_out, qkv.dtype, "q output")
@@ -150,10 +154,16 @@ def qk_norm_rope_kv_write(qkv: torch.Tensor, q_norm: Optional[torch.Tensor], k_n
         _need(inv_freq, torch.float32, "inv_freq")
         if inv_freq.numel() * 2 != rotary_dim:
             raise KernelError("rope: inv_freq length is not rotary_dim / 2")
+    table_positions = 0
+    if rope_table is not None:
+        _need(rope_table, torch.float32, "rope table")
+        if rope_table.dim() != 2 or rope_table.shape[1] != rotary_dim:
+            raise KernelError("rope: the table is not [positions, rotary_dim]")
+        table_positions = rope_table.shape[0]
     _check(lib, lib.x0ne_qk_norm_rope_kv_write(
         _ptr(qkv), c_int(dtype_tag(qkv.dtype)), _ptr(q_norm), _ptr(k_norm), _ptr(inv_freq), c_int(rotary_dim),
         _ptr(q_out), cache, _ptr(row_slot), _ptr(row_pos), c_int(n_rows), c_int(q_heads), c_float(eps),
-        c_int(1 if write_kv else 0), _stream()), "qk_norm_rope_kv_write")
+        c_int(1 if write_kv else 0), _ptr(rope_table), c_int(table_positions), _stream()), "qk_norm_rope_kv_write")
 
 
 def attention_rows(q: torch.Tensor, out: torch.Tensor, cache: PagedCacheArg, row_slot: torch.Tensor,

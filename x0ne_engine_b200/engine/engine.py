@@ -75,10 +75,10 @@ class Engine:
         self.dtype = DTYPES[dtype]
         self.spec = spec
         torch.cuda.set_device(self.device)
-        self.model = CausalLM(spec, self.dtype, self.device)
+        self.max_seq_len = min(max_seq_len or spec.max_position_embeddings, spec.max_position_embeddings)
+        self.model = CausalLM(spec, self.dtype, self.device, max_positions=self.max_seq_len)
         self.model.bind(tensors)
         self.vocab_size = spec.vocab_size
-        self.max_seq_len = min(max_seq_len or spec.max_position_embeddings, spec.max_position_embeddings)
         needs = self.model.cache_needs()
         self.cache = SequenceCache(needs, [e.reads_cache_of for e in spec.run_order], max_tokens, self.max_seq_len,
                                    self.dtype, self.device, max_slots=max_slots)

@@ -48,12 +48,12 @@ def optional_duplicates_of_spec(spec: ModelSpec) -> Dict[str, str]:
 
 
 class CausalLM:
-    def __init__(self, spec: ModelSpec, dtype: torch.dtype, device):
+    def __init__(self, spec: ModelSpec, dtype: torch.dtype, device, max_positions: int = 0):
         spec.validate()
         self.spec = spec
         self.dtype = dtype
         self.device = torch.device(device)
-        env = P.BuildEnv(dtype=dtype, device=self.device)
+        env = P.BuildEnv(dtype=dtype, device=self.device, max_positions=max_positions)
         for name, ps in spec.positions.items():
             env.positions[name] = P.POSITIONS.get(ps.kind)(ps, env)
         self.env = env

@@ -109,10 +109,13 @@ class GQAttention(Mixer):
         view = ctx.cache.kv_view(entry if cache_entry is None else cache_entry)
         rot = self.position.rotary() if self.position is not None else None
         inv_freq, rot_dim = rot if rot is not None else (None, 0)
+        table = None
+        if rot is not None and self.env.max_positions and hasattr(self.position, "cos_sin_table"):
+            table = self.position.cos_sin_table(self.env.max_positions)
         ops.qk_norm_rope_kv_write(qkv, self.q_norm, self.k_norm, inv_freq, rot_dim, q, view, ctx.row_slot,
                                   ctx.row_pos, n_rows, self.q_heads,
                                   float(self.qk_norm_eps) if self.qk_norm_eps is not None else 0.0,
-                                  write_kv=write_cache)
+                                  write_kv=write_cache, rope_table=table)
         run_attention(ctx, q, att, view, n_rows, self.q_heads, self.scale, int(self.window or 0))
         self.o(att, out, n_rows)
         return out

@@ -51,6 +51,7 @@ class BuildEnv:
     dtype: torch.dtype
     device: torch.device
     positions: Dict[str, "PositionEncoding"] = field(default_factory=dict)
+    max_positions: int = 0          # longest sequence the engine will hold (for tables made at start-up)
 
 
 class Part:

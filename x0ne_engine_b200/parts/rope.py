@@ -29,10 +29,23 @@ class Rope(PositionEncoding):
         if self.rotary_dim % 2 or not 0 < self.rotary_dim <= self.head_dim:
             raise ValueError(f"rotary_dim {self.rotary_dim} must be even and at most head_dim {self.head_dim}")
         self.theta = float(spec["theta"])
-        self.table = torch.from_numpy(inv_freq_f32(self.rotary_dim, self.theta)).to(env.device)
+        self.inv_freq = inv_freq_f32(self.rotary_dim, self.theta)
+        self.table = torch.from_numpy(self.inv_freq).to(env.device)
+        self._cos_sin = None
 
     def rotary(self):
         return self.table, self.rotary_dim
+
+    def cos_sin_table(self, positions: int):
+        """float32 [positions, rotary_dim]: cos then sin of the float32 angle position * inv_freq[i],
+        made once on the host; mixers pass it to the fused kernel so that it reads two short rows
+        instead of computing the row's sines and cosines for every head."""
+        if self._cos_sin is None or self._cos_sin.shape[0] < positions:
+            pos = np.arange(positions, dtype=np.float32)[:, None]
+            ang = (pos * self.inv_freq[None, :]).astype(np.float32).astype(np.float64)
+            tab = np.concatenate([np.cos(ang), np.sin(ang)], axis=1).astype(np.float32)
+            self._cos_sin = torch.from_numpy(tab).to(self.env.device)
+        return self._cos_sin
 
 
 class NoPosition(PositionEncoding):
