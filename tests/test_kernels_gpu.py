@@ -150,8 +150,9 @@ def cache_rows(storage, table, slot, which, kv_head, n):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("q_heads,kv_heads,hd,rot", [(4, 2, 16, 16), (6, 2, 32, 32), (5, 1, 48, 48), (3, 3, 24, 12),
-                                                       (2, 1, 128, 128)])
-def test_qk_norm_rope_kv_write(dtype, q_heads, kv_heads, hd, rot):
+                                                       (2, 1, 128, 128), (5, 3, 64, 64), (3, 1, 256, 256)])
+@pytest.mark.parametrize("table_rows", [0, 100, 200])      # no table; one that ends before position 130; a full one
+def test_qk_norm_rope_kv_write(dtype, q_heads, kv_heads, hd, rot, table_rows):
     o = ops()
     n, eps, theta = 7, 1e-5, 50000.0
     storage, table, view = make_cache(kv_heads, hd, 8, 2, dtype, 3)
@@ -162,7 +163,11 @@ def test_qk_norm_rope_kv_write(dtype, q_heads, kv_heads, hd, rot):
     slots = torch.tensor([0, 0, 0, 1, 1, 1, 1], dtype=torch.int32, device=DEV)
     pos = torch.tensor([63, 64, 65, 0, 1, 130, 5], dtype=torch.int32, device=DEV)
     q_out = torch.empty((n, q_heads * hd), dtype=dtype, device=DEV)
-    o.qk_norm_rope_kv_write(qkv, qn, kn, inv, rot, q_out, view, slots, pos, n, q_heads, eps)
+    rope_tab = None
+    if table_rows:
+        ang = (np.arange(table_rows, dtype=np.float32)[:, None] * P.inv_freq(rot, theta)[None, :]).astype(np.float64)
+        rope_tab = torch.from_numpy(np.concatenate([np.cos(ang), np.sin(ang)], 1).astype(np.float32)).to(DEV)
+    o.qk_norm_rope_kv_write(qkv, qn, kn, inv, rot, q_out, view, slots, pos, n, q_heads, eps, rope_table=rope_tab)
 
     x = qkv.double().cpu().numpy()
     qd, kvd = q_heads * hd, kv_heads * hd

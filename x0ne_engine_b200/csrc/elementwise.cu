@@ -136,6 +136,11 @@ __device__ __forceinline__ void store2(float* p, const float* v) { *reinterpret_
 __device__ __forceinline__ void store2(bf16* p, const float* v) {
     *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(v[0], v[1]);
 }
+__device__ __forceinline__ void copy16(float* d, const float* s) {    // 8 values
+    reinterpret_cast<float4*>(d)[0] = reinterpret_cast<const float4*>(s)[0];
+    reinterpret_cast<float4*>(d)[1] = reinterpret_cast<const float4*>(s)[1];
+}
+__device__ __forceinline__ void copy16(bf16* d, const bf16* s) { *reinterpret_cast<uint4*>(d) = *reinterpret_cast<const uint4*>(s); }
 __device__ __forceinline__ void copy2(float* d, const float* s) { *reinterpret_cast<float2*>(d) = *reinterpret_cast<const float2*>(s); }
 __device__ __forceinline__ void copy2(bf16* d, const bf16* s) { *reinterpret_cast<uint32_t*>(d) = *reinterpret_cast<const uint32_t*>(s); }
 
@@ -211,8 +216,8 @@ X0NE_API int x0ne_add_rmsnorm(float* resid, const void* delta, const float* w, v
 
 // ----------------------------------------------------------------------------------------
 // Per-head RMSNorm of q and k (optional), rotate-half RoPE, and the K/V write into the
-// paged cache (x0ne-core/kernels/cuda/rope.cu:7-47).  One block per row: the row's sines and cosines
-// are computed once into shared memory, then one warp per head; heads
+// paged cache (x0ne-core/kernels/cuda/rope.cu:7-47).  One warp per (row, head); the row's sines and
+// cosines come from a table made at start-up (or are computed by the warp); heads
 // 0..q_heads-1 are q heads, the rest k heads, whose warps also copy the v head.
 //   scale = rsqrt(mean(x^2 over head_dim) + eps); n = x * scale * w
 //   angle = (float)pos * inv_freq[i]; (a, b) = (n[i], n[i + rot/2])
@@ -333,34 +338,128 @@ __global__ void qk_norm_rope_kv_write_kernel(const T* __restrict__ qkv, const fl
                                              const int32_t* __restrict__ row_pos, int n_rows, int q_heads,
                                              float eps, int write_kv, const float* __restrict__ rope_table,
                                              int table_positions) {
-    extern __shared__ float rope_cs[];          // [half] cosines, then [half] sines of this row's angles
+    extern __shared__ float rope_cs[];          // [warps][rot]: per warp, cosines then sines (only without a table)
     pdl_prologue();
-    const int lane = threadIdx.x & 31;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int heads = q_heads + cache.kv_heads;
-    const int row = blockIdx.x;
-    const int hd = cache.head_dim, half = rot >> 1;
-    const int q_dim = q_heads * hd, kv_dim = cache.kv_heads * hd;
+    const int64_t item = (int64_t)blockIdx.x * (blockDim.x >> 5) + warp;
+    if (item >= (int64_t)n_rows * heads) return;
+    const int row = (int)(item / heads), head = (int)(item % heads);
+    const int half = rot >> 1;
     const int pos = row_pos[row];
     // The row's cosines and sines: from the table the position encoding made at start-up
-    // ([position][cos..., sin...]) when it covers the position, else computed here.
+    // ([position][cos..., sin...]) when it covers the position, else computed here by the warp.
     const float* cs_tab;
     const float* sn_tab;
     if (rope_table != nullptr && pos >= 0 && pos < table_positions) {
         cs_tab = rope_table + (int64_t)pos * rot;
         sn_tab = cs_tab + half;
     } else {
-        float* c = rope_cs;
-        float* sn = rope_cs + half;
-        for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf((float)pos * inv_freq[i], &sn[i], &c[i]);
-        __syncthreads();
+        float* c = rope_cs + warp * rot;
+        float* sn = c + half;
+        for (int i = lane; i < half; i += 32) sincosf((float)pos * inv_freq[i], &sn[i], &c[i]);
+        __syncwarp();
         cs_tab = c;
         sn_tab = sn;
     }
-    // blockIdx.y picks this block's share of the heads (one share when there are many rows)
-    const int per_block = (heads + gridDim.y - 1) / gridDim.y;
-    const int h_lo = blockIdx.y * per_block, h_hi = min(heads, h_lo + per_block);
-    for (int head = h_lo + (threadIdx.x >> 5); head < h_hi; head += blockDim.x >> 5)
-        rope_one_head<T>(qkv, norm_q, norm_k, rot, q_out, cache, row_slot, row, pos, head, q_heads, eps, write_kv, cs_tab, sn_tab);
+    rope_one_head<T>(qkv, norm_q, norm_k, rot, q_out, cache, row_slot, row, pos, head, q_heads, eps, write_kv, cs_tab, sn_tab);
+}
+
+// The same for the common shapes (whole head rotated, head_dim 32, 64, 128 or 256, a table for the
+// row's position): head_dim / 16 lanes per head, each owning 8 consecutive values of the first half
+// and the 8 they pair with, moved 16 bytes at a time; a warp serves 512 / head_dim heads at once.
+template <typename T, int HD>
+__global__ void qk_norm_rope_kv_write_vec_kernel(const T* __restrict__ qkv, const float* __restrict__ norm_q,
+                                                 const float* __restrict__ norm_k, T* __restrict__ q_out,
+                                                 PagedCache cache, const int32_t* __restrict__ row_slot,
+                                                 const int32_t* __restrict__ row_pos, int n_rows, int q_heads, float eps,
+                                                 int write_kv, const float* __restrict__ rope_table, int table_positions,
+                                                 const float* __restrict__ inv_freq) {
+    constexpr int LPH = HD / 16;        // lanes per head
+    constexpr int HPW = 32 / LPH;       // heads per warp
+    constexpr int HALF = HD / 2;
+    pdl_prologue();
+    const int lane = threadIdx.x & 31;
+    const int heads = q_heads + cache.kv_heads;
+    const int64_t item = ((int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * HPW + lane / LPH;
+    const bool live = item < (int64_t)n_rows * heads;
+    const int row = live ? (int)(item / heads) : 0, head = live ? (int)(item % heads) : 0;
+    const int c = (lane % LPH) * 8;     // this lane's values: c .. c + 7 and HALF + c .. HALF + c + 7
+    const int q_dim = q_heads * HD, kv_dim = cache.kv_heads * HD;
+    const bool is_q = head < q_heads;
+    const int kh = is_q ? 0 : head - q_heads;
+    const T* src = qkv + (int64_t)row * (q_dim + 2 * kv_dim) + (is_q ? head * HD : q_dim + kh * HD);
+    const float* nw = is_q ? norm_q : norm_k;
+    const int pos = row_pos[row];
+    float a[8], b[8];
+    load8(src + c, a);
+    load8(src + HALF + c, b);
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) ss += a[k] * a[k] + b[k] * b[k];
+#pragma unroll
+    for (int o = 1; o < LPH; o <<= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if (!live || (!is_q && !write_kv)) return;
+    T* dst;
+    if (is_q) {
+        dst = q_out + (int64_t)row * q_dim + head * HD;
+    } else {
+        const int64_t off = cache_row_offset(cache, row_slot[row], pos, kh, 0);
+        if (off < 0) return;
+        dst = (T*)cache.base + off;
+    }
+    if (nw) {
+        const float scale = 1.0f / sqrtf(ss / (float)HD + eps);
+        float wa[8], wb[8];
+        load8(nw + c, wa);
+        load8(nw + HALF + c, wb);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            a[k] = a[k] * scale * wa[k];
+            b[k] = b[k] * scale * wb[k];
+        }
+    }
+    float cs[8], sn[8], ra[8], rb[8];
+    if (pos >= 0 && pos < table_positions) {
+        load8(rope_table + (int64_t)pos * HD + c, cs);
+        load8(rope_table + (int64_t)pos * HD + HALF + c, sn);
+    } else {        // a position the table does not cover
+#pragma unroll
+        for (int k = 0; k < 8; ++k) sincosf((float)pos * inv_freq[c + k], &sn[k], &cs[k]);
+    }
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        ra[k] = a[k] * cs[k] - b[k] * sn[k];
+        rb[k] = b[k] * cs[k] + a[k] * sn[k];
+    }
+    store8(dst + c, ra);
+    store8(dst + HALF + c, rb);
+    if (!is_q) {
+        const T* vs = src + kv_dim;
+        T* vd = dst + (int64_t)cache.kv_heads * cache.page_size * HD;
+        copy16(vd + c, vs + c);
+        copy16(vd + HALF + c, vs + HALF + c);
+    }
+}
+
+template <typename T>
+static int launch_rope_vec(const T* qkv, const float* norm_q, const float* norm_k, T* q_out, const PagedCache& cache,
+                           const int32_t* row_slot, const int32_t* row_pos, int n_rows, int q_heads, float eps, int write_kv,
+                           const float* rope_table, int table_positions, const float* inv_freq, cudaStream_t stream) {
+    const int hd = cache.head_dim;
+    const int64_t items = (int64_t)n_rows * (q_heads + cache.kv_heads);
+    const int hpw = 32 / (hd / 16), warps = 4;
+    const int64_t blocks = (items + (int64_t)hpw * warps - 1) / ((int64_t)hpw * warps);
+    X0NE_REQUIRE(blocks <= 0x7fffffff, "rope: too many rows");
+#define X0NE_ROPE_VEC(HDV)                                                                                             \
+    x0ne_launch(qk_norm_rope_kv_write_vec_kernel<T, HDV>, dim3((unsigned)blocks), dim3(warps * 32), 0, stream, qkv, norm_q, \
+                norm_k, q_out, cache, row_slot, row_pos, n_rows, q_heads, eps, write_kv, rope_table, table_positions, inv_freq)
+    if (hd == 32) X0NE_ROPE_VEC(32);
+    else if (hd == 64) X0NE_ROPE_VEC(64);
+    else if (hd == 128) X0NE_ROPE_VEC(128);
+    else X0NE_ROPE_VEC(256);
+#undef X0NE_ROPE_VEC
+    X0NE_LAUNCH_CHECK();
 }
 
 X0NE_API int x0ne_qk_norm_rope_kv_write(const void* qkv, int dt, const float* norm_q, const float* norm_k,
@@ -373,14 +472,24 @@ X0NE_API int x0ne_qk_norm_rope_kv_write(const void* qkv, int dt, const float* no
                  "rope: rotary_dim %d must be even and at most head_dim %d", rotary_dim, cache.head_dim);
     X0NE_REQUIRE(rotary_dim == 0 || inv_freq != nullptr, "rope: no inv_freq table");
     if (n_rows == 0) return 0;
-    // One block of 8 warps per row when there are many rows; with few rows (decode) the heads of a
-    // row are spread over several blocks of 4 warps, each of which computes the row's table itself.
+    const int hd_ = cache.head_dim;
+    if (rope_table != nullptr && rotary_dim == hd_ && (hd_ == 32 || hd_ == 64 || hd_ == 128 || hd_ == 256) &&
+        (((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)cache.base | (uintptr_t)rope_table | (uintptr_t)norm_q |
+          (uintptr_t)norm_k) & 15) == 0) {
+        if (dt == X0NE_F32)
+            return launch_rope_vec<float>((const float*)qkv, norm_q, norm_k, (float*)q_out, cache, row_slot, row_pos, n_rows,
+                                          q_heads, eps, write_kv, rope_table, table_positions, inv_freq, stream);
+        if (dt == X0NE_BF16)
+            return launch_rope_vec<bf16>((const bf16*)qkv, norm_q, norm_k, (bf16*)q_out, cache, row_slot, row_pos, n_rows,
+                                         q_heads, eps, write_kv, rope_table, table_positions, inv_freq, stream);
+    }
+    // one warp per (row, head)
     const int heads = q_heads + cache.kv_heads;
-    const int warps = n_rows >= 64 ? 8 : 4;
-    const int shares = n_rows >= 64 ? 1 : (heads + warps - 1) / warps;
-    X0NE_REQUIRE(n_rows <= 0x7fffffff && shares <= 65535, "rope: too many rows or heads");
-    const dim3 grid((unsigned)n_rows, (unsigned)shares);
-    const size_t smem = (size_t)rotary_dim * sizeof(float);
+    const int warps = 4;
+    const int64_t items = (int64_t)n_rows * heads;
+    X0NE_REQUIRE((items + warps - 1) / warps <= 0x7fffffff, "rope: too many rows");
+    const dim3 grid((unsigned)((items + warps - 1) / warps));
+    const size_t smem = (size_t)warps * rotary_dim * sizeof(float);
     if (dt == X0NE_F32)
         x0ne_launch(qk_norm_rope_kv_write_kernel<float>, dim3(grid), dim3(warps * 32), smem, stream, 
             (const float*)qkv, norm_q, norm_k, inv_freq, rotary_dim, (float*)q_out, cache, row_slot, row_pos, n_rows,
