@@ -246,3 +246,63 @@ def test_a_layer_can_read_another_layers_cache():
     got = eng.step([s], [ids[:5]], [list(range(5))]).cpu().numpy()
     got = np.concatenate([got] + [eng.step([s], [[t]]).cpu().numpy() for t in ids[5:]])
     assert np.abs(got - want).max() / np.abs(want).max() < 1e-4
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_model_with_a_windowed_layer_has_two_cache_groups_and_matches_the_plain_run(dtype):
+    """Layer 1 of a toy two-layer model sees only the last 40 keys.  Its keys and values live in a
+    group of their own, a ring of a few pages, while layer 0 keeps everything.  A 300-token sequence
+    laps that ring several times; the engine must cut the prompt into passes the ring can take and
+    still give the plain implementation's logits, whole and token by token."""
+    import dataclasses
+    from x0ne_engine_b200 import Engine, Qwen3Config
+    from x0ne_engine_b200.config import PartSpec
+    from x0ne_engine_b200.engine import tensor_needs_of_spec
+    from x0ne_engine_b200.weights import RandomInit, make_tensor
+    window = 40
+    cfg = Qwen3Config(hidden_size=64, intermediate_size=96, num_hidden_layers=2, num_attention_heads=4,
+                      num_key_value_heads=2, head_dim=16, vocab_size=90, max_position_embeddings=512,
+                      rms_norm_eps=1e-6, rope_theta=1e4, tie_word_embeddings=True, dtype=dtype)
+    spec = cfg.to_spec()
+    l1 = spec.layers[1]
+    l1 = dataclasses.replace(l1, mixer=PartSpec(l1.mixer.kind, {**l1.mixer.params, "window": window}))
+    spec = dataclasses.replace(spec, layers=(spec.layers[0], l1))
+    tdt = torch.float32 if dtype == "float32" else torch.bfloat16
+    init = RandomInit(seed=11, linear_std=0.1, norm_jitter=0.1)
+    cpu = {n.name: make_tensor(n, init, tdt, "cpu") for n in tensor_needs_of_spec(spec)}
+    from x0ne_engine_b200.weights.loader import held_dtype
+    dev = {n.name: cpu[n.name].to(DEV).to(held_dtype(n, tdt, tdt)) for n in tensor_needs_of_spec(spec)}
+    eng = Engine(spec, dev, dtype, DEV, max_tokens=1024)
+    assert len(eng.cache.groups) == 2
+    full, win = sorted(eng.cache.groups, key=lambda g: g.need.window is not None)
+    assert full.need.window is None and win.need.window == window and win.ring_pages < full.ring_pages
+    assert eng.cache.max_chunk <= 64
+
+    w = {k: v.double().numpy() for k, v in cpu.items()}
+    pc = dict(q_heads=4, kv_heads=2, head_dim=16, eps=1e-6, theta=1e4)
+    ids = np.random.default_rng(3).integers(0, 90, 300).tolist()
+    pos = np.arange(len(ids))
+    x = w["model.embed_tokens.weight"][ids]
+    for l, win_l in ((0, None), (1, window)):
+        p = f"model.layers.{l}."
+        x = x + P.attention_block(P.rmsnorm(x, w[p + "input_layernorm.weight"], 1e-6), w, p + "self_attn.", pc, pos,
+                                  window=win_l)
+        x = x + P.swiglu_mlp(P.rmsnorm(x, w[p + "post_attention_layernorm.weight"], 1e-6), w, p + "mlp.")
+    want = P.rmsnorm(x, w["model.norm.weight"], 1e-6) @ w["model.embed_tokens.weight"].T
+
+    def close(got, ref, what):
+        err = np.max(np.abs(got - ref) / np.max(np.abs(ref), axis=-1, keepdims=True))
+        assert err <= (1e-4 if dtype == "float32" else 0.05), f"{what}: {err:.3e}"
+
+    s = eng.new_sequence()
+    got = eng.step([s], [ids], [list(range(len(ids)))]).cpu().numpy()
+    close(got, want, "whole")
+    assert len(win.pages_of[s]) == win.ring_pages and len(full.pages_of[s]) == 5
+    eng.free_sequence(s)
+    s = eng.new_sequence()
+    rows = [eng.step([s], [ids[:230]], [[229]]).cpu().numpy()[0]]
+    rows += [eng.step([s], [[t]]).cpu().numpy()[0] for t in ids[230:]]
+    eng.free_sequence(s)
+    close(np.stack(rows), want[229:], "token by token")
+    if dtype == "float32":
+        assert np.array_equal(np.stack(rows), got[229:])
