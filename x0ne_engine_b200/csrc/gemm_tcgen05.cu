@@ -1,0 +1,317 @@
+// y[M,N] = x[M,K] W[N,K]^T for bfloat16 on the 5th-generation tensor cores: tcgen05.mma with the
+// accumulator in tensor memory, operands brought to shared memory by TMA, an mbarrier pipeline
+// between a copy thread, an MMA thread and four epilogue warps.  For passes with many rows
+// (prefill); the library engine gives these products to cublasGemmEx
+// (x0ne-core/runtime/src/gpu.rs:1098-1149).
+//
+// One block computes one 128 x 256 tile of y:
+//   * warp 0, one thread: for every 64-wide slice of K, waits until the stage is free, then issues
+//     two TMA tile loads (x: 128 rows x 128 bytes, W: 256 rows x 128 bytes, 128-byte swizzle) that
+//     complete on the stage's "full" barrier.  Rows or k values past the matrices read as zeros.
+//   * warp 1, one thread: waits for "full", issues four tcgen05.mma (M 128, N 256, K 16) whose
+//     shared-memory descriptors step 32 bytes through the swizzled slice, then tcgen05.commit to the
+//     stage's "empty" barrier (the stage is free when those MMAs are done); after the last slice,
+//     commits to the "accumulator ready" barrier.
+//   * warps 2-5: wait for it, read their 32 rows of the accumulator with tcgen05.ld, convert, store.
+// With SwiGLU the W tile is 128 gate rows and the 128 up rows that pair with them, the two halves
+// accumulate side by side, and the epilogue writes silu(gate) * up (x0ne-core/kernels/cuda/
+// swiglu.cu:5-11 without the intermediate bfloat16 rounding).
+//
+// No TMA multicast is used.  Every barrier wait is bounded (about a second); when one runs out the
+// kernel records where in `status`, skips the rest, still frees its tensor memory, and returns.
+#include <cuda.h>
+
+#include "common.cuh"
+
+#define TC_BM 128
+#define TC_BK 64
+#define TC_STAGES 4
+#define TC_THREADS 192
+#define TC_TMEM_COLS 256
+#define TC_WAIT_CYCLES (2000000000ll)
+
+__device__ __forceinline__ uint32_t tc_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(tc_smem(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(tc_smem(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(tc_smem(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Waits for the barrier's phase of the given parity, at most about a second.  On a timeout writes
+// `code` to *status (if it is still 0) and returns false.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int code) {
+    const long long start = clock64();
+    while (!mbar_try_wait(bar, parity)) {
+        if (clock64() - start > TC_WAIT_CYCLES) {
+            atomicCAS(status, 0, code);
+            return false;
+        }
+    }
+    return true;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(tc_smem(dst)), "l"(map), "r"(x), "r"(y), "r"(tc_smem(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a K-major tile with 128-byte swizzle: rows of 128 bytes,
+// 8-row groups 1024 bytes apart (stride offset 64 in 16-byte units), leading offset 1, version 1.
+__device__ __forceinline__ uint64_t tc_desc(uint32_t smem_addr) {
+    const uint32_t lo = ((smem_addr >> 4) & 0x3FFFu) | (1u << 16);
+    const uint32_t hi = 64u | (1u << 14) | (2u << 29);
+    return ((uint64_t)hi << 32) | lo;
+}
+__device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(tc_smem(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, float* v) {
+    uint32_t r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+__device__ __forceinline__ void tc_store8(float* p, const float* v) {
+    reinterpret_cast<float4*>(p)[0] = make_float4(v[0], v[1], v[2], v[3]);
+    reinterpret_cast<float4*>(p)[1] = make_float4(v[4], v[5], v[6], v[7]);
+}
+__device__ __forceinline__ void tc_store8(bf16* p, const float* v) {
+    uint4 u;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+    *reinterpret_cast<uint4*>(p) = u;
+}
+
+struct TcShared {
+    uint64_t full[TC_STAGES];
+    uint64_t empty[TC_STAGES];
+    uint64_t accum;
+    uint32_t tmem_base;
+    int failed;
+};
+
+// SWIGLU: W is the packed [gate; up] weight of 2 * N rows; the block's W tile is gate rows
+// n0 .. n0 + 127 and up rows N + n0 .. N + n0 + 127, and y has N columns.
+template <bool SWIGLU, typename OutT>
+__global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x,
+                                                             const __grid_constant__ CUtensorMap map_w, OutT* __restrict__ Y,
+                                                             int M, int N, int K, int ldy, int* status) {
+    extern __shared__ unsigned char tc_raw[];
+    // tiles need 1024-byte alignment for the 128-byte swizzle
+    unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(tc_raw) + 1023) & ~(uintptr_t)1023);
+    constexpr int A_BYTES = TC_BM * 128, B_BYTES = 256 * 128, STAGE_BYTES = A_BYTES + B_BYTES;
+    TcShared* sh = reinterpret_cast<TcShared*>(base + TC_STAGES * STAGE_BYTES);
+    constexpr int BN = SWIGLU ? 128 : 256;      // columns of y per block
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m0 = blockIdx.y * TC_BM, n0 = blockIdx.x * BN;
+    const int k_blocks = (K + TC_BK - 1) / TC_BK;
+
+    pdl_launch_dependents();
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < TC_STAGES; ++s) {
+            mbar_init(&sh->full[s], 1);
+            mbar_init(&sh->empty[s], 1);
+        }
+        mbar_init(&sh->accum, 1);
+        sh->failed = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tc_smem(&sh->tmem_base)),
+                     "r"(TC_TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = sh->tmem_base;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            pdl_wait();      // x was written by the kernel before this one
+            for (int kb = 0; kb < k_blocks; ++kb) {
+                const int s = kb % TC_STAGES;
+                if (kb >= TC_STAGES && !mbar_wait(&sh->empty[s], ((kb / TC_STAGES) - 1) & 1, status, 1)) {
+                    sh->failed = 1;
+                    break;
+                }
+                unsigned char* a = base + s * STAGE_BYTES;
+                unsigned char* b = a + A_BYTES;
+                mbar_expect_tx(&sh->full[s], STAGE_BYTES);
+                tma_load_2d(a, &map_x, kb * TC_BK, m0, &sh->full[s]);
+                if (SWIGLU) {
+                    tma_load_2d(b, &map_w, kb * TC_BK, n0, &sh->full[s]);
+                    tma_load_2d(b + 128 * 128, &map_w, kb * TC_BK, N + n0, &sh->full[s]);
+                } else {
+                    tma_load_2d(b, &map_w, kb * TC_BK, n0, &sh->full[s]);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // instruction descriptor: f32 accumulate, bf16 x bf16, both K-major, M = 128
+            const uint32_t idesc_n = SWIGLU ? 128u : 256u;
+            const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((idesc_n >> 3) << 17) | ((128u >> 4) << 24);
+            bool ok = true;
+            for (int kb = 0; kb < k_blocks && ok; ++kb) {
+                const int s = kb % TC_STAGES;
+                if (!mbar_wait(&sh->full[s], (kb / TC_STAGES) & 1, status, 2)) {
+                    sh->failed = 1;
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t a = tc_smem(base + s * STAGE_BYTES), b = a + A_BYTES;
+#pragma unroll
+                for (int k = 0; k < TC_BK / 16; ++k) {
+                    const uint32_t acc = (kb > 0 || k > 0) ? 1u : 0u;
+                    if (SWIGLU) {
+                        tc_mma(tmem, tc_desc(a + k * 32), tc_desc(b + k * 32), idesc, acc);
+                        tc_mma(tmem + 128, tc_desc(a + k * 32), tc_desc(b + 128 * 128 + k * 32), idesc, acc);
+                    } else {
+                        tc_mma(tmem, tc_desc(a + k * 32), tc_desc(b + k * 32), idesc, acc);
+                    }
+                }
+                tc_commit(&sh->empty[s]);      // arrives when the MMAs above have read the stage
+            }
+            tc_commit(&sh->accum);             // arrives when every MMA is done (at once if none was issued)
+        }
+    } else {
+        // epilogue: warp w reads tensor-memory lanes 32 (w % 4) .. 32 (w % 4) + 31 = rows of the tile
+        const int quarter = warp & 3;
+        const int m = m0 + quarter * 32 + lane;
+        const bool ok = mbar_wait(&sh->accum, 0, status, 3);
+        tc_fence_after();
+        if (ok && !sh->failed) {
+            const uint32_t trow = tmem + ((uint32_t)(quarter * 32) << 16);
+#pragma unroll 1
+            for (int c = 0; c < 128 / 32 * (SWIGLU ? 1 : 2); ++c) {
+                float v[32];
+                tc_ld32(trow + c * 32, v);
+                if (SWIGLU) {
+                    float u[32];
+                    tc_ld32(trow + 128 + c * 32, u);
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) v[i] = v[i] / (1.0f + expf(-v[i])) * u[i];
+                }
+                const int n = n0 + c * 32;
+                if (m < M) {
+                    OutT* dst = Y + (int64_t)m * ldy + n;
+                    if (n + 32 <= N && (((uintptr_t)dst) & 31) == 0) {
+#pragma unroll
+                        for (int i = 0; i < 32; i += 8) tc_store8(dst + i, v + i);
+                    } else {
+                        for (int i = 0; i < 32; ++i)
+                            if (n + i < N) dst[i] = from_f32<OutT>(v[i]);
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TC_TMEM_COLS) : "memory");
+    }
+}
+
+// ----------------------------------------------------------------------------------------
+// host
+// ----------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (fn == nullptr) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    }
+    return fn;
+}
+
+// A [rows, cols] row-major bfloat16 matrix, boxes of box_rows x 64 values, 128-byte swizzle, zeros outside.
+static int make_map(CUtensorMap* map, const void* ptr, int64_t rows, int64_t cols, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    X0NE_REQUIRE(fn != nullptr, "gemm_tc: the driver has no cuTensorMapEncodeTiled");
+    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+    const cuuint32_t box[2] = {TC_BK, (cuuint32_t)box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    X0NE_REQUIRE(r == CUDA_SUCCESS, "gemm_tc: cuTensorMapEncodeTiled failed with code %d", (int)r);
+    return 0;
+}
+
+template <bool SWIGLU, typename OutT>
+static int launch_tc(const void* W, const void* X, OutT* Y, int M, int N, int K, int ldy, int* status, cudaStream_t stream) {
+    CUtensorMap map_x, map_w;
+    if (int e = make_map(&map_x, X, M, K, TC_BM)) return e;
+    if (int e = make_map(&map_w, W, SWIGLU ? 2 * (int64_t)N : N, K, SWIGLU ? 128 : 256)) return e;
+    const size_t smem = (size_t)TC_STAGES * (TC_BM * 128 + 256 * 128) + sizeof(TcShared) + 1024;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<SWIGLU, OutT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) {
+            x0ne_set_error("gemm_tc: cannot set %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
+            return (int)e;
+        }
+        configured = true;
+    }
+    constexpr int BN = SWIGLU ? 128 : 256;
+    dim3 grid((N + BN - 1) / BN, (M + TC_BM - 1) / TC_BM);
+    X0NE_REQUIRE(grid.y <= 65535, "gemm_tc: M %d needs more than 65535 row tiles", M);
+    x0ne_launch(gemm_tc_kernel<SWIGLU, OutT>, grid, dim3(TC_THREADS), smem, stream, map_x, map_w, Y, M, N, K, ldy, status);
+    X0NE_LAUNCH_CHECK();
+}
+
+// out_kind: 0 = bfloat16, 1 = float32, 2 = bfloat16 with SwiGLU over the packed [gate; up] weight
+// (W then has 2*N rows and y has N columns).  `status` is one int in device memory, zero before the
+// first call; a non-zero value afterwards says a barrier wait ran out (1 copy, 2 MMA, 3 epilogue)
+// and the output is not valid.
+X0NE_API int x0ne_gemm_bf16_tcgen05(const void* W, const void* X, void* Y, int M, int N, int K, int ldy, int out_kind,
+                                    int* status, cudaStream_t stream) {
+    X0NE_REQUIRE(M > 0 && N > 0 && K > 0, "gemm_tc: M %d N %d K %d", M, N, K);
+    X0NE_REQUIRE(K % 8 == 0, "gemm_tc: K %d is not a multiple of 8 (rows must be 16-byte aligned)", K);
+    X0NE_REQUIRE(ldy >= N && out_kind >= 0 && out_kind <= 2 && status != nullptr, "gemm_tc: ldy %d N %d kind %d", ldy, N, out_kind);
+    X0NE_REQUIRE((((uintptr_t)W | (uintptr_t)X) & 15) == 0, "gemm_tc: operands are not 16-byte aligned");
+    if (out_kind == 0) return launch_tc<false, bf16>(W, X, (bf16*)Y, M, N, K, ldy, status, stream);
+    if (out_kind == 1) return launch_tc<false, float>(W, X, (float*)Y, M, N, K, ldy, status, stream);
+    return launch_tc<true, bf16>(W, X, (bf16*)Y, M, N, K, ldy, status, stream);
+}

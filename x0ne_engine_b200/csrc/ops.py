@@ -343,3 +343,40 @@ def gemm_bf16_smallm(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, m: int, 
         raise KernelError(f"gemm_smallm: no output kind for {y.dtype} (swiglu={swiglu})")
     _check(lib, lib.x0ne_gemm_bf16_smallm(_ptr(w), _ptr(x), _ptr(y), c_int(m), c_int(n), c_int(k), c_int(n),
                                           c_int(kind), c_int(_sms(w.device)), _stream()), "gemm_bf16_smallm")
+
+
+# ---------------------------------------------------------------------------------------------
+# bfloat16 product on tcgen05 tensor cores with TMA operands (module `tc`), for passes with many rows
+# ---------------------------------------------------------------------------------------------
+_tc_status = {}
+
+
+def gemm_tc_status(device) -> torch.Tensor:
+    """The int the tcgen05 kernels report a timed-out barrier wait in (0 = all waits succeeded)."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    t = _tc_status.get(idx)
+    if t is None:
+        t = _tc_status[idx] = torch.zeros(1, dtype=torch.int32, device=device)
+    return t
+
+
+def gemm_bf16_tcgen05(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, m: int, swiglu: bool = False) -> None:
+    """y[:m] = x[:m] @ w.T on the tcgen05 tensor cores (128 x 256 tiles, TMA loads, accumulator in
+    tensor memory); y is bfloat16 or float32.  With `swiglu`, w is the packed [gate; up] weight and
+    y[:m] = silu(x gate^T) * (x up^T).  Needs K % 8 == 0."""
+    lib = _lib("tc")
+    _need(x, torch.bfloat16, "gemm input")
+    _need(w, torch.bfloat16, "gemm weight")
+    _need(y, y.dtype, "gemm output")
+    rows, k = w.shape
+    n = rows // 2 if swiglu else rows
+    if x.shape[-1] != k or y.shape[-1] != n or x.numel() < m * k or y.numel() < m * n or (swiglu and rows % 2):
+        raise KernelError(f"gemm_tc: shapes x {tuple(x.shape)} w {tuple(w.shape)} y {tuple(y.shape)} m {m}")
+    if y.dtype == torch.float32 and not swiglu:
+        kind = 1
+    elif y.dtype == torch.bfloat16:
+        kind = 2 if swiglu else 0
+    else:
+        raise KernelError(f"gemm_tc: no output kind for {y.dtype} (swiglu={swiglu})")
+    _check(lib, lib.x0ne_gemm_bf16_tcgen05(_ptr(w), _ptr(x), _ptr(y), c_int(m), c_int(n), c_int(k), c_int(n),
+                                           c_int(kind), _ptr(gemm_tc_status(w.device)), _stream()), "gemm_bf16_tcgen05")
