@@ -360,9 +360,10 @@ def gemm_tc_status(device) -> torch.Tensor:
     return t
 
 
-def gemm_bf16_tcgen05(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, m: int, swiglu: bool = False) -> None:
+def gemm_bf16_tcgen05(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, m: int, swiglu: bool = False,
+                      pair: bool = True) -> None:
     """y[:m] = x[:m] @ w.T on the tcgen05 tensor cores (128 x 256 tiles, TMA loads, accumulator in
-    tensor memory); y is bfloat16 or float32.  With `swiglu`, w is the packed [gate; up] weight and
+    tensor memory; with `pair`, pairs of blocks on 256 x 256 tiles); y is bfloat16 or float32.  With `swiglu`, w is the packed [gate; up] weight and
     y[:m] = silu(x gate^T) * (x up^T).  Needs K % 8 == 0."""
     lib = _lib("tc")
     _need(x, torch.bfloat16, "gemm input")
@@ -379,4 +380,5 @@ def gemm_bf16_tcgen05(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, m: int,
     else:
         raise KernelError(f"gemm_tc: no output kind for {y.dtype} (swiglu={swiglu})")
     _check(lib, lib.x0ne_gemm_bf16_tcgen05(_ptr(w), _ptr(x), _ptr(y), c_int(m), c_int(n), c_int(k), c_int(n),
-                                           c_int(kind), _ptr(gemm_tc_status(w.device)), _stream()), "gemm_bf16_tcgen05")
+                                           c_int(kind), c_int(1 if pair else 0), _ptr(gemm_tc_status(w.device)),
+                                           _stream()), "gemm_bf16_tcgen05")
