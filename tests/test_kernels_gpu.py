@@ -121,6 +121,37 @@ def test_gemm_bf16_smallm_with_swiglu_epilogue(m, inter, k):
     assert (y.double() - want).abs().max() / want.abs().max() < 2 * BF16_EPS
 
 
+# ------------------------------------------------------------------------------------------ tcgen05 product
+@pytest.mark.parametrize("pair", [True, False])
+@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (100, 300, 200), (1000, 520, 328), (2048, 1024, 512)])
+def test_gemm_bf16_tcgen05(m, n, k, pair):
+    """TMA + tcgen05.mma + tensor memory, single blocks and pairs; rows, columns and k past the tiles."""
+    o = ops()
+    x, w = rnd((m, k), torch.bfloat16, 90), rnd((n, k), torch.bfloat16, 91, 0.05)
+    want = x.double() @ w.double().T
+    mag = (x.double().abs() @ w.double().abs().T).max()
+    for out_dtype, bound in ((torch.bfloat16, BF16_EPS), (torch.float32, 1e-5)):
+        y = torch.full((m, n), 9.0, dtype=out_dtype, device=DEV)
+        o.gemm_bf16_tcgen05(x, w, y, m, pair=pair)
+        assert int(o.gemm_tc_status(x.device)[0]) == 0
+        assert (y.double() - want).abs().max() / mag < bound
+    o.check_tc_status(x.device)
+
+
+@pytest.mark.parametrize("pair", [True, False])
+@pytest.mark.parametrize("m,inter,k", [(128, 128, 64), (300, 200, 136), (1024, 1000, 512)])
+def test_gemm_bf16_tcgen05_with_swiglu_epilogue(m, inter, k, pair):
+    o = ops()
+    x, w = rnd((m, k), torch.bfloat16, 92), rnd((2 * inter, k), torch.bfloat16, 93, 0.2)
+    y = torch.zeros((m, inter), dtype=torch.bfloat16, device=DEV)
+    o.gemm_bf16_tcgen05(x, w, y, m, swiglu=True, pair=pair)
+    assert int(o.gemm_tc_status(x.device)[0]) == 0
+    gu = x.double() @ w.double().T
+    g, u = gu[:, :inter], gu[:, inter:]
+    want = g / (1 + torch.exp(-g)) * u
+    assert (y.double() - want).abs().max() / want.abs().max() < 2 * BF16_EPS
+
+
 # ------------------------------------------------------------------------------------------ rope + cache write
 def make_cache(kv_heads, head_dim, n_pages, n_slots, dtype, pages_per_slot):
     """A one-entry paged cache with a page table that scatters each slot's pages."""

@@ -179,7 +179,8 @@ def cmd_kernel_bench(a) -> int:
                           "us": us, "gb_s": bytes_per_launch / us / 1e3, "tflops": flops_per_launch / us / 1e6,
                           "copies": copies}))
 
-    if a.kernel in ("gemm_smallm", "gemm_smallm_swiglu", "gemm_library", "gemm_tc", "gemm_tc_swiglu"):
+    if a.kernel in ("gemm_smallm", "gemm_smallm_swiglu", "gemm_library", "gemm_tc", "gemm_tc_swiglu", "gemm_tc1",
+                    "gemm_tc1_swiglu"):
         swiglu = a.kernel.endswith("_swiglu")
         rows = 2 * a.n if swiglu else a.n
         wbytes = rows * a.k * 2
@@ -195,7 +196,7 @@ def cmd_kernel_bench(a) -> int:
             if a.kernel == "gemm_library":
                 torch.mm(x[:a.m], w.t(), out=y[:a.m])
             elif a.kernel.startswith("gemm_tc"):
-                ops.gemm_bf16_tcgen05(x, w, y, a.m, swiglu=swiglu)
+                ops.gemm_bf16_tcgen05(x, w, y, a.m, swiglu=swiglu, pair=not a.kernel.startswith("gemm_tc1"))
             else:
                 ops.gemm_bf16_smallm(x, w, y, a.m, swiglu=swiglu)
         timed(fn, wbytes, 2.0 * a.m * rows * a.k)

@@ -349,6 +349,25 @@ def gemm_bf16_smallm(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, m: int, 
 # bfloat16 product on tcgen05 tensor cores with TMA operands (module `tc`), for passes with many rows
 # ---------------------------------------------------------------------------------------------
 _tc_status = {}
+TC_MIN_ROWS = 768        # from about this many rows the fused tcgen05 gate/up product beats the library product + SwiGLU
+tc_used = False          # set when a tcgen05 product was launched since the last check_tc_status()
+
+
+def gemm_tc_takes(w: torch.Tensor, m: int) -> bool:
+    return w.dtype == torch.bfloat16 and m >= TC_MIN_ROWS and w.shape[1] % 8 == 0
+
+
+def check_tc_status(device) -> None:
+    """Raises if a tcgen05 kernel reported a barrier wait that ran out (reads one int back)."""
+    global tc_used
+    if not tc_used:
+        return
+    tc_used = False
+    st = int(gemm_tc_status(device)[0])
+    if st != 0:
+        gemm_tc_status(device).zero_()
+        raise KernelError(f"a tcgen05 product gave up waiting on a barrier (code {st}: 1 copy, 2 MMA, 3 epilogue, "
+                          "4 accumulator); its output is not valid")
 
 
 def gemm_tc_status(device) -> torch.Tensor:
@@ -379,6 +398,8 @@ def gemm_bf16_tcgen05(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, m: int,
         kind = 2 if swiglu else 0
     else:
         raise KernelError(f"gemm_tc: no output kind for {y.dtype} (swiglu={swiglu})")
+    global tc_used
+    tc_used = True
     _check(lib, lib.x0ne_gemm_bf16_tcgen05(_ptr(w), _ptr(x), _ptr(y), c_int(m), c_int(n), c_int(k), c_int(n),
                                            c_int(kind), c_int(1 if pair else 0), _ptr(gemm_tc_status(w.device)),
                                            _stream()), "gemm_bf16_tcgen05")

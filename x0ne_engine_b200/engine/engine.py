@@ -207,6 +207,9 @@ class Engine:
                            logits, decode, slots, starts, lens, first_row, r0, r1)
         for s, n in zip(slots, lens):
             self.cache.lengths[s] += n
+        if self.dtype == torch.bfloat16:
+            from ..csrc import ops
+            ops.check_tc_status(self.device)
         return logits
 
     def _run_pass(self, toks, rslot, rpos, want_rows, want_dest, logits, decode, slots, starts, lens, first_row,

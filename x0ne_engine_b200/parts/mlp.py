@@ -44,6 +44,8 @@ class SwiGLU(FeedForward):
         out = ctx.ws.buffer("delta", (ctx.ws.max_rows, self.hidden), self.env.dtype)
         if ops.gemm_smallm_takes(self.gate_up.weight, n_rows):
             ops.gemm_bf16_smallm(x, self.gate_up.weight, act, n_rows, swiglu=True)     # activation in the epilogue
+        elif ops.gemm_tc_takes(self.gate_up.weight, n_rows):
+            ops.gemm_bf16_tcgen05(x, self.gate_up.weight, act, n_rows, swiglu=True)    # tcgen05, activation in the epilogue
         else:
             self.gate_up(x, gu, n_rows)
             ops.swiglu(gu, act, n_rows)
