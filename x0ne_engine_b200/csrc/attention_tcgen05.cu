@@ -1,0 +1,304 @@
+// Causal GQA flash attention for passes with many rows, on the 5th-generation tensor cores:
+// both products of a tile (S = Q K^T and P V) are tcgen05.mma with their results in tensor memory,
+// Q and the cache pages come to shared memory by TMA, and the softmax runs in registers, one
+// thread per query row.  Same arithmetic as the mma.sync kernel of attention_bf16.cu (formulas:
+// x0ne-core/kernels/cuda/attention.cu:20-59,138-157): scores, running max and sum, exponentials
+// and the output accumulator in float32, P rounded to bfloat16 for the second product, one
+// rounding of the output at the end.  head_dim 64 or 128; other sizes use the mma.sync kernel.
+//
+// A block takes one tile of up to 128 query rows of one sequence and one q head (grid: q heads x
+// tiles, longest contexts first) and walks the cache pages (64 keys) the tile can see:
+//   * control thread (warp 4): TMA loads of Q (once) and of each page's K and V tiles (two stages,
+//     128-byte swizzle; a page of one kv head is 64 consecutive rows of the cache seen as one long
+//     [rows, head_dim] matrix); issues S = Q K^T (M 128, N 64, K 16 x head_dim/16) and, when the
+//     softmax threads have written P, O_tile = P V (M 128, N head_dim, K 16 x 4; V is the N-major
+//     operand, straight from the page as it lies in the cache).
+//   * softmax threads (warps 0-3, thread = row): read S from tensor memory, scale, mask, update
+//     the running max and sum, write P to shared memory in the swizzled layout the MMA reads, then
+//     read O_tile and fold it into the row's accumulator: o = o * alpha + O_tile.
+// Every barrier wait is bounded; when one runs out the block records it in `status`, skips the
+// rest, frees its tensor memory and returns.  Two blocks fit on an SM and overlap each other.
+#include "tcgen05.cuh"
+
+struct AttnTcArgs {
+    bf16* out;
+    const int32_t* tile_seq;       // [tiles]
+    const int32_t* tile_row0;      // [tiles] first row of the tile within the pass
+    const int32_t* seq_first_row;  // [seqs + 1]
+    const int32_t* seq_slot;       // [seqs]
+    const int32_t* seq_pos0;       // [seqs]
+    int32_t q_heads;
+    int32_t window;
+    float scale_log2;
+};
+
+struct AttnTcShared {
+    uint64_t q_full;
+    uint64_t kv_full[2];
+    uint64_t s_ready;
+    uint64_t p_ready;
+    uint64_t pv_ready;
+    uint32_t tmem_base;
+    int failed;
+};
+
+// N-major (the matrix's N runs along the 128-byte rows) shared-memory descriptor, 128-byte swizzle:
+// 8-row groups 1024 bytes apart, 64-wide column blocks `block_bytes` apart.
+__device__ __forceinline__ uint64_t tc_desc_nmajor(uint32_t smem_addr, uint32_t block_bytes) {
+    const uint32_t lo = ((smem_addr >> 4) & 0x3FFFu) | (((block_bytes >> 4) & 0x3FFFu) << 16);
+    const uint32_t hi = 64u | (1u << 14) | (2u << 29);
+    return ((uint64_t)hi << 32) | lo;
+}
+
+#define ATC_THREADS 160
+#define ATC_TMEM_COLS 256
+
+template <int HD>
+__global__ void __launch_bounds__(ATC_THREADS, 2) attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
+                                                                           const __grid_constant__ CUtensorMap map_kv,
+                                                                           AttnTcArgs a, PagedCache cache, int* status) {
+    extern __shared__ __align__(1024) unsigned char atc_raw[];
+    constexpr int NB = HD / 64;                   // 64-wide blocks of a head: 128 bytes per row each
+    constexpr int Q_BYTES = NB * 128 * 128;       // [NB][128 rows][128 B]
+    constexpr int KV_BYTES = NB * 64 * 128;       // one K or V tile: [NB][64 keys][128 B]
+    constexpr int P_BYTES = 128 * 128;            // [128 rows][64 keys]
+    unsigned char* qs = atc_raw;
+    unsigned char* ks = qs + Q_BYTES;             // 2 stages
+    unsigned char* vs = ks + 2 * KV_BYTES;        // 2 stages
+    unsigned char* ps = vs + 2 * KV_BYTES;
+    AttnTcShared* sh = reinterpret_cast<AttnTcShared*>(ps + P_BYTES);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    const int head = blockIdx.x, tile = gridDim.y - 1 - blockIdx.y;
+    const int kh = head / (a.q_heads / cache.kv_heads);
+    const int seq = a.tile_seq[tile], row0 = a.tile_row0[tile];
+    const int nrows = min(128, a.seq_first_row[seq + 1] - row0);
+    const int slot = a.seq_slot[seq];
+    const int pos_first = a.seq_pos0[seq] + (row0 - a.seq_first_row[seq]);
+    const int pos_last = pos_first + nrows - 1;
+    const int j_lo = a.window > 0 ? max(0, pos_first - a.window + 1) : 0;
+    const int kt_lo = j_lo / 64, n_kt = pos_last / 64 - kt_lo + 1;
+
+    pdl_launch_dependents();
+    if (threadIdx.x == 0) {
+        mbar_init(&sh->q_full, 1);
+        mbar_init(&sh->kv_full[0], 1);
+        mbar_init(&sh->kv_full[1], 1);
+        mbar_init(&sh->s_ready, 1);
+        mbar_init(&sh->p_ready, 128);
+        mbar_init(&sh->pv_ready, 1);
+        sh->failed = (tc_smem(atc_raw) & 1023u) != 0 ? 1 : 0;      // the swizzle needs 1024-byte aligned tiles
+        if (sh->failed) atomicCAS(status, 0, 9);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 4) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tc_smem(&sh->tmem_base)),
+                     "r"(ATC_TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = sh->tmem_base;
+    const uint32_t tmem_s = tmem, tmem_o = tmem + 64;       // S: 64 columns; O_tile: HD columns
+
+    if (warp == 4) {
+        if (lane == 0 && !sh->failed) {
+            pdl_wait();      // q and the newest cache rows were written by the kernel before this one
+            mbar_expect_tx(&sh->q_full, Q_BYTES);
+#pragma unroll
+            for (int nb = 0; nb < NB; ++nb) tma_load_2d(qs + nb * 128 * 128, &map_q, head * HD + nb * 64, row0, &sh->q_full);
+            auto load_kv = [&](int i) {
+                const int st = i & 1;
+                int page = cache.page_table[(int64_t)slot * cache.table_stride + ((kt_lo + i) % cache.ring_pages)];
+                if (page < 0 || page >= cache.n_pages) page = 0;      // never for a sequence that holds its pages
+                const int krow = ((page * 2 + 0) * cache.kv_heads + kh) * 64;
+                const int vrow = ((page * 2 + 1) * cache.kv_heads + kh) * 64;
+                mbar_expect_tx(&sh->kv_full[st], 2 * KV_BYTES);
+#pragma unroll
+                for (int nb = 0; nb < NB; ++nb) {
+                    tma_load_2d(ks + st * KV_BYTES + nb * 64 * 128, &map_kv, nb * 64, krow, &sh->kv_full[st]);
+                    tma_load_2d(vs + st * KV_BYTES + nb * 64 * 128, &map_kv, nb * 64, vrow, &sh->kv_full[st]);
+                }
+            };
+            load_kv(0);
+            if (n_kt > 1) load_kv(1);
+            // instruction descriptors: f32 accumulate, bf16 operands, M = 128
+            const uint32_t idesc_qk = (1u << 4) | (1u << 7) | (1u << 10) | ((64u >> 3) << 17) | ((128u >> 4) << 24);
+            const uint32_t idesc_pv = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | (((uint32_t)HD >> 3) << 17) | ((128u >> 4) << 24);
+            bool ok = mbar_wait(&sh->q_full, 0, status, 5);
+            for (int i = 0; i < n_kt && ok; ++i) {
+                const int st = i & 1;
+                if (!(ok = mbar_wait(&sh->kv_full[st], (i >> 1) & 1, status, 6))) break;
+                tc_fence_after();
+                const uint32_t kb = tc_smem(ks + st * KV_BYTES), vb = tc_smem(vs + st * KV_BYTES), qb = tc_smem(qs);
+#pragma unroll
+                for (int kk = 0; kk < HD / 16; ++kk)
+                    tc_mma(tmem_s, tc_desc(qb + (kk / 4) * 128 * 128 + (kk % 4) * 32),
+                           tc_desc(kb + (kk / 4) * 64 * 128 + (kk % 4) * 32), idesc_qk, kk > 0 ? 1u : 0u);
+                tc_commit(&sh->s_ready);
+                if (!(ok = mbar_wait(&sh->p_ready, i & 1, status, 7))) break;
+                tc_fence_after();
+#pragma unroll
+                for (int kk = 0; kk < 4; ++kk)
+                    tc_mma(tmem_o, tc_desc(tc_smem(ps) + kk * 32), tc_desc_nmajor(vb + kk * 16 * 128, 64 * 128), idesc_pv,
+                           kk > 0 ? 1u : 0u);
+                tc_commit(&sh->pv_ready);
+                if (i + 2 < n_kt) {       // the stage is free once both products of this page are done
+                    if (!(ok = mbar_wait(&sh->pv_ready, i & 1, status, 8))) break;
+                    load_kv(i + 2);
+                }
+            }
+            if (!ok) sh->failed = 1;
+        }
+    } else {
+        const int r = warp * 32 + lane;                       // this thread's row of the tile = its tensor-memory lane
+        const int p = pos_first + r;
+        const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+        float o[HD];
+#pragma unroll
+        for (int d = 0; d < HD; ++d) o[d] = 0.f;
+        float m = -INFINITY, l = 0.f;
+        bool ok = !sh->failed;
+        for (int i = 0; i < n_kt && ok; ++i) {
+            const int kt = kt_lo + i;
+            if (!(ok = mbar_wait(&sh->s_ready, i & 1, status, 10))) break;
+            tc_fence_after();
+            const bool edge = (kt * 64 + 63 > pos_first) || (a.window > 0 && kt * 64 <= pos_last - a.window);
+            // Two sweeps over the row's 64 scores, 32 at a time (they are read from tensor memory twice
+            // rather than all kept in registers): first the maximum, then the exponentials.
+            auto load_scores = [&](int half, float* s) {
+                tc_ld32(tmem_s + lane_base + half * 32, s);
+#pragma unroll
+                for (int c = 0; c < 32; ++c) {
+                    float v = s[c] * a.scale_log2;
+                    if (edge) {
+                        const int j = kt * 64 + half * 32 + c;
+                        if (j > p || (a.window > 0 && j <= p - a.window)) v = -INFINITY;
+                    }
+                    s[c] = v;
+                }
+            };
+            float mx = -INFINITY;
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                float s[32];
+                load_scores(half, s);
+#pragma unroll
+                for (int c = 0; c < 32; ++c) mx = fmaxf(mx, s[c]);
+            }
+            const float m_new = fmaxf(m, mx);
+            const float base = m_new == -INFINITY ? 0.f : m_new;
+            const float alpha = exp2f(m - base);
+            float sum = 0.f;
+            // P row -> shared memory, 16 bytes (8 keys) at a time, chunk c at position c ^ (row & 7)
+            unsigned char* prow = ps + r * 128;
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                float s[32];
+                load_scores(half, s);
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    uint32_t w[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const float p0 = exp2f(s[c * 8 + 2 * e] - base), p1 = exp2f(s[c * 8 + 2 * e + 1] - base);
+                        sum += p0 + p1;
+                        __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+                        w[e] = *reinterpret_cast<uint32_t*>(&h);
+                    }
+                    *reinterpret_cast<uint4*>(prow + (((half * 4 + c) ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+                }
+            }
+            l = l * alpha + sum;
+            m = m_new;
+            // The page's rows past the sequence's last position may hold anything (an earlier
+            // sequence's values): zero them in V, so that 0 * value stays 0.
+            if (kt * 64 + 63 > pos_last && r < 64 && kt * 64 + r > pos_last) {
+                unsigned char* vrow = vs + (i & 1) * KV_BYTES + r * 128;
+#pragma unroll
+                for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+                    for (int c = 0; c < 8; ++c)
+                        *reinterpret_cast<uint4*>(vrow + nb * 64 * 128 + c * 16) = make_uint4(0, 0, 0, 0);
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // P (and the zeros) are for the MMA to read
+            tc_fence_before();
+            mbar_arrive(&sh->p_ready);
+            if (!(ok = mbar_wait(&sh->pv_ready, i & 1, status, 11))) break;
+            tc_fence_after();
+#pragma unroll
+            for (int c = 0; c < HD / 32; ++c) {
+                float pv[32];
+                tc_ld32(tmem_o + lane_base + c * 32, pv);
+#pragma unroll
+                for (int d = 0; d < 32; ++d) o[c * 32 + d] = o[c * 32 + d] * alpha + pv[d];
+            }
+        }
+        if (!ok) sh->failed = 1;
+        if (ok && r < nrows) {
+            const float inv = 1.0f / l;
+            bf16* dst = a.out + (int64_t)(row0 + r) * (a.q_heads * HD) + head * HD;
+#pragma unroll
+            for (int d = 0; d < HD; d += 8) {
+                float v8[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) v8[e] = o[d + e] * inv;
+                tc_store8(dst + d, v8);
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 4) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(ATC_TMEM_COLS) : "memory");
+    }
+}
+
+// ----------------------------------------------------------------------------------------
+// host
+// ----------------------------------------------------------------------------------------
+template <int HD>
+static int launch_attn_tc(const CUtensorMap& map_q, const CUtensorMap& map_kv, const AttnTcArgs& a, const PagedCache& cache,
+                          int n_tiles, int* status, cudaStream_t stream) {
+    constexpr int NB = HD / 64;
+    const size_t smem = (size_t)NB * 128 * 128 + 4 * (size_t)NB * 64 * 128 + 128 * 128 + sizeof(AttnTcShared);
+    static bool configured = false;
+    if (!configured) {
+        cudaFuncSetAttribute(attention_prefill_tc_kernel<HD>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
+        cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) {
+            x0ne_set_error("attention_prefill_tc: cannot set %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
+            return (int)e;
+        }
+        configured = true;
+    }
+    x0ne_launch(attention_prefill_tc_kernel<HD>, dim3(a.q_heads, n_tiles), dim3(ATC_THREADS), smem, stream, map_q, map_kv, a,
+                cache, status);
+    X0NE_LAUNCH_CHECK();
+}
+
+// q, out: bfloat16 [q_rows, q_heads * head_dim]; tiles of up to 128 rows (tile tables as for the
+// mma.sync prefill kernel).  `status`: one int in device memory, zero before the first call; not
+// zero afterwards means a barrier wait ran out and the output is not valid.
+X0NE_API int x0ne_attention_prefill_tcgen05(const void* q, void* out, int q_rows, PagedCache cache, const int32_t* tile_seq,
+                                            const int32_t* tile_row0, int n_tiles, const int32_t* seq_first_row,
+                                            const int32_t* seq_slot, const int32_t* seq_pos0, int q_heads, float scale,
+                                            int window, int* status, cudaStream_t stream) {
+    X0NE_REQUIRE(cache.page_size == 64, "attention_prefill_tc: pages of %d positions, the kernel takes 64", cache.page_size);
+    X0NE_REQUIRE(cache.head_dim == 64 || cache.head_dim == 128, "attention_prefill_tc: head_dim %d (64 or 128)", cache.head_dim);
+    X0NE_REQUIRE(q_heads > 0 && cache.kv_heads > 0 && q_heads % cache.kv_heads == 0, "attention_prefill_tc: %d q heads over %d kv heads",
+                 q_heads, cache.kv_heads);
+    X0NE_REQUIRE(n_tiles >= 0 && n_tiles <= 65535 && window >= 0 && q_rows > 0 && status != nullptr, "attention_prefill_tc: bad sizes");
+    X0NE_REQUIRE((int64_t)cache.n_pages * 2 * cache.kv_heads * 64 <= 0x7fffffff, "attention_prefill_tc: the cache has too many rows");
+    X0NE_REQUIRE(cache.page_stride == (int64_t)2 * cache.kv_heads * 64 * cache.head_dim, "attention_prefill_tc: pages are not contiguous");
+    if (n_tiles == 0) return 0;
+    CUtensorMap map_q, map_kv;
+    if (int e = x0ne_tc_make_map(&map_q, q, q_rows, (int64_t)q_heads * cache.head_dim, 128)) return e;
+    if (int e = x0ne_tc_make_map(&map_kv, cache.base, (int64_t)cache.n_pages * 2 * cache.kv_heads * 64, cache.head_dim, 64)) return e;
+    AttnTcArgs a{(bf16*)out, tile_seq, tile_row0, seq_first_row, seq_slot, seq_pos0, q_heads, window, scale * 1.4426950408889634f};
+    if (cache.head_dim == 128) return launch_attn_tc<128>(map_q, map_kv, a, cache, n_tiles, status, stream);
+    return launch_attn_tc<64>(map_q, map_kv, a, cache, n_tiles, status, stream);
+}

@@ -403,3 +403,35 @@ def gemm_bf16_tcgen05(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, m: int,
     _check(lib, lib.x0ne_gemm_bf16_tcgen05(_ptr(w), _ptr(x), _ptr(y), c_int(m), c_int(n), c_int(k), c_int(n),
                                            c_int(kind), c_int(1 if pair else 0), _ptr(gemm_tc_status(w.device)),
                                            _stream()), "gemm_bf16_tcgen05")
+
+
+def attention_tc_takes(cache: PagedCacheArg, dtype: torch.dtype) -> bool:
+    """Whether the tcgen05 prefill attention takes this shape."""
+    return dtype == torch.bfloat16 and cache.page_size == 64 and cache.head_dim in (64, 128)
+
+
+def attention_prefill_tcgen05(q: torch.Tensor, out: torch.Tensor, cache: PagedCacheArg, tile_seq: torch.Tensor,
+                              tile_row0: torch.Tensor, n_tiles: int, seq_first_row: torch.Tensor,
+                              seq_slot: torch.Tensor, seq_pos0: torch.Tensor, q_heads: int, scale: float,
+                              window: int = 0) -> None:
+    """Causal flash attention of a pass whose sequences bring several rows, on tcgen05 with TMA loads;
+    tiles are up to 128 consecutive rows of one sequence (`attention_prefill_tile_rows()`)."""
+    global tc_used
+    lib = _lib("tc")
+    _need(q, torch.bfloat16, "q")
+    _need(out, torch.bfloat16, "attention output")
+    for t, what in ((tile_seq, "tile sequences"), (tile_row0, "tile rows"), (seq_first_row, "sequence rows"),
+                    (seq_slot, "sequence slots"), (seq_pos0, "sequence positions")):
+        _need(t, torch.int32, what)
+    if tile_seq.numel() < n_tiles or tile_row0.numel() < n_tiles:
+        raise KernelError("attention_prefill_tc: tile tables shorter than the tiles asked for")
+    if q.dim() != 2 or q.shape[-1] != q_heads * cache.head_dim or out.shape != q.shape:
+        raise KernelError("attention_prefill_tc: q or output do not match the head counts")
+    tc_used = True
+    for first in range(0, n_tiles, 65535):
+        n = min(65535, n_tiles - first)
+        _check(lib, lib.x0ne_attention_prefill_tcgen05(
+            _ptr(q), _ptr(out), c_int(q.shape[0]), cache, c_void_p(tile_seq.data_ptr() + 4 * first),
+            c_void_p(tile_row0.data_ptr() + 4 * first), c_int(n), _ptr(seq_first_row), _ptr(seq_slot), _ptr(seq_pos0),
+            c_int(q_heads), c_float(scale), c_int(window), _ptr(gemm_tc_status(q.device)), _stream()),
+            "attention_prefill_tcgen05")
