@@ -234,7 +234,7 @@ def cmd_kernel_bench(a) -> int:
         timed(fn, B * ctx * 2 * kvh * hd * 2, 4.0 * B * qh * hd * ctx)
         return 0
 
-    if a.kernel == "attention_prefill":
+    if a.kernel in ("attention_prefill", "attention_prefill_tc"):
         hd, kvh, qh, T = a.head_dim, a.kv_heads, a.q_heads, a.context
         pages_per = (T + 63) // 64
         store = torch.randn(pages_per, 2, kvh, 64, hd, device=dev).bfloat16()
@@ -251,8 +251,12 @@ def cmd_kernel_bench(a) -> int:
         copies = 1
 
         def fn():
-            ops.attention_prefill_bf16(q, out, view, tile_seq, tile_row0, n_tiles, first, sslot, spos0, qh,
-                                       1 / math.sqrt(hd), 0)
+            if a.kernel == "attention_prefill_tc":
+                ops.attention_prefill_tcgen05(q, out, view, tile_seq, tile_row0, n_tiles, first, sslot, spos0, qh,
+                                              1 / math.sqrt(hd), 0)
+            else:
+                ops.attention_prefill_bf16(q, out, view, tile_seq, tile_row0, n_tiles, first, sslot, spos0, qh,
+                                           1 / math.sqrt(hd), 0)
         timed(fn, 2 * T * qh * hd * 2 + 2 * T * kvh * hd * 2, 4.0 * qh * hd * T * (T + 1) / 2)
         return 0
 

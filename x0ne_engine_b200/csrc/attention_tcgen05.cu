@@ -11,11 +11,13 @@
 //   * control thread (warp 4): TMA loads of Q (once) and of each page's K and V tiles (two stages,
 //     128-byte swizzle; a page of one kv head is 64 consecutive rows of the cache seen as one long
 //     [rows, head_dim] matrix); issues S = Q K^T (M 128, N 64, K 16 x head_dim/16) and, when the
-//     softmax threads have written P, O_tile = P V (M 128, N head_dim, K 16 x 4; V is the N-major
+//     softmax threads have written P, O += P V (M 128, N head_dim, K 16 x 4; V is the N-major
 //     operand, straight from the page as it lies in the cache).
-//   * softmax threads (warps 0-3, thread = row): read S from tensor memory, scale, mask, update
-//     the running max and sum, write P to shared memory in the swizzled layout the MMA reads, then
-//     read O_tile and fold it into the row's accumulator: o = o * alpha + O_tile.
+//   * softmax threads (warps 0-3, thread = row): read S from tensor memory, mask, update the row's
+//     reference maximum and sum, and write P = 2^((s - reference) * scale) to shared memory in the
+//     swizzled layout the MMA reads.  The output accumulates in tensor memory across the pages (the
+//     MMA adds to it); it is rescaled there, by the softmax threads, only when a row's maximum has
+//     grown by more than 2^8 over its reference, and divided by the row's sum at the end.
 // Every barrier wait is bounded; when one runs out the block records it in `status`, skips the
 // rest, frees its tensor memory and returns.  Two blocks fit on an SM and overlap each other.
 #include "tcgen05.cuh"
@@ -49,6 +51,53 @@ __device__ __forceinline__ uint64_t tc_desc_nmajor(uint32_t smem_addr, uint32_t 
     const uint32_t hi = 64u | (1u << 14) | (2u << 29);
     return ((uint64_t)hi << 32) | lo;
 }
+
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ void tc_st32(uint32_t taddr, const float* v) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        ::"r"(taddr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])),
+          "r"(__float_as_uint(v[3])), "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])),
+          "r"(__float_as_uint(v[7])), "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])),
+          "r"(__float_as_uint(v[11])), "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])),
+          "r"(__float_as_uint(v[15])), "r"(__float_as_uint(v[16])), "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])),
+          "r"(__float_as_uint(v[19])), "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])),
+          "r"(__float_as_uint(v[23])), "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])),
+          "r"(__float_as_uint(v[27])), "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])),
+          "r"(__float_as_uint(v[31]))
+        : "memory");
+}
+// Two 32-column loads, one wait.
+__device__ __forceinline__ void tc_ld64(uint32_t taddr, float* v) {
+    uint32_t r[64];
+#define X0NE_LD32(OFF, T)                                                                                                   \
+    asm volatile(                                                                                                          \
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "   \
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"                          \
+        : "=r"(r[OFF + 0]), "=r"(r[OFF + 1]), "=r"(r[OFF + 2]), "=r"(r[OFF + 3]), "=r"(r[OFF + 4]), "=r"(r[OFF + 5]),      \
+          "=r"(r[OFF + 6]), "=r"(r[OFF + 7]), "=r"(r[OFF + 8]), "=r"(r[OFF + 9]), "=r"(r[OFF + 10]), "=r"(r[OFF + 11]),    \
+          "=r"(r[OFF + 12]), "=r"(r[OFF + 13]), "=r"(r[OFF + 14]), "=r"(r[OFF + 15]), "=r"(r[OFF + 16]), "=r"(r[OFF + 17]), \
+          "=r"(r[OFF + 18]), "=r"(r[OFF + 19]), "=r"(r[OFF + 20]), "=r"(r[OFF + 21]), "=r"(r[OFF + 22]), "=r"(r[OFF + 23]), \
+          "=r"(r[OFF + 24]), "=r"(r[OFF + 25]), "=r"(r[OFF + 26]), "=r"(r[OFF + 27]), "=r"(r[OFF + 28]), "=r"(r[OFF + 29]), \
+          "=r"(r[OFF + 30]), "=r"(r[OFF + 31])                                                                             \
+        : "r"(T) : "memory")
+    X0NE_LD32(0, taddr);
+    X0NE_LD32(32, taddr + 32);
+#undef X0NE_LD32
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 64; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// The running maximum a row's exponentials refer to is only raised when the new maximum exceeds it
+// by more than this many powers of two: then the accumulator in tensor memory has to be rescaled,
+// which is a read-modify-write of the whole row.  Until then p = 2^(s - reference) stays below 2^8.
+#define ATC_RESCALE_LOG2 8.0f
 
 #define ATC_THREADS 160
 #define ATC_TMEM_COLS 256
@@ -143,7 +192,7 @@ __global__ void __launch_bounds__(ATC_THREADS, 2) attention_prefill_tc_kernel(co
 #pragma unroll
                 for (int kk = 0; kk < 4; ++kk)
                     tc_mma(tmem_o, tc_desc(tc_smem(ps) + kk * 32), tc_desc_nmajor(vb + kk * 16 * 128, 64 * 128), idesc_pv,
-                           kk > 0 ? 1u : 0u);
+                           (i > 0 || kk > 0) ? 1u : 0u);          // the output accumulates in tensor memory over the pages
                 tc_commit(&sh->pv_ready);
                 if (i + 2 < n_kt) {       // the stage is free once both products of this page are done
                     if (!(ok = mbar_wait(&sh->pv_ready, i & 1, status, 8))) break;
@@ -156,63 +205,59 @@ __global__ void __launch_bounds__(ATC_THREADS, 2) attention_prefill_tc_kernel(co
         const int r = warp * 32 + lane;                       // this thread's row of the tile = its tensor-memory lane
         const int p = pos_first + r;
         const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
-        float o[HD];
-#pragma unroll
-        for (int d = 0; d < HD; ++d) o[d] = 0.f;
-        float m = -INFINITY, l = 0.f;
+        const float sc = a.scale_log2;
+        float m_ref = -INFINITY, l = 0.f;                     // reference maximum (raw scores) and the sum of p
         bool ok = !sh->failed;
         for (int i = 0; i < n_kt && ok; ++i) {
             const int kt = kt_lo + i;
             if (!(ok = mbar_wait(&sh->s_ready, i & 1, status, 10))) break;
-            tc_fence_after();
+            tc_fence_after();      // S of this page is complete, and so is every product issued before it
+            float s[64];
+            tc_ld64(tmem_s + lane_base, s);
             const bool edge = (kt * 64 + 63 > pos_first) || (a.window > 0 && kt * 64 <= pos_last - a.window);
-            // Two sweeps over the row's 64 scores, 32 at a time (they are read from tensor memory twice
-            // rather than all kept in registers): first the maximum, then the exponentials.
-            auto load_scores = [&](int half, float* s) {
-                tc_ld32(tmem_s + lane_base + half * 32, s);
-#pragma unroll
-                for (int c = 0; c < 32; ++c) {
-                    float v = s[c] * a.scale_log2;
-                    if (edge) {
-                        const int j = kt * 64 + half * 32 + c;
-                        if (j > p || (a.window > 0 && j <= p - a.window)) v = -INFINITY;
-                    }
-                    s[c] = v;
-                }
-            };
             float mx = -INFINITY;
 #pragma unroll
-            for (int half = 0; half < 2; ++half) {
-                float s[32];
-                load_scores(half, s);
-#pragma unroll
-                for (int c = 0; c < 32; ++c) mx = fmaxf(mx, s[c]);
+            for (int c = 0; c < 64; ++c) {
+                if (edge) {
+                    const int j = kt * 64 + c;
+                    if (j > p || (a.window > 0 && j <= p - a.window)) s[c] = -INFINITY;
+                }
+                mx = fmaxf(mx, s[c]);
             }
-            const float m_new = fmaxf(m, mx);
-            const float base = m_new == -INFINITY ? 0.f : m_new;
-            const float alpha = exp2f(m - base);
+            // raise the reference only when it is first set or falls too far behind
+            const bool raise = mx > m_ref && (m_ref == -INFINITY || (mx - m_ref) * sc > ATC_RESCALE_LOG2);
+            if (i > 0 && __any_sync(0xffffffffu, raise && m_ref != -INFINITY)) {
+                // rescale this warp's rows of the accumulator (rows that keep their reference: factor 1)
+                const float alpha = (raise && m_ref != -INFINITY) ? ex2_approx((m_ref - mx) * sc) : 1.f;
+                l *= alpha;
+#pragma unroll 1
+                for (int c = 0; c < HD / 32; ++c) {
+                    float ov[32];
+                    tc_ld32(tmem_o + lane_base + c * 32, ov);
+#pragma unroll
+                    for (int d = 0; d < 32; ++d) ov[d] *= alpha;
+                    tc_st32(tmem_o + lane_base + c * 32, ov);
+                }
+                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+            }
+            if (raise) m_ref = mx;
+            const float neg = m_ref == -INFINITY ? 0.f : -m_ref * sc;
             float sum = 0.f;
             // P row -> shared memory, 16 bytes (8 keys) at a time, chunk c at position c ^ (row & 7)
             unsigned char* prow = ps + r * 128;
 #pragma unroll
-            for (int half = 0; half < 2; ++half) {
-                float s[32];
-                load_scores(half, s);
+            for (int c = 0; c < 8; ++c) {
+                uint32_t w[4];
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    uint32_t w[4];
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const float p0 = exp2f(s[c * 8 + 2 * e] - base), p1 = exp2f(s[c * 8 + 2 * e + 1] - base);
-                        sum += p0 + p1;
-                        __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
-                        w[e] = *reinterpret_cast<uint32_t*>(&h);
-                    }
-                    *reinterpret_cast<uint4*>(prow + (((half * 4 + c) ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+                for (int e = 0; e < 4; ++e) {
+                    const float p0 = ex2_approx(fmaf(s[c * 8 + 2 * e], sc, neg)), p1 = ex2_approx(fmaf(s[c * 8 + 2 * e + 1], sc, neg));
+                    sum += p0 + p1;
+                    __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+                    w[e] = *reinterpret_cast<uint32_t*>(&h);
                 }
+                *reinterpret_cast<uint4*>(prow + ((c ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
             }
-            l = l * alpha + sum;
-            m = m_new;
+            l += sum;
             // The page's rows past the sequence's last position may hold anything (an earlier
             // sequence's values): zero them in V, so that 0 * value stays 0.
             if (kt * 64 + 63 > pos_last && r < 64 && kt * 64 + r > pos_last) {
@@ -226,26 +271,26 @@ __global__ void __launch_bounds__(ATC_THREADS, 2) attention_prefill_tc_kernel(co
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // P (and the zeros) are for the MMA to read
             tc_fence_before();
             mbar_arrive(&sh->p_ready);
-            if (!(ok = mbar_wait(&sh->pv_ready, i & 1, status, 11))) break;
-            tc_fence_after();
-#pragma unroll
-            for (int c = 0; c < HD / 32; ++c) {
-                float pv[32];
-                tc_ld32(tmem_o + lane_base + c * 32, pv);
-#pragma unroll
-                for (int d = 0; d < 32; ++d) o[c * 32 + d] = o[c * 32 + d] * alpha + pv[d];
-            }
         }
+        if (ok && n_kt > 0) ok = mbar_wait(&sh->pv_ready, (n_kt - 1) & 1, status, 11);
+        tc_fence_after();
         if (!ok) sh->failed = 1;
-        if (ok && r < nrows) {
+        if (ok) {
             const float inv = 1.0f / l;
             bf16* dst = a.out + (int64_t)(row0 + r) * (a.q_heads * HD) + head * HD;
+#pragma unroll 1
+            for (int c = 0; c < HD / 32; ++c) {
+                float ov[32];
+                tc_ld32(tmem_o + lane_base + c * 32, ov);      // every lane takes part in the load
+                if (r < nrows) {
 #pragma unroll
-            for (int d = 0; d < HD; d += 8) {
-                float v8[8];
+                    for (int d = 0; d < 32; d += 8) {
+                        float v8[8];
 #pragma unroll
-                for (int e = 0; e < 8; ++e) v8[e] = o[d + e] * inv;
-                tc_store8(dst + d, v8);
+                        for (int e = 0; e < 8; ++e) v8[e] = ov[d + e] * inv;
+                        tc_store8(dst + c * 32 + d, v8);
+                    }
+                }
             }
         }
     }
