@@ -335,6 +335,77 @@ def test_prefill_attention_bf16_equals_plain_kernel(q_heads, kv_heads, hd, windo
     assert (out[rows].double().cpu() - want).abs().max() / vmax < BF16_EPS
 
 
+def run_tc_attention(q_heads, kv_heads, hd, window, lens, pos0, seq_slots, seed=40, edit=None, q_edit=None):
+    """The tcgen05 prefill kernel and the plain kernel on the same cache and queries; returns
+    (out, ref, largest cached magnitude, q, storage, table, slots, pos)."""
+    o = ops()
+    n_slots = len(lens)
+    pages_per = max((p + l + 63) // 64 for p, l in zip(pos0, lens)) + 1
+    storage, table, view = make_cache(kv_heads, hd, n_slots * pages_per, n_slots, torch.bfloat16, pages_per)
+    fill_cache(storage, torch.bfloat16, seed)
+    if edit is not None:
+        edit(storage, table)
+    first = [0]
+    for l in lens:
+        first.append(first[-1] + l)
+    n = first[-1]
+    slots = torch.tensor(sum(([s] * l for s, l in zip(seq_slots, lens)), []), dtype=torch.int32, device=DEV)
+    pos = torch.tensor(sum((list(range(p, p + l)) for p, l in zip(pos0, lens)), []), dtype=torch.int32, device=DEV)
+    q = rnd((n, q_heads * hd), torch.bfloat16, seed + 1)
+    if q_edit is not None:
+        q_edit(q)
+    out = torch.full_like(q, 55.0)
+    tile_seq, tile_row0, n_tiles = tiles_for(first)
+    mk = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)   # noqa: E731
+    assert o.attention_tc_takes(view, torch.bfloat16)
+    o.attention_prefill_tcgen05(q, out, view, tile_seq, tile_row0, n_tiles, mk(first), mk(seq_slots), mk(pos0), q_heads,
+                                1 / math.sqrt(hd), window)
+    o.check_tc_status(q.device)
+    ref = torch.empty_like(q)
+    o.attention_rows(q, ref, view, slots, pos, n, q_heads, 1 / math.sqrt(hd), window)
+    return out, ref, float(storage.float().abs().max()), q, storage, table, slots, pos
+
+
+@pytest.mark.parametrize("q_heads,kv_heads,hd", [(8, 2, 64), (4, 1, 128), (3, 3, 64), (10, 5, 128)])
+@pytest.mark.parametrize("window", [0, 3, 64, 100])
+def test_prefill_attention_tcgen05_equals_plain_kernel(q_heads, kv_heads, hd, window):
+    """Unequal sequences, one continuing from position 70 and one of four tiles, slots in another
+    order than the rows: the tcgen05 kernel against the plain kernel and the float64 restatement."""
+    out, ref, vmax, q, storage, table, slots, pos = run_tc_attention(
+        q_heads, kv_heads, hd, window, [65, 1, 130, 500], [0, 7, 70, 3], [2, 0, 1, 3])
+    assert (out.float() - ref.float()).abs().max() / vmax < 2 * BF16_EPS
+    rows = [0, 63, 64, 65, 66, 130, 195, 196, 323, 324, 695]
+    n = q.shape[0]
+    want = plain_attention_over_cache(q.reshape(n, q_heads, hd)[rows], storage, table, slots[rows], pos[rows], q_heads,
+                                      kv_heads, hd, window)
+    assert (out[rows].double().cpu() - want).abs().max() / vmax < BF16_EPS
+
+
+@pytest.mark.parametrize("gain", [0.7, 40.0])
+def test_prefill_attention_tcgen05_late_large_key(gain):
+    """A key at position 300 scores far above everything before it for every later query.  With
+    the small gain the rows keep their reference maximum (the kernel raises it only past a
+    threshold); with the large one the output accumulated so far is rescaled in tensor memory.
+    Rows before 300 never see the key."""
+    hd, far = 128, 300
+
+    def edit(storage, table):
+        page = int(table[0, far // 64])
+        storage[page, 0, 0, far % 64] = gain                       # key: all components equal
+
+    def q_edit(q):
+        q[:, :hd] = q[:, :hd].abs()                                # head 0: positive queries, so the score is large
+
+    out, ref, vmax, q, storage, table, slots, pos = run_tc_attention(2, 1, hd, 0, [450], [0], [0], seed=70, edit=edit,
+                                                                     q_edit=q_edit)
+    assert (out.float() - ref.float()).abs().max() / vmax < 2 * BF16_EPS
+    if gain > 10:
+        page = int(table[0, far // 64])
+        value = storage[page, 1, 0, far % 64].float()
+        assert (out[far + 5, :hd].float() - value).abs().max() < 2 * BF16_EPS * vmax     # that key alone
+    assert torch.isfinite(out.float()).all()
+
+
 @pytest.mark.parametrize("q_heads,kv_heads,hd", [(4, 2, 16), (6, 2, 32), (5, 1, 48), (32, 8, 128), (20, 1, 64), (3, 3, 96)])
 @pytest.mark.parametrize("window", [0, 9, 200])
 @pytest.mark.parametrize("splits", [1, 2, 5, 13])

@@ -366,8 +366,9 @@ def check_tc_status(device) -> None:
     st = int(gemm_tc_status(device)[0])
     if st != 0:
         gemm_tc_status(device).zero_()
-        raise KernelError(f"a tcgen05 product gave up waiting on a barrier (code {st}: 1 copy, 2 MMA, 3 epilogue, "
-                          "4 accumulator); its output is not valid")
+        raise KernelError(f"a tcgen05 kernel gave up waiting on a barrier (code {st}; products: 1 copy, 2 MMA, "
+                          "3 epilogue, 4 accumulator; attention: 5 queries, 6 keys and values, 7 probabilities, "
+                          "8 and 11 output, 10 scores); its output is not valid")
 
 
 def gemm_tc_status(device) -> torch.Tensor:

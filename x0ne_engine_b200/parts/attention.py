@@ -27,8 +27,9 @@ def run_attention(ctx, q, out, view, n_rows, q_heads, scale, window):
         ops.attention_decode_bf16(q, out, view, ctx.row_slot, ctx.row_pos, n_rows, q_heads, scale, window, splits,
                                   scratch)
     else:
-        ops.attention_prefill_bf16(q, out, view, ctx.tile_seq, ctx.tile_row0, ctx.n_tiles, ctx.seq_first_row,
-                                   ctx.seq_slot, ctx.seq_pos0, q_heads, scale, window)
+        kernel = ops.attention_prefill_tcgen05 if ops.attention_tc_takes(view, q.dtype) else ops.attention_prefill_bf16
+        kernel(q, out, view, ctx.tile_seq, ctx.tile_row0, ctx.n_tiles, ctx.seq_first_row, ctx.seq_slot, ctx.seq_pos0,
+               q_heads, scale, window)
 
 
 def decode_splits(ctx, n_rows: int, kv_heads: int, q_heads: int) -> int:
