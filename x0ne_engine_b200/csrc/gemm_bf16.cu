@@ -39,9 +39,11 @@ __device__ __forceinline__ void cp_commit() { asm volatile("cp.async.commit_grou
 template <int N> __device__ __forceinline__ void cp_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
 
 // Each thread streams its 16-byte pieces of W through a private ring of DEPTH slots in shared
-// memory with cp.async: DEPTH chunks (2 rows x 16 bytes each, per weight set) are in flight per
+// memory with cp.async: DEPTH - 1 chunks (2 rows x 16 bytes each, per weight set) are in flight per
 // thread whatever the register allocator does, which is what hides the memory latency.  A thread
-// reads back only what it copied itself, so no barrier is needed inside the k loop.
+// reads back only what it copied itself, so no barrier is needed inside the k loop.  A block owns
+// the tiles (16 weight rows each) blockIdx.x, blockIdx.x + gridDim.x, ...; the copies run ahead
+// across the tile boundary, so the stream does not drain while a tile's partial sums are reduced.
 template <int MT, typename OutT, bool SWIGLU, int DEPTH>
 __global__ void __launch_bounds__(SM_WARPS * 32) gemm_smallm_kernel(const bf16* __restrict__ W, const bf16* __restrict__ X,
                                                                     OutT* __restrict__ Y, int M, int N, int K, int ldy,
@@ -54,50 +56,66 @@ __global__ void __launch_bounds__(SM_WARPS * 32) gemm_smallm_kernel(const bf16* 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
     const int chunks = (K + 31) / 32;
     const int my_chunks = chunks > warp ? (chunks - warp + SM_WARPS - 1) / SM_WARPS : 0;   // chunks warp, warp + 8, ...
+    const int my_tiles = (int)blockIdx.x < n_tiles ? (n_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
     auto slot = [&](int d, int s, int h) -> uint4* { return ring + (d * SLOTS + s * 2 + h) * (SM_WARPS * 32) + tid; };
     auto xslot = [&](int d, int j) -> uint4* { return ring + (d * SLOTS + SETS * 2 + j) * (SM_WARPS * 32) + tid; };
 
     pdl_launch_dependents();
-    bool first_tile = true;
-    for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
-        const int n0 = tile * 16;
-        const bf16* wrow[SETS][2];
-        bool wok[SETS][2];
+
+    // the copies' cursor: tile p_tile of this block, chunk p_chunk of this warp, ring slot p_slot
+    int p_tile = 0, p_chunk = 0, p_slot = 0;
+    const bool streams = my_chunks > 0 && my_tiles > 0;
+    auto issue_w = [&](int tile_j, int i, int d) {
+        const int n0 = ((int)blockIdx.x + tile_j * (int)gridDim.x) * 16;
+        const int k = (warp + i * SM_WARPS) * 32 + 8 * t;
+        const bool kok = k < K;
 #pragma unroll
-        for (int s = 0; s < SETS; ++s)
+        for (int h = 0; h < 2; ++h) {
+            const int n = n0 + g + 8 * h;
+            const bool ok = kok && n < N;
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                const int n = n0 + g + 8 * h;
-                wok[s][h] = n < N;
-                wrow[s][h] = W + (int64_t)(s * N + (wok[s][h] ? n : 0)) * K;
-            }
-        auto issue_w = [&](int i) {
-            if (i < my_chunks) {
-                const int k = (warp + i * SM_WARPS) * 32 + 8 * t;
-                const bool kok = k < K;
+            for (int s = 0; s < SETS; ++s)
+                cp_async16_zfill(slot(d, s, h), W + (ok ? (int64_t)(s * N + n) * K + k : 0), ok ? 16 : 0);
+        }
+    };
+    auto issue_x = [&](int i, int d) {
+        const int k = (warp + i * SM_WARPS) * 32 + 8 * t;
 #pragma unroll
-                for (int s = 0; s < SETS; ++s)
+        for (int j = 0; j < MT; ++j) {
+            const int m = 8 * j + g;
+            const bool ok = k < K && m < M;
+            cp_async16_zfill(xslot(d, j), X + (ok ? (int64_t)m * K + k : 0), ok ? 16 : 0);
+        }
+    };
+    auto advance = [&]() {
+        if (++p_chunk == my_chunks) {
+            p_chunk = 0;
+            ++p_tile;
+        }
+        p_slot = p_slot + 1 == DEPTH ? 0 : p_slot + 1;
+    };
+
+    // The weights do not depend on the kernel before this one: the first chunks are requested
+    // before waiting for it (their copies then all belong to the first commit group, which is
+    // harmless: that group is waited for first).
+    {
+        int jt = 0, ic = 0;
 #pragma unroll
-                    for (int h = 0; h < 2; ++h)
-                        cp_async16_zfill(slot(i % DEPTH, s, h), wrow[s][h] + (kok ? k : 0), (kok && wok[s][h]) ? 16 : 0);
-            }
-        };
-        auto issue_x = [&](int i) {
-            if (i < my_chunks) {
-                const int k = (warp + i * SM_WARPS) * 32 + 8 * t;
+        for (int d = 0; d < DEPTH - 1; ++d) {
+            if (streams && jt < my_tiles) issue_w(jt, ic, d);
+            if (++ic >= my_chunks) { ic = 0; ++jt; }
+        }
+    }
+    pdl_wait();
 #pragma unroll
-                for (int j = 0; j < MT; ++j) {
-                    const int m = 8 * j + g;
-                    const bool ok = k < K && m < M;
-                    cp_async16_zfill(xslot(i % DEPTH, j), X + (ok ? (int64_t)m * K + k : 0), ok ? 16 : 0);
-                }
-            }
-            cp_commit();
-        };
-        auto issue = [&](int i) {
-            issue_w(i);
-            issue_x(i);
-        };
+    for (int d = 0; d < DEPTH - 1; ++d) {
+        if (streams && p_tile < my_tiles) issue_x(p_chunk, d);
+        cp_commit();
+        if (streams) advance();
+    }
+
+    int c_slot = 0;
+    for (int tile_j = 0; tile_j < my_tiles; ++tile_j) {
         float acc[SETS][MT][4];
 #pragma unroll
         for (int s = 0; s < SETS; ++s)
@@ -105,36 +123,30 @@ __global__ void __launch_bounds__(SM_WARPS * 32) gemm_smallm_kernel(const bf16* 
             for (int j = 0; j < MT; ++j)
 #pragma unroll
                 for (int i = 0; i < 4; ++i) acc[s][j][i] = 0.f;
-
-        // The weights do not depend on the kernel before this one: the first chunks of the first
-        // tile are requested before waiting for it (their copies then all belong to the first
-        // commit group, which is harmless: that group is waited for first).
-#pragma unroll
-        for (int i = 0; i < DEPTH - 1; ++i) issue_w(i);
-        if (first_tile) {
-            pdl_wait();
-            first_tile = false;
-        }
-#pragma unroll
-        for (int i = 0; i < DEPTH - 1; ++i) issue_x(i);
         for (int i = 0; i < my_chunks; ++i) {
-            issue(i + DEPTH - 1);
+            if (p_tile < my_tiles) {
+                issue_w(p_tile, p_chunk, p_slot);
+                issue_x(p_chunk, p_slot);
+            }
+            cp_commit();
+            advance();
             cp_wait<DEPTH - 1>();
             uint4 b[MT];
 #pragma unroll
-            for (int j = 0; j < MT; ++j) b[j] = *xslot(i % DEPTH, j);
+            for (int j = 0; j < MT; ++j) b[j] = *xslot(c_slot, j);
 #pragma unroll
             for (int s = 0; s < SETS; ++s) {
-                const uint4 a0 = *slot(i % DEPTH, s, 0), a1 = *slot(i % DEPTH, s, 1);
+                const uint4 a0 = *slot(c_slot, s, 0), a1 = *slot(c_slot, s, 1);
 #pragma unroll
                 for (int j = 0; j < MT; ++j) {
                     mma16816(acc[s][j], a0.x, a1.x, a0.y, a1.y, b[j].x, b[j].y);
                     mma16816(acc[s][j], a0.z, a1.z, a0.w, a1.w, b[j].z, b[j].w);
                 }
             }
+            c_slot = c_slot + 1 == DEPTH ? 0 : c_slot + 1;
         }
-        cp_wait<0>();
         // partials: part[warp][set][j][row * 8 + col], row = weight row in the tile, col = m in the tile
+        const int n0 = ((int)blockIdx.x + tile_j * (int)gridDim.x) * 16;
 #pragma unroll
         for (int s = 0; s < SETS; ++s)
 #pragma unroll
@@ -166,6 +178,7 @@ __global__ void __launch_bounds__(SM_WARPS * 32) gemm_smallm_kernel(const bf16* 
         }
         __syncthreads();
     }
+    cp_wait<0>();
 }
 
 template <int MT, typename OutT, bool SWIGLU>
@@ -188,9 +201,11 @@ static int launch_smallm(const bf16* W, const bf16* X, OutT* Y, int M, int N, in
         if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, SM_WARPS * 32, SMEM) != cudaSuccess || n < 1) n = 1;
         per_sm = n;
     }
+    // Every block gets the same number of tiles (but for the remainder), and no more blocks are
+    // launched than are resident at once: the blocks then end together.
     const int resident = sms * per_sm;
-    // All tiles at once if they fit; else one block per resident slot, each walking its share of tiles.
-    const int grid = n_tiles < resident ? n_tiles : resident;
+    const int tiles_per_block = (n_tiles + resident - 1) / resident;
+    const int grid = (n_tiles + tiles_per_block - 1) / tiles_per_block;
     x0ne_launch(gemm_smallm_kernel<MT, OutT, SWIGLU, DEPTH>, dim3(grid), dim3(SM_WARPS * 32), SMEM, stream, W, X, Y, M, N, K, ldy, n_tiles);
     X0NE_LAUNCH_CHECK();
 }
