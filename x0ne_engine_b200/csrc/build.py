@@ -11,6 +11,7 @@ from __future__ import annotations
 
 import ctypes
 import hashlib
+import shlex
 import os
 import shutil
 import subprocess
@@ -26,6 +27,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",
               "--expt-relaxed-constexpr"]
+# extra compiler flags for experiments (-D...); they are part of the library's hash
+NVCC_FLAGS += shlex.split(os.environ.get("X0NE_NVCC_FLAGS", ""))
 
 # module name -> sources.  `core` is all a 32-bit run needs; `fast` holds the bfloat16 kernels.
 MODULES: Dict[str, List[str]] = {
