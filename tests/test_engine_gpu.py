@@ -265,6 +265,36 @@ def test_stop_tokens_and_early_endings_in_generation(dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("decode", ["graph", "eager"])
+def test_running_one_step_ahead_changes_no_token(dtype, decode):
+    """The batch runner queues the next step before the host has read the current picks.  Each
+    request here stops at a token of its own (which the device does not know, so the ended rows are
+    stepped once more than needed), in two batches one after the other: the tokens are those of a
+    runner that waits for every step, and of the free run cut at the stop."""
+    from x0ne_engine_b200 import Model, SamplingParams
+    from x0ne_engine_b200.engine.decode import DeviceBatch
+    from x0ne_engine_b200.engine.generate import Generator
+    folder = model_folder("B", "float32" if dtype == "float32" else "bfloat16")
+    prompts = prompts_for(plain_model(folder)[0]["vocab"], [9, 4, 21, 6, 13, 30], seed=18)
+    m = Model.from_folder(folder, dtype=dtype, max_batch=4, max_ctx=128)
+    free = m.generate(prompts, max_tokens=24, stop_token_ids=()).tokens
+    params = [SamplingParams(max_tokens=24, stop_token_ids=(f[2 + 3 * i],)) for i, f in enumerate(free)]
+    outs = []
+    for ahead in (True, False):
+        def factory():
+            r = DeviceBatch(m.engine, 4, cuda_graph=decode == "graph")
+            r.run_ahead = ahead
+            return r
+        done = Generator(m.engine, max_batch=4, runner_factory=factory).generate(prompts, params)
+        outs.append([c.tokens for c in done])
+        assert all(c.finish_reason == "stop" for c in done)
+        assert m.engine.cache.slots.held() == 0
+    assert outs[0] == outs[1]
+    for f, got, q in zip(free, outs[0], params):
+        assert got == f[:f.index(q.stop_token_ids[0])]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 def test_sampled_generation_follows_seed_and_ignores_batch_mates(dtype):
     from x0ne_engine_b200 import Model, SamplingParams
     folder = model_folder("B", "float32" if dtype == "float32" else "bfloat16")

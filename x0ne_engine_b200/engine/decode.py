@@ -7,6 +7,12 @@ copy, and its launches are captured once per batch size into a CUDA graph and re
 library engine does for its single sequence (x0ne-core/runtime/src/engine.rs:484-501,
 1095-1132).  Per step the host reads back one int32 per live sequence.
 
+Because a step needs nothing from the host, the step after the one whose picks are being read is
+already queued: `step(live)` returns the picks of the step it was asked for and leaves the next
+one (for the same rows) running.  A row that the loop ends on those picks has then been stepped
+once more than needed; the device has marked it finished where it could know (stop token, budget),
+and either way its extra pick is dropped.  So the GPU never waits for the host's decisions.
+
 When sequences finish, the live rows are compacted on the device and the graph of the smaller
 batch size is used.
 """
@@ -43,7 +49,11 @@ class DeviceBatch:
         self.seq_first_row = torch.arange(max_batch + 1, **i32)
         self.want_rows = torch.arange(max_batch, **i32)
         self.logits = torch.empty((max_batch, engine.vocab_size), dtype=torch.float32, device=dev)
-        self._out_host = torch.zeros(max_batch, dtype=torch.int32).pin_memory()
+        self._out_host = [torch.zeros(max_batch, dtype=torch.int32).pin_memory() for _ in range(2)]
+        self._out_event = [torch.cuda.Event(), torch.cuda.Event()]
+        self._queued = 0                # steps queued so far in this batch (picks buffer = count % 2)
+        self._ahead: Optional[List[int]] = None    # rows of the step that is queued and not read yet
+        self.run_ahead = True           # queue the next step before reading the current one's picks
         self._per_row = [self.tokens, self.row_slot, self.row_pos, self.counter, self.finished, self.budget,
                          self.temperature, self.top_p, self.seed]
         self.stop_ids: Optional[torch.Tensor] = None
@@ -91,10 +101,44 @@ class DeviceBatch:
         self.stop_ids = torch.tensor(common, dtype=torch.int32, device=eng.device) if common else None
         logits = eng.step(self.slots, [r.prompt for r in rows])
         self._sample(logits, n)
-        return self._read(n)
+        self._ahead = None
+        return self._read(self._queue_read(n), n)
 
     def step(self, live: Sequence[int]) -> List[int]:
         live = list(live)
+        if self._ahead is None:
+            self._queue_step(live)
+        ahead, k = self._ahead, self._queued - 1           # the queued step, and where its picks go
+        if ahead != live and not set(live) <= set(ahead):
+            raise GenerationError("a decode step was asked for rows that are not in the batch any more")
+        self._ahead = None
+        if self.run_ahead:
+            # rows whose budget the queued step uses up need no step after it
+            nxt = [i for i in live if len(self.rows[i].generated) + 1 < self.rows[i].budget]
+            if nxt:
+                self._queue_step(nxt)                       # runs while the host reads and decides
+        picks = self._read(k, len(ahead))
+        if ahead == live:
+            return picks
+        where = {row: j for j, row in enumerate(ahead)}
+        return [picks[where[i]] for i in live]
+
+    def close(self) -> None:
+        if self._ahead is not None:
+            torch.cuda.current_stream().synchronize()       # a step is still running on these slots
+            self._ahead = None
+        for s in self.slots:
+            self.engine.free_sequence(s)
+        self.slots, self.rows, self.live = [], (), []
+
+    # ------------------------------------------------------------------ pieces
+    def _sample(self, logits: torch.Tensor, n: int) -> None:
+        ops.sample(logits, n, self.out_token, temperature=self.temperature, top_p=self.top_p, seed=self.seed,
+                   draw_counter=self.counter, stop_ids=self.stop_ids, finished=self.finished, budget=self.budget,
+                   next_token=self.tokens, next_pos=self.row_pos)
+
+    def _queue_step(self, live: List[int]) -> None:
+        """Queues one decode step for `live` and the copy of its picks to the host."""
         if live != self.live:
             self._compact(live)
         n = len(live)
@@ -109,23 +153,19 @@ class DeviceBatch:
             self.eager_steps += 1
         for i in live:
             self.engine.cache.lengths[self.slots[i]] += 1
-        return self._read(n)
+        self._queue_read(n)
+        self._ahead = live
 
-    def close(self) -> None:
-        for s in self.slots:
-            self.engine.free_sequence(s)
-        self.slots, self.rows, self.live = [], (), []
+    def _queue_read(self, n: int) -> int:
+        k = self._queued
+        self._queued += 1
+        self._out_host[k % 2][:n].copy_(self.out_token[:n], non_blocking=True)
+        self._out_event[k % 2].record()
+        return k
 
-    # ------------------------------------------------------------------ pieces
-    def _sample(self, logits: torch.Tensor, n: int) -> None:
-        ops.sample(logits, n, self.out_token, temperature=self.temperature, top_p=self.top_p, seed=self.seed,
-                   draw_counter=self.counter, stop_ids=self.stop_ids, finished=self.finished, budget=self.budget,
-                   next_token=self.tokens, next_pos=self.row_pos)
-
-    def _read(self, n: int) -> List[int]:
-        self._out_host[:n].copy_(self.out_token[:n], non_blocking=True)
-        torch.cuda.current_stream().synchronize()
-        return self._out_host[:n].tolist()
+    def _read(self, k: int, n: int) -> List[int]:
+        self._out_event[k % 2].synchronize()
+        return self._out_host[k % 2][:n].tolist()
 
     def _compact(self, live: List[int]) -> None:
         where = {row: k for k, row in enumerate(self.live)}
