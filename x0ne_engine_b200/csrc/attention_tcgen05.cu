@@ -36,8 +36,9 @@ struct AttnTcArgs {
 
 struct AttnTcShared {
     uint64_t q_full;
-    uint64_t kv_full[2];
-    uint64_t s_ready;
+    uint64_t k_full[2];
+    uint64_t v_full[2];
+    uint64_t s_ready[2];
     uint64_t p_ready;
     uint64_t pv_ready;
     uint32_t tmem_base;
@@ -131,9 +132,11 @@ __global__ void __launch_bounds__(ATC_THREADS, 2) attention_prefill_tc_kernel(co
     pdl_launch_dependents();
     if (threadIdx.x == 0) {
         mbar_init(&sh->q_full, 1);
-        mbar_init(&sh->kv_full[0], 1);
-        mbar_init(&sh->kv_full[1], 1);
-        mbar_init(&sh->s_ready, 1);
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&sh->k_full[b], 1);
+            mbar_init(&sh->v_full[b], 1);
+            mbar_init(&sh->s_ready[b], 1);
+        }
         mbar_init(&sh->p_ready, 128);
         mbar_init(&sh->pv_ready, 1);
         sh->failed = (tc_smem(atc_raw) & 1023u) != 0 ? 1 : 0;      // the swizzle needs 1024-byte aligned tiles
@@ -150,54 +153,91 @@ __global__ void __launch_bounds__(ATC_THREADS, 2) attention_prefill_tc_kernel(co
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = sh->tmem_base;
-    const uint32_t tmem_s = tmem, tmem_o = tmem + 64;       // S: 64 columns; O_tile: HD columns
+    const uint32_t tmem_s = tmem, tmem_o = tmem + 128;       // S: two buffers of 64 columns; O: HD columns
 
     if (warp == 4) {
         if (lane == 0 && !sh->failed) {
+            // Page numbers are looked up well before the copies that need them (the table is older
+            // than the kernel before this one): a lookup in front of a copy would be a dependent
+            // global load in this thread's loop.
+            auto page_of = [&](int i) -> int {
+                if (i >= n_kt) return 0;
+                const int pg = cache.page_table[(int64_t)slot * cache.table_stride + ((kt_lo + i) % cache.ring_pages)];
+                return (pg < 0 || pg >= cache.n_pages) ? 0 : pg;      // never out of range for a sequence that holds its pages
+            };
+            const int pg0 = page_of(0), pg1 = page_of(1);
+            int pg_cur = page_of(2);                                  // the page of tile i + 2 in iteration i
             pdl_wait();      // q and the newest cache rows were written by the kernel before this one
             mbar_expect_tx(&sh->q_full, Q_BYTES);
 #pragma unroll
             for (int nb = 0; nb < NB; ++nb) tma_load_2d(qs + nb * 128 * 128, &map_q, head * HD + nb * 64, row0, &sh->q_full);
-            auto load_kv = [&](int i) {
+            auto load_k = [&](int i, int page) {
                 const int st = i & 1;
-                int page = cache.page_table[(int64_t)slot * cache.table_stride + ((kt_lo + i) % cache.ring_pages)];
-                if (page < 0 || page >= cache.n_pages) page = 0;      // never for a sequence that holds its pages
                 const int krow = ((page * 2 + 0) * cache.kv_heads + kh) * 64;
-                const int vrow = ((page * 2 + 1) * cache.kv_heads + kh) * 64;
-                mbar_expect_tx(&sh->kv_full[st], 2 * KV_BYTES);
+                mbar_expect_tx(&sh->k_full[st], KV_BYTES);
 #pragma unroll
-                for (int nb = 0; nb < NB; ++nb) {
-                    tma_load_2d(ks + st * KV_BYTES + nb * 64 * 128, &map_kv, nb * 64, krow, &sh->kv_full[st]);
-                    tma_load_2d(vs + st * KV_BYTES + nb * 64 * 128, &map_kv, nb * 64, vrow, &sh->kv_full[st]);
-                }
+                for (int nb = 0; nb < NB; ++nb)
+                    tma_load_2d(ks + st * KV_BYTES + nb * 64 * 128, &map_kv, nb * 64, krow, &sh->k_full[st]);
             };
-            load_kv(0);
-            if (n_kt > 1) load_kv(1);
+            auto load_v = [&](int i, int page) {
+                const int st = i & 1;
+                const int vrow = ((page * 2 + 1) * cache.kv_heads + kh) * 64;
+                mbar_expect_tx(&sh->v_full[st], KV_BYTES);
+#pragma unroll
+                for (int nb = 0; nb < NB; ++nb)
+                    tma_load_2d(vs + st * KV_BYTES + nb * 64 * 128, &map_kv, nb * 64, vrow, &sh->v_full[st]);
+            };
             // instruction descriptors: f32 accumulate, bf16 operands, M = 128
             const uint32_t idesc_qk = (1u << 4) | (1u << 7) | (1u << 10) | ((64u >> 3) << 17) | ((128u >> 4) << 24);
             const uint32_t idesc_pv = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | (((uint32_t)HD >> 3) << 17) | ((128u >> 4) << 24);
-            bool ok = mbar_wait(&sh->q_full, 0, status, 5);
-            for (int i = 0; i < n_kt && ok; ++i) {
-                const int st = i & 1;
-                if (!(ok = mbar_wait(&sh->kv_full[st], (i >> 1) & 1, status, 6))) break;
-                tc_fence_after();
-                const uint32_t kb = tc_smem(ks + st * KV_BYTES), vb = tc_smem(vs + st * KV_BYTES), qb = tc_smem(qs);
+            const uint32_t qb = tc_smem(qs);
+            auto issue_qk = [&](int i) {                 // S[i & 1] = Q K(i)^T
+                const uint32_t kb = tc_smem(ks + (i & 1) * KV_BYTES);
 #pragma unroll
                 for (int kk = 0; kk < HD / 16; ++kk)
-                    tc_mma(tmem_s, tc_desc(qb + (kk / 4) * 128 * 128 + (kk % 4) * 32),
+                    tc_mma(tmem_s + (i & 1) * 64, tc_desc(qb + (kk / 4) * 128 * 128 + (kk % 4) * 32),
                            tc_desc(kb + (kk / 4) * 64 * 128 + (kk % 4) * 32), idesc_qk, kk > 0 ? 1u : 0u);
-                tc_commit(&sh->s_ready);
-                if (!(ok = mbar_wait(&sh->p_ready, i & 1, status, 7))) break;
+                tc_commit(&sh->s_ready[i & 1]);
+            };
+            load_k(0, pg0);
+            load_v(0, pg0);
+            if (n_kt > 1) {
+                load_k(1, pg1);
+                load_v(1, pg1);
+            }
+            bool ok = mbar_wait(&sh->q_full, 0, status, 5);
+            if (ok) ok = mbar_wait(&sh->k_full[0], 0, status, 6);
+            if (ok) {
                 tc_fence_after();
+                issue_qk(0);
+            }
+            // Order of this thread's work for page i: the scores of page i + 1 (so that they are
+            // ready when the softmax threads finish page i), then O += P(i) V(i), then the copies
+            // that the finished products make room for.
+            for (int i = 0; i < n_kt && ok; ++i) {
+                const int st = i & 1;
+                const int pg_next = page_of(i + 3);
+                if (i + 1 < n_kt) {
+                    if (!(ok = mbar_wait(&sh->s_ready[st], (i >> 1) & 1, status, 12))) break;     // K(i) has been read
+                    if (i + 2 < n_kt) load_k(i + 2, pg_cur);
+                    if (!(ok = mbar_wait(&sh->k_full[st ^ 1], ((i + 1) >> 1) & 1, status, 6))) break;
+                    tc_fence_after();
+                    issue_qk(i + 1);      // its buffer was read by the softmax of page i - 1, which has arrived (below)
+                }
+                if (!(ok = mbar_wait(&sh->p_ready, i & 1, status, 7))) break;
+                if (!(ok = mbar_wait(&sh->v_full[st], (i >> 1) & 1, status, 13))) break;
+                tc_fence_after();
+                const uint32_t vb = tc_smem(vs + st * KV_BYTES);
 #pragma unroll
                 for (int kk = 0; kk < 4; ++kk)
                     tc_mma(tmem_o, tc_desc(tc_smem(ps) + kk * 32), tc_desc_nmajor(vb + kk * 16 * 128, 64 * 128), idesc_pv,
                            (i > 0 || kk > 0) ? 1u : 0u);          // the output accumulates in tensor memory over the pages
                 tc_commit(&sh->pv_ready);
-                if (i + 2 < n_kt) {       // the stage is free once both products of this page are done
+                if (i + 2 < n_kt) {       // V's stage is free once this product is done
                     if (!(ok = mbar_wait(&sh->pv_ready, i & 1, status, 8))) break;
-                    load_kv(i + 2);
+                    load_v(i + 2, pg_cur);
                 }
+                pg_cur = pg_next;
             }
             if (!ok) sh->failed = 1;
         }
@@ -210,10 +250,10 @@ __global__ void __launch_bounds__(ATC_THREADS, 2) attention_prefill_tc_kernel(co
         bool ok = !sh->failed;
         for (int i = 0; i < n_kt && ok; ++i) {
             const int kt = kt_lo + i;
-            if (!(ok = mbar_wait(&sh->s_ready, i & 1, status, 10))) break;
-            tc_fence_after();      // S of this page is complete, and so is every product issued before it
+            if (!(ok = mbar_wait(&sh->s_ready[i & 1], (i >> 1) & 1, status, 10))) break;
+            tc_fence_after();
             float s[64];
-            tc_ld64(tmem_s + lane_base, s);
+            tc_ld64(tmem_s + (i & 1) * 64 + lane_base, s);
             const bool edge = (kt * 64 + 63 > pos_first) || (a.window > 0 && kt * 64 <= pos_last - a.window);
             float mx = -INFINITY;
 #pragma unroll
@@ -226,10 +266,27 @@ __global__ void __launch_bounds__(ATC_THREADS, 2) attention_prefill_tc_kernel(co
             }
             // raise the reference only when it is first set or falls too far behind
             const bool raise = mx > m_ref && (m_ref == -INFINITY || (mx - m_ref) * sc > ATC_RESCALE_LOG2);
-            if (i > 0 && __any_sync(0xffffffffu, raise && m_ref != -INFINITY)) {
-                // rescale this warp's rows of the accumulator (rows that keep their reference: factor 1)
-                const float alpha = (raise && m_ref != -INFINITY) ? ex2_approx((m_ref - mx) * sc) : 1.f;
-                l *= alpha;
+            const bool shrink = raise && m_ref != -INFINITY;          // what this row has accumulated must be rescaled
+            const bool rescale = i > 0 && __any_sync(0xffffffffu, shrink);
+            const float alpha = shrink ? ex2_approx((m_ref - mx) * sc) : 1.f;
+            if (raise) m_ref = mx;
+            const float neg = m_ref == -INFINITY ? 0.f : -m_ref * sc;
+            float sum = 0.f;
+            uint32_t w[32];                                           // the row of P, bfloat16 pairs
+#pragma unroll
+            for (int e = 0; e < 32; ++e) {
+                const float p0 = ex2_approx(fmaf(s[2 * e], sc, neg)), p1 = ex2_approx(fmaf(s[2 * e + 1], sc, neg));
+                sum += p0 + p1;
+                __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+                w[e] = *reinterpret_cast<uint32_t*>(&h);
+            }
+            l = l * alpha + sum;
+            // P's buffer and the accumulator belong to the product of the page before until it is done
+            if (i > 0) {
+                if (!(ok = mbar_wait(&sh->pv_ready, (i - 1) & 1, status, 14))) break;
+                tc_fence_after();
+            }
+            if (rescale) {       // this warp's rows of the accumulator (rows that keep their reference: factor 1)
 #pragma unroll 1
                 for (int c = 0; c < HD / 32; ++c) {
                     float ov[32];
@@ -240,26 +297,16 @@ __global__ void __launch_bounds__(ATC_THREADS, 2) attention_prefill_tc_kernel(co
                 }
                 asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             }
-            if (raise) m_ref = mx;
-            const float neg = m_ref == -INFINITY ? 0.f : -m_ref * sc;
-            float sum = 0.f;
             // P row -> shared memory, 16 bytes (8 keys) at a time, chunk c at position c ^ (row & 7)
             unsigned char* prow = ps + r * 128;
 #pragma unroll
-            for (int c = 0; c < 8; ++c) {
-                uint32_t w[4];
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const float p0 = ex2_approx(fmaf(s[c * 8 + 2 * e], sc, neg)), p1 = ex2_approx(fmaf(s[c * 8 + 2 * e + 1], sc, neg));
-                    sum += p0 + p1;
-                    __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
-                    w[e] = *reinterpret_cast<uint32_t*>(&h);
-                }
-                *reinterpret_cast<uint4*>(prow + ((c ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
-            }
-            l += sum;
+            for (int c = 0; c < 8; ++c)
+                *reinterpret_cast<uint4*>(prow + ((c ^ (r & 7)) << 4)) = make_uint4(w[4 * c], w[4 * c + 1], w[4 * c + 2], w[4 * c + 3]);
             // The page's rows past the sequence's last position may hold anything (an earlier
             // sequence's values): zero them in V, so that 0 * value stays 0.
+            if (kt * 64 + 63 > pos_last) {
+                if (!(ok = mbar_wait(&sh->v_full[i & 1], (i >> 1) & 1, status, 15))) break;     // V has landed
+            }
             if (kt * 64 + 63 > pos_last && r < 64 && kt * 64 + r > pos_last) {
                 unsigned char* vrow = vs + (i & 1) * KV_BYTES + r * 128;
 #pragma unroll

@@ -367,8 +367,8 @@ def check_tc_status(device) -> None:
     if st != 0:
         gemm_tc_status(device).zero_()
         raise KernelError(f"a tcgen05 kernel gave up waiting on a barrier (code {st}; products: 1 copy, 2 MMA, "
-                          "3 epilogue, 4 accumulator; attention: 5 queries, 6 keys and values, 7 probabilities, "
-                          "8 and 11 output, 10 scores); its output is not valid")
+                          "3 epilogue, 4 accumulator; attention: 5 queries, 6 keys, 13 and 15 values, 7 probabilities, "
+                          "8, 11 and 14 output, 10 and 12 scores); its output is not valid")
 
 
 def gemm_tc_status(device) -> torch.Tensor:
