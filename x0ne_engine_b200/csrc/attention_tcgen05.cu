@@ -255,15 +255,20 @@ __global__ void __launch_bounds__(ATC_THREADS, 2) attention_prefill_tc_kernel(co
             float s[64];
             tc_ld64(tmem_s + (i & 1) * 64 + lane_base, s);
             const bool edge = (kt * 64 + 63 > pos_first) || (a.window > 0 && kt * 64 <= pos_last - a.window);
-            float mx = -INFINITY;
+            if (edge) {
 #pragma unroll
-            for (int c = 0; c < 64; ++c) {
-                if (edge) {
+                for (int c = 0; c < 64; ++c) {
                     const int j = kt * 64 + c;
                     if (j > p || (a.window > 0 && j <= p - a.window)) s[c] = -INFINITY;
                 }
-                mx = fmaxf(mx, s[c]);
             }
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};      // four chains instead of one
+#pragma unroll
+            for (int c = 0; c < 64; c += 4) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) mx4[e] = fmaxf(mx4[e], s[c + e]);
+            }
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
             // raise the reference only when it is first set or falls too far behind
             const bool raise = mx > m_ref && (m_ref == -INFINITY || (mx - m_ref) * sc > ATC_RESCALE_LOG2);
             const bool shrink = raise && m_ref != -INFINITY;          // what this row has accumulated must be rescaled
@@ -271,16 +276,16 @@ __global__ void __launch_bounds__(ATC_THREADS, 2) attention_prefill_tc_kernel(co
             const float alpha = shrink ? ex2_approx((m_ref - mx) * sc) : 1.f;
             if (raise) m_ref = mx;
             const float neg = m_ref == -INFINITY ? 0.f : -m_ref * sc;
-            float sum = 0.f;
+            float sum4[4] = {0.f, 0.f, 0.f, 0.f};
             uint32_t w[32];                                           // the row of P, bfloat16 pairs
 #pragma unroll
             for (int e = 0; e < 32; ++e) {
                 const float p0 = ex2_approx(fmaf(s[2 * e], sc, neg)), p1 = ex2_approx(fmaf(s[2 * e + 1], sc, neg));
-                sum += p0 + p1;
+                sum4[e & 3] += p0 + p1;
                 __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
                 w[e] = *reinterpret_cast<uint32_t*>(&h);
             }
-            l = l * alpha + sum;
+            l = l * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
             // P's buffer and the accumulator belong to the product of the page before until it is done
             if (i > 0) {
                 if (!(ok = mbar_wait(&sh->pv_ready, (i - 1) & 1, status, 14))) break;
