@@ -1,23 +1,29 @@
 // Causal GQA flash attention for passes with many rows, on the 5th-generation tensor cores:
 // both products of a tile (S = Q K^T and P V) are tcgen05.mma with their results in tensor memory,
-// Q and the cache pages come to shared memory by TMA, and the softmax runs in registers, one
-// thread per query row.  Same arithmetic as the mma.sync kernel of attention_bf16.cu (formulas:
-// x0ne-core/kernels/cuda/attention.cu:20-59,138-157): scores, running max and sum, exponentials
+// Q and the cache pages come to shared memory by TMA, and the softmax runs in registers, two
+// threads per query row.  Same arithmetic as the mma.sync kernel of attention_bf16.cu (formulas:
+// x0ne-core/kernels/cuda/attention.cu:20-59,138-157): scores, maximum and sum, exponentials
 // and the output accumulator in float32, P rounded to bfloat16 for the second product, one
 // rounding of the output at the end.  head_dim 64 or 128; other sizes use the mma.sync kernel.
 //
 // A block takes one tile of up to 128 query rows of one sequence and one q head (grid: q heads x
 // tiles, longest contexts first) and walks the cache pages (64 keys) the tile can see:
-//   * control thread (warp 4): TMA loads of Q (once) and of each page's K and V tiles (two stages,
-//     128-byte swizzle; a page of one kv head is 64 consecutive rows of the cache seen as one long
-//     [rows, head_dim] matrix); issues S = Q K^T (M 128, N 64, K 16 x head_dim/16) and, when the
-//     softmax threads have written P, O += P V (M 128, N head_dim, K 16 x 4; V is the N-major
-//     operand, straight from the page as it lies in the cache).
-//   * softmax threads (warps 0-3, thread = row): read S from tensor memory, mask, update the row's
-//     reference maximum and sum, and write P = 2^((s - reference) * scale) to shared memory in the
-//     swizzled layout the MMA reads.  The output accumulates in tensor memory across the pages (the
-//     MMA adds to it); it is rescaled there, by the softmax threads, only when a row's maximum has
-//     grown by more than 2^8 over its reference, and divided by the row's sum at the end.
+//   * QK warp (warp 8): TMA loads of Q (once) and of each page's K tile (two stages, 128-byte
+//     swizzle; a page of one kv head is 64 consecutive rows of the cache seen as one long
+//     [rows, head_dim] matrix); issues S(i) = Q K(i)^T (M 128, N 64, K 16 x head_dim/16) into one of
+//     two score buffers in tensor memory as soon as the softmax threads have read that buffer, so
+//     the scores of page i + 1 are computed while page i is in the softmax.
+//   * PV warp (warp 9): TMA loads of the V tiles (two stages); when the softmax threads have
+//     written P(i) it issues O += P(i) V(i) (M 128, N head_dim, K 16 x 4; V is the N-major operand,
+//     straight from the page as it lies in the cache).
+//     Both warps run their loops with all lanes and let one elected lane issue; every lane comes
+//     back together (__syncwarp) before any of them waits for what that lane had to ask for.
+//   * softmax threads (warps 0-7; warps w and w + 4 share rows 32 (w % 4) ... + 31 and take one
+//     half of a page's keys each): read S from tensor memory, mask, agree on the row's reference
+//     maximum, and write P = 2^((s - reference) * scale) to shared memory in the swizzled layout
+//     the MMA reads.  The output accumulates in tensor memory across the pages (the MMA adds to
+//     it); it is rescaled there, by the softmax threads, only when a row's maximum has grown by
+//     more than 2^8 over its reference, and divided by the row's sum at the end.
 // Every barrier wait is bounded; when one runs out the block records it in `status`, skips the
 // rest, frees its tensor memory and returns.  Two blocks fit on an SM and overlap each other.
 #include "tcgen05.cuh"
@@ -39,10 +45,13 @@ struct AttnTcShared {
     uint64_t k_full[2];
     uint64_t v_full[2];
     uint64_t s_ready[2];
+    uint64_t s_free[2];        // the softmax threads have read a score buffer
     uint64_t p_ready;
     uint64_t pv_ready;
+    uint64_t pair[4];          // the two warps that share 32 rows meet here
     uint32_t tmem_base;
     int failed;
+    __nv_bfloat16 xmax[2][128];   // each half's row maxima, for the other half (512 bytes; at the end: 128 floats)
 };
 
 // N-major (the matrix's N runs along the 128-byte rows) shared-memory descriptor, 128-byte swizzle:
@@ -100,8 +109,22 @@ __device__ __forceinline__ void tc_ld64(uint32_t taddr, float* v) {
 // which is a read-modify-write of the whole row.  Until then p = 2^(s - reference) stays below 2^8.
 #define ATC_RESCALE_LOG2 8.0f
 
-#define ATC_THREADS 160
+#define ATC_THREADS 320      // 8 softmax warps (4 row groups x 2 column halves), the QK warp and the PV warp
 #define ATC_TMEM_COLS 256
+
+#ifdef X0NE_ATC_TIMING
+__device__ long long atc_timing[32];
+#define ATC_T(idx) do { if (timed) { const long long now_ = clock64(); atomicAdd((unsigned long long*)&atc_timing[idx], (unsigned long long)(now_ - t_last)); t_last = now_; } } while (0)
+extern "C" __attribute__((visibility("default"))) int x0ne_atc_timing(long long* out) {
+    cudaDeviceSynchronize();
+    cudaMemcpyFromSymbol(out, atc_timing, sizeof(atc_timing));
+    long long zero[32] = {0};
+    cudaMemcpyToSymbol(atc_timing, zero, sizeof(zero));
+    return 0;
+}
+#else
+#define ATC_T(idx) do { } while (0)
+#endif
 
 template <int HD>
 __global__ void __launch_bounds__(ATC_THREADS, 2) attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
@@ -117,7 +140,8 @@ __global__ void __launch_bounds__(ATC_THREADS, 2) attention_prefill_tc_kernel(co
     unsigned char* vs = ks + 2 * KV_BYTES;        // 2 stages
     unsigned char* ps = vs + 2 * KV_BYTES;
     AttnTcShared* sh = reinterpret_cast<AttnTcShared*>(ps + P_BYTES);
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // the warp index through a shuffle, so that the compiler knows it is the same for the whole warp
+    const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
 
     const int head = blockIdx.x, tile = gridDim.y - 1 - blockIdx.y;
     const int kh = head / (a.q_heads / cache.kv_heads);
@@ -136,15 +160,17 @@ __global__ void __launch_bounds__(ATC_THREADS, 2) attention_prefill_tc_kernel(co
             mbar_init(&sh->k_full[b], 1);
             mbar_init(&sh->v_full[b], 1);
             mbar_init(&sh->s_ready[b], 1);
+            mbar_init(&sh->s_free[b], 256);
         }
-        mbar_init(&sh->p_ready, 128);
+        mbar_init(&sh->p_ready, 256);
+        for (int b = 0; b < 4; ++b) mbar_init(&sh->pair[b], 64);
         mbar_init(&sh->pv_ready, 1);
         sh->failed = (tc_smem(atc_raw) & 1023u) != 0 ? 1 : 0;      // the swizzle needs 1024-byte aligned tiles
-        if (sh->failed) atomicCAS(status, 0, 9);
+        if (sh->failed) atomicOr(status, 1 << 9);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
-    if (warp == 4) {
+    if (warp == 8) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tc_smem(&sh->tmem_base)),
                      "r"(ATC_TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -155,120 +181,171 @@ __global__ void __launch_bounds__(ATC_THREADS, 2) attention_prefill_tc_kernel(co
     const uint32_t tmem = sh->tmem_base;
     const uint32_t tmem_s = tmem, tmem_o = tmem + 128;       // S: two buffers of 64 columns; O: HD columns
 
-    if (warp == 4) {
-        if (lane == 0 && !sh->failed) {
-            // Page numbers are looked up well before the copies that need them (the table is older
-            // than the kernel before this one): a lookup in front of a copy would be a dependent
-            // global load in this thread's loop.
-            auto page_of = [&](int i) -> int {
-                if (i >= n_kt) return 0;
-                const int pg = cache.page_table[(int64_t)slot * cache.table_stride + ((kt_lo + i) % cache.ring_pages)];
-                return (pg < 0 || pg >= cache.n_pages) ? 0 : pg;      // never out of range for a sequence that holds its pages
-            };
-            const int pg0 = page_of(0), pg1 = page_of(1);
-            int pg_cur = page_of(2);                                  // the page of tile i + 2 in iteration i
-            pdl_wait();      // q and the newest cache rows were written by the kernel before this one
-            mbar_expect_tx(&sh->q_full, Q_BYTES);
-#pragma unroll
-            for (int nb = 0; nb < NB; ++nb) tma_load_2d(qs + nb * 128 * 128, &map_q, head * HD + nb * 64, row0, &sh->q_full);
+    // The two control warps run their loops with all lanes (the values are the same in every lane,
+    // which lets the compiler keep descriptors and addresses in uniform registers); one elected
+    // lane issues the copies and the products.
+    if (warp >= 8) {
+        uint32_t leader = 0;
+        asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(leader));
+        // Page numbers are looked up well before the copies that need them (the table is older
+        // than the kernel before this one): a lookup in front of a copy would be a dependent
+        // global load in the loop.
+        auto page_of = [&](int i) -> int {
+            if (i >= n_kt) return 0;
+            const int pg = cache.page_table[(int64_t)slot * cache.table_stride + ((kt_lo + i) % cache.ring_pages)];
+            return (pg < 0 || pg >= cache.n_pages) ? 0 : pg;      // never out of range for a sequence that holds its pages
+        };
+        const int pg0 = page_of(0), pg1 = page_of(1);
+        int pg_cur = page_of(2);
+        bool ok = !sh->failed;
+        auto wait = [&](uint64_t* bar, int parity, int code) {
+            if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar, parity, status, code));
+        };
+        pdl_wait();      // q and the newest cache rows were written by the kernel before this one
+        if (warp == 8) {
+            // ---- scores: Q once, K pages through two stages, S(i) = Q K(i)^T into buffer i & 1
             auto load_k = [&](int i, int page) {
                 const int st = i & 1;
                 const int krow = ((page * 2 + 0) * cache.kv_heads + kh) * 64;
-                mbar_expect_tx(&sh->k_full[st], KV_BYTES);
+                if (leader) {
+                    mbar_expect_tx(&sh->k_full[st], KV_BYTES);
 #pragma unroll
-                for (int nb = 0; nb < NB; ++nb)
-                    tma_load_2d(ks + st * KV_BYTES + nb * 64 * 128, &map_kv, nb * 64, krow, &sh->k_full[st]);
+                    for (int nb = 0; nb < NB; ++nb)
+                        tma_load_2d(ks + st * KV_BYTES + nb * 64 * 128, &map_kv, nb * 64, krow, &sh->k_full[st]);
+                }
+                __syncwarp();      // no lane waits for what the elected lane has not yet asked for
             };
+            if (leader && ok) {
+                mbar_expect_tx(&sh->q_full, Q_BYTES);
+#pragma unroll
+                for (int nb = 0; nb < NB; ++nb) tma_load_2d(qs + nb * 128 * 128, &map_q, head * HD + nb * 64, row0, &sh->q_full);
+            }
+            __syncwarp();
+            if (ok) {
+                load_k(0, pg0);
+                if (n_kt > 1) load_k(1, pg1);
+            }
+            // instruction descriptor: f32 accumulate, bf16 operands, M = 128, N = 64
+            const uint32_t idesc_qk = (1u << 4) | (1u << 7) | (1u << 10) | ((64u >> 3) << 17) | ((128u >> 4) << 24);
+            const uint32_t qb = tc_smem(qs);
+            wait(&sh->q_full, 0, 5);
+            for (int i = 0; i < n_kt && ok; ++i) {
+                const int st = i & 1;
+                const int pg_next = page_of(i + 2);
+                wait(&sh->k_full[st], (i >> 1) & 1, 6);
+                if (i >= 2) wait(&sh->s_free[st], ((i - 2) >> 1) & 1, 12);      // the softmax of page i - 2 has read this buffer
+                if (!ok) break;
+                tc_fence_after();
+                if (leader) {
+                    const uint32_t kb = tc_smem(ks + st * KV_BYTES);
+#pragma unroll
+                    for (int kk = 0; kk < HD / 16; ++kk)
+                        tc_mma(tmem_s + st * 64, tc_desc(qb + (kk / 4) * 128 * 128 + (kk % 4) * 32),
+                               tc_desc(kb + (kk / 4) * 64 * 128 + (kk % 4) * 32), idesc_qk, kk > 0 ? 1u : 0u);
+                    tc_commit(&sh->s_ready[st]);
+                }
+                __syncwarp();
+                if (i >= 1 && i + 1 < n_kt) {      // K(i - 1) has been read when S(i - 1) is complete: its stage takes K(i + 1)
+                    wait(&sh->s_ready[st ^ 1], ((i - 1) >> 1) & 1, 17);
+                    if (!ok) break;
+                    load_k(i + 1, pg_cur);
+                }
+                if (i >= 1) pg_cur = pg_next;
+            }
+        } else {
+            // ---- output: V pages through two stages, O += P(i) V(i) when the softmax threads have written P(i)
             auto load_v = [&](int i, int page) {
                 const int st = i & 1;
                 const int vrow = ((page * 2 + 1) * cache.kv_heads + kh) * 64;
-                mbar_expect_tx(&sh->v_full[st], KV_BYTES);
+                if (leader) {
+                    mbar_expect_tx(&sh->v_full[st], KV_BYTES);
 #pragma unroll
-                for (int nb = 0; nb < NB; ++nb)
-                    tma_load_2d(vs + st * KV_BYTES + nb * 64 * 128, &map_kv, nb * 64, vrow, &sh->v_full[st]);
+                    for (int nb = 0; nb < NB; ++nb)
+                        tma_load_2d(vs + st * KV_BYTES + nb * 64 * 128, &map_kv, nb * 64, vrow, &sh->v_full[st]);
+                }
+                __syncwarp();
             };
-            // instruction descriptors: f32 accumulate, bf16 operands, M = 128
-            const uint32_t idesc_qk = (1u << 4) | (1u << 7) | (1u << 10) | ((64u >> 3) << 17) | ((128u >> 4) << 24);
-            const uint32_t idesc_pv = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | (((uint32_t)HD >> 3) << 17) | ((128u >> 4) << 24);
-            const uint32_t qb = tc_smem(qs);
-            auto issue_qk = [&](int i) {                 // S[i & 1] = Q K(i)^T
-                const uint32_t kb = tc_smem(ks + (i & 1) * KV_BYTES);
-#pragma unroll
-                for (int kk = 0; kk < HD / 16; ++kk)
-                    tc_mma(tmem_s + (i & 1) * 64, tc_desc(qb + (kk / 4) * 128 * 128 + (kk % 4) * 32),
-                           tc_desc(kb + (kk / 4) * 64 * 128 + (kk % 4) * 32), idesc_qk, kk > 0 ? 1u : 0u);
-                tc_commit(&sh->s_ready[i & 1]);
-            };
-            load_k(0, pg0);
-            load_v(0, pg0);
-            if (n_kt > 1) {
-                load_k(1, pg1);
-                load_v(1, pg1);
-            }
-            bool ok = mbar_wait(&sh->q_full, 0, status, 5);
-            if (ok) ok = mbar_wait(&sh->k_full[0], 0, status, 6);
             if (ok) {
-                tc_fence_after();
-                issue_qk(0);
+                load_v(0, pg0);
+                if (n_kt > 1) load_v(1, pg1);
             }
-            // Order of this thread's work for page i: the scores of page i + 1 (so that they are
-            // ready when the softmax threads finish page i), then O += P(i) V(i), then the copies
-            // that the finished products make room for.
+            const uint32_t idesc_pv = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | (((uint32_t)HD >> 3) << 17) | ((128u >> 4) << 24);
+            const uint32_t pb = tc_smem(ps);
             for (int i = 0; i < n_kt && ok; ++i) {
                 const int st = i & 1;
                 const int pg_next = page_of(i + 3);
-                if (i + 1 < n_kt) {
-                    if (!(ok = mbar_wait(&sh->s_ready[st], (i >> 1) & 1, status, 12))) break;     // K(i) has been read
-                    if (i + 2 < n_kt) load_k(i + 2, pg_cur);
-                    if (!(ok = mbar_wait(&sh->k_full[st ^ 1], ((i + 1) >> 1) & 1, status, 6))) break;
-                    tc_fence_after();
-                    issue_qk(i + 1);      // its buffer was read by the softmax of page i - 1, which has arrived (below)
-                }
-                if (!(ok = mbar_wait(&sh->p_ready, i & 1, status, 7))) break;
-                if (!(ok = mbar_wait(&sh->v_full[st], (i >> 1) & 1, status, 13))) break;
+                wait(&sh->v_full[st], (i >> 1) & 1, 13);
+                wait(&sh->p_ready, i & 1, 7);
+                if (!ok) break;
                 tc_fence_after();
-                const uint32_t vb = tc_smem(vs + st * KV_BYTES);
+                if (leader) {
+                    const uint32_t vb = tc_smem(vs + st * KV_BYTES);
 #pragma unroll
-                for (int kk = 0; kk < 4; ++kk)
-                    tc_mma(tmem_o, tc_desc(tc_smem(ps) + kk * 32), tc_desc_nmajor(vb + kk * 16 * 128, 64 * 128), idesc_pv,
-                           (i > 0 || kk > 0) ? 1u : 0u);          // the output accumulates in tensor memory over the pages
-                tc_commit(&sh->pv_ready);
+                    for (int kk = 0; kk < 4; ++kk)
+                        tc_mma(tmem_o, tc_desc(pb + kk * 32), tc_desc_nmajor(vb + kk * 16 * 128, 64 * 128), idesc_pv,
+                               (i > 0 || kk > 0) ? 1u : 0u);          // the output accumulates in tensor memory over the pages
+                    tc_commit(&sh->pv_ready);
+                }
+                __syncwarp();
                 if (i + 2 < n_kt) {       // V's stage is free once this product is done
-                    if (!(ok = mbar_wait(&sh->pv_ready, i & 1, status, 8))) break;
+                    wait(&sh->pv_ready, i & 1, 8);
+                    if (!ok) break;
                     load_v(i + 2, pg_cur);
                 }
                 pg_cur = pg_next;
             }
-            if (!ok) sh->failed = 1;
         }
+        if (!ok) sh->failed = 1;
     } else {
-        const int r = warp * 32 + lane;                       // this thread's row of the tile = its tensor-memory lane
+        // Two threads per row: warp w and warp w + 4 own rows 32 (w % 4) ... + 31 (their lanes of
+        // tensor memory) and each takes one half of a page's 64 keys, and one half of the output's
+        // columns.  They agree on the row's reference maximum through shared memory.
+        const int sw = warp & 3, half = warp >> 2;
+        const int r = sw * 32 + lane;
         const int p = pos_first + r;
-        const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+        const uint32_t lane_base = (uint32_t)(sw * 32) << 16;
         const float sc = a.scale_log2;
-        float m_ref = -INFINITY, l = 0.f;                     // reference maximum (raw scores) and the sum of p
+        float m_ref = -INFINITY, l = 0.f;                     // reference maximum (raw scores) and this half's sum of p
+        int pair_phase = 0;
         bool ok = !sh->failed;
+#ifdef X0NE_ATC_TIMING
+        const bool timed = blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0;
+        long long t_last = clock64();
+#endif
         for (int i = 0; i < n_kt && ok; ++i) {
             const int kt = kt_lo + i;
             if (!(ok = mbar_wait(&sh->s_ready[i & 1], (i >> 1) & 1, status, 10))) break;
+            ATC_T(0);
             tc_fence_after();
-            float s[64];
-            tc_ld64(tmem_s + (i & 1) * 64 + lane_base, s);
+            float s[32];
+            tc_ld32(tmem_s + (i & 1) * 64 + half * 32 + lane_base, s);
+            tc_fence_before();
+            mbar_arrive(&sh->s_free[i & 1]);      // the scores are in registers: the buffer may take the page after next
+            ATC_T(1);
             const bool edge = (kt * 64 + 63 > pos_first) || (a.window > 0 && kt * 64 <= pos_last - a.window);
             if (edge) {
 #pragma unroll
-                for (int c = 0; c < 64; ++c) {
-                    const int j = kt * 64 + c;
+                for (int c = 0; c < 32; ++c) {
+                    const int j = kt * 64 + half * 32 + c;
                     if (j > p || (a.window > 0 && j <= p - a.window)) s[c] = -INFINITY;
                 }
             }
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};      // four chains instead of one
 #pragma unroll
-            for (int c = 0; c < 64; c += 4) {
+            for (int c = 0; c < 32; c += 4) {
 #pragma unroll
                 for (int e = 0; e < 4; ++e) mx4[e] = fmaxf(mx4[e], s[c + e]);
             }
-            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+            // The halves exchange their maxima rounded up to bfloat16 (a reference may lie above the
+            // true maximum; it must only be the same for the whole row).
+            const __nv_bfloat16 mine = __float2bfloat16_ru(fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])));
+            sh->xmax[half][r] = mine;
+            mbar_arrive(&sh->pair[sw]);
+            ATC_T(2);
+            if (!(ok = mbar_wait(&sh->pair[sw], pair_phase & 1, status, 16))) break;
+            ATC_T(3);
+            ++pair_phase;
+            const float mx = fmaxf(__bfloat162float(mine), __bfloat162float(sh->xmax[half ^ 1][r]));
             // raise the reference only when it is first set or falls too far behind
             const bool raise = mx > m_ref && (m_ref == -INFINITY || (mx - m_ref) * sc > ATC_RESCALE_LOG2);
             const bool shrink = raise && m_ref != -INFINITY;          // what this row has accumulated must be rescaled
@@ -277,42 +354,44 @@ __global__ void __launch_bounds__(ATC_THREADS, 2) attention_prefill_tc_kernel(co
             if (raise) m_ref = mx;
             const float neg = m_ref == -INFINITY ? 0.f : -m_ref * sc;
             float sum4[4] = {0.f, 0.f, 0.f, 0.f};
-            uint32_t w[32];                                           // the row of P, bfloat16 pairs
+            uint32_t w[16];                                           // this half of the row of P, bfloat16 pairs
 #pragma unroll
-            for (int e = 0; e < 32; ++e) {
+            for (int e = 0; e < 16; ++e) {
                 const float p0 = ex2_approx(fmaf(s[2 * e], sc, neg)), p1 = ex2_approx(fmaf(s[2 * e + 1], sc, neg));
                 sum4[e & 3] += p0 + p1;
-                __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
-                w[e] = *reinterpret_cast<uint32_t*>(&h);
+                __nv_bfloat162 h2 = __floats2bfloat162_rn(p0, p1);
+                w[e] = *reinterpret_cast<uint32_t*>(&h2);
             }
             l = l * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
+            ATC_T(4);
             // P's buffer and the accumulator belong to the product of the page before until it is done
             if (i > 0) {
                 if (!(ok = mbar_wait(&sh->pv_ready, (i - 1) & 1, status, 14))) break;
                 tc_fence_after();
             }
-            if (rescale) {       // this warp's rows of the accumulator (rows that keep their reference: factor 1)
+            ATC_T(5);
+            if (rescale) {       // this warp's rows and half of the columns (rows that keep their reference: factor 1)
 #pragma unroll 1
-                for (int c = 0; c < HD / 32; ++c) {
+                for (int c = 0; c < HD / 64; ++c) {
                     float ov[32];
-                    tc_ld32(tmem_o + lane_base + c * 32, ov);
+                    tc_ld32(tmem_o + lane_base + half * (HD / 2) + c * 32, ov);
 #pragma unroll
                     for (int d = 0; d < 32; ++d) ov[d] *= alpha;
-                    tc_st32(tmem_o + lane_base + c * 32, ov);
+                    tc_st32(tmem_o + lane_base + half * (HD / 2) + c * 32, ov);
                 }
                 asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             }
             // P row -> shared memory, 16 bytes (8 keys) at a time, chunk c at position c ^ (row & 7)
             unsigned char* prow = ps + r * 128;
 #pragma unroll
-            for (int c = 0; c < 8; ++c)
-                *reinterpret_cast<uint4*>(prow + ((c ^ (r & 7)) << 4)) = make_uint4(w[4 * c], w[4 * c + 1], w[4 * c + 2], w[4 * c + 3]);
+            for (int c = 0; c < 4; ++c)
+                *reinterpret_cast<uint4*>(prow + (((half * 4 + c) ^ (r & 7)) << 4)) = make_uint4(w[4 * c], w[4 * c + 1], w[4 * c + 2], w[4 * c + 3]);
             // The page's rows past the sequence's last position may hold anything (an earlier
             // sequence's values): zero them in V, so that 0 * value stays 0.
             if (kt * 64 + 63 > pos_last) {
                 if (!(ok = mbar_wait(&sh->v_full[i & 1], (i >> 1) & 1, status, 15))) break;     // V has landed
             }
-            if (kt * 64 + 63 > pos_last && r < 64 && kt * 64 + r > pos_last) {
+            if (kt * 64 + 63 > pos_last && half == 0 && r < 64 && kt * 64 + r > pos_last) {
                 unsigned char* vrow = vs + (i & 1) * KV_BYTES + r * 128;
 #pragma unroll
                 for (int nb = 0; nb < NB; ++nb)
@@ -320,20 +399,40 @@ __global__ void __launch_bounds__(ATC_THREADS, 2) attention_prefill_tc_kernel(co
                     for (int c = 0; c < 8; ++c)
                         *reinterpret_cast<uint4*>(vrow + nb * 64 * 128 + c * 16) = make_uint4(0, 0, 0, 0);
             }
+            ATC_T(6);
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // P (and the zeros) are for the MMA to read
             tc_fence_before();
             mbar_arrive(&sh->p_ready);
+            ATC_T(7);
         }
         if (ok && n_kt > 0) ok = mbar_wait(&sh->pv_ready, (n_kt - 1) & 1, status, 11);
         tc_fence_after();
+        // 1 / (sum of both halves): the second half hands its sum over, the first hands the quotient back
+        float* xl = reinterpret_cast<float*>(&sh->xmax[0][0]);
+        float inv = 0.f;
+        if (ok) {
+            if (half == 1) xl[r] = l;
+            mbar_arrive(&sh->pair[sw]);
+            ok = mbar_wait(&sh->pair[sw], pair_phase & 1, status, 16);
+            ++pair_phase;
+        }
+        if (ok) {
+            if (half == 0) {
+                inv = 1.0f / (l + xl[r]);
+                xl[r] = inv;
+            }
+            mbar_arrive(&sh->pair[sw]);
+            ok = mbar_wait(&sh->pair[sw], pair_phase & 1, status, 16);
+            ++pair_phase;
+        }
         if (!ok) sh->failed = 1;
         if (ok) {
-            const float inv = 1.0f / l;
-            bf16* dst = a.out + (int64_t)(row0 + r) * (a.q_heads * HD) + head * HD;
+            if (half == 1) inv = xl[r];
+            bf16* dst = a.out + (int64_t)(row0 + r) * (a.q_heads * HD) + head * HD + half * (HD / 2);
 #pragma unroll 1
-            for (int c = 0; c < HD / 32; ++c) {
+            for (int c = 0; c < HD / 64; ++c) {
                 float ov[32];
-                tc_ld32(tmem_o + lane_base + c * 32, ov);      // every lane takes part in the load
+                tc_ld32(tmem_o + lane_base + half * (HD / 2) + c * 32, ov);      // every lane takes part in the load
                 if (r < nrows) {
 #pragma unroll
                     for (int d = 0; d < 32; d += 8) {
@@ -348,7 +447,7 @@ __global__ void __launch_bounds__(ATC_THREADS, 2) attention_prefill_tc_kernel(co
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 4) {
+    if (warp == 8) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(ATC_TMEM_COLS) : "memory");
     }

@@ -366,9 +366,11 @@ def check_tc_status(device) -> None:
     st = int(gemm_tc_status(device)[0])
     if st != 0:
         gemm_tc_status(device).zero_()
-        raise KernelError(f"a tcgen05 kernel gave up waiting on a barrier (code {st}; products: 1 copy, 2 MMA, "
+        codes = [b for b in range(32) if st >> b & 1]
+        raise KernelError(f"a tcgen05 kernel gave up waiting on a barrier (codes {codes}; products: 1 copy, 2 MMA, "
                           "3 epilogue, 4 accumulator; attention: 5 queries, 6 keys, 13 and 15 values, 7 probabilities, "
-                          "8, 11 and 14 output, 10 and 12 scores); its output is not valid")
+                          "8, 11 and 14 output, 10, 12 and 17 scores, 16 the other half of the row; 9: misaligned "
+                          "shared memory); its output is not valid")
 
 
 def gemm_tc_status(device) -> torch.Tensor:

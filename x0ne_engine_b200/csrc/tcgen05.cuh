@@ -21,18 +21,22 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
+#ifdef X0NE_MBAR_POLL
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+#else
         "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+#endif
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok) : "r"(tc_smem(bar)), "r"(parity) : "memory");
     return ok != 0;
 }
-// Waits for the barrier's phase of the given parity, at most about a second.  On a timeout writes
-// `code` to *status (if it is still 0) and returns false.
+// Waits for the barrier's phase of the given parity, at most about a second.  On a timeout sets
+// bit `code` of *status and returns false.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int code) {
     const long long start = clock64();
     while (!mbar_try_wait(bar, parity)) {
         if (clock64() - start > TC_WAIT_CYCLES) {
-            atomicCAS(status, 0, code);
+            atomicOr(status, 1 << code);
             return false;
         }
     }
