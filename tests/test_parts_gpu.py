@@ -306,3 +306,203 @@ def test_a_model_with_a_windowed_layer_has_two_cache_groups_and_matches_the_plai
     close(np.stack(rows), want[229:], "token by token")
     if dtype == "float32":
         assert np.array_equal(np.stack(rows), got[229:])
+
+
+def test_rope_part_alone():
+    """The position encoding part owns the table of inverse frequencies and the cos/sin table; both
+    equal the plain formulas in float32, also for a rotary width below the head size."""
+    from x0ne_engine_b200.config import PartSpec
+    from x0ne_engine_b200.parts import POSITIONS, BuildEnv
+    env = BuildEnv(dtype=torch.float32, device=torch.device(DEV))
+    for head_dim, rot, theta in ((48, 48, 1e4), (80, 32, 5e5)):
+        part = POSITIONS.get("rope")(PartSpec("rope", dict(head_dim=head_dim, rotary_dim=rot, theta=theta)), env)
+        table, width = part.rotary()
+        assert width == rot and table.dtype == torch.float32 and tuple(table.shape) == (rot // 2,)
+        want = P.inv_freq(rot, theta)
+        assert np.abs(table.cpu().numpy() - want).max() / want.max() < 1e-6
+        cs = part.cos_sin_table(300).cpu().numpy()
+        assert cs.shape == (300, rot)
+        ang = (np.arange(300, dtype=np.float32)[:, None] * table.cpu().numpy()[None, :]).astype(np.float64)
+        assert np.abs(cs[:, :rot // 2] - np.cos(ang)).max() < 1e-6 and np.abs(cs[:, rot // 2:] - np.sin(ang)).max() < 1e-6
+    with pytest.raises(ValueError):
+        POSITIONS.get("rope")(PartSpec("rope", dict(head_dim=16, rotary_dim=18, theta=1e4)), env)
+    assert POSITIONS.get("none")(PartSpec("none", {}), env).rotary() is None
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_embedding_and_head_parts_alone(dtype):
+    """Rows of the table as float32 (an id outside the table gives zeros); logits in float32 for a
+    vocabulary and a width that are no powers of two, through the small-row and the library product."""
+    from x0ne_engine_b200.config import PartSpec
+    from x0ne_engine_b200.parts import BuildEnv, LMHead, TokenEmbedding
+    vocab, h = 203, 72
+    env = BuildEnv(dtype=dtype, device=torch.device(DEV))
+    table = rnd((vocab, h), 5).to(dtype).to(DEV)
+    spec = PartSpec("token_embedding", dict(vocab_size=vocab, hidden_size=h, names=dict(weight="emb")))
+    emb = TokenEmbedding(spec, env)
+    assert [(n.name, n.shape) for n in TokenEmbedding.tensor_needs(spec)] == [("emb", (vocab, h))]
+    emb.bind({"emb": table})
+    toks = [0, 202, 17, 17, 500, 3]
+    ctx = make_ctx(dtype, len(toks), [0] * len(toks), list(range(len(toks))), None)
+    ctx.tokens = torch.tensor(toks, dtype=torch.int32, device=DEV)
+    resid = torch.full((ctx.ws.max_rows, h), 7.0, device=DEV)
+    emb.forward(ctx, resid, len(toks))
+    want = table.float()[[0, 202, 17, 17, 0, 3]]
+    want[4] = 0
+    assert torch.equal(resid[:len(toks)], want) and float(resid[len(toks)].min()) == 7.0
+    head = LMHead(PartSpec("lm_head", dict(vocab_size=vocab, hidden_size=h, tied=True, names=dict(weight="emb"))), env)
+    head.bind({"emb": table})
+    assert head.weight_bytes() == vocab * h * table.element_size()
+    for n in (3, 40):                                   # 40 rows: the library product in bfloat16
+        x = rnd((n, h), 6).to(dtype).to(DEV)
+        logits = torch.empty((n, vocab), dtype=torch.float32, device=DEV)
+        head.forward(x, logits, n)
+        ref = x.double() @ table.double().T
+        tol = 1e-5 if dtype == torch.float32 else 2e-2
+        assert float((logits.double() - ref).abs().max() / ref.abs().max()) < tol
+
+
+def test_prenorm_block_alone_with_toy_parts():
+    """The arrangement alone: with a mixer that doubles and a feed-forward that triples their
+    inputs, and norms that are the identity, x' = x + d + 2 (x + d) and the pending delta is
+    3 x': the block adds each delta in the norm that follows it and returns its own."""
+    from x0ne_engine_b200.parts import BLOCKS, FeedForward, Mixer, Norm
+
+    class Same(Norm):
+        def add_norm(self, ctx, resid, delta, out, n_rows, rows=None):
+            if delta is not None:
+                resid[:n_rows] += delta[:n_rows].float()
+            out[:n_rows] = resid[:n_rows].to(out.dtype)
+
+    class Twice(Mixer):
+        def forward(self, ctx, entry, x, n_rows, cache_entry=None, write_cache=True):
+            assert (entry, cache_entry, write_cache) == (5, 2, False)
+            return (2 * x).clone()
+
+    class Thrice(FeedForward):
+        def forward(self, ctx, x, n_rows):
+            return (3 * x).clone()
+
+    block = BLOCKS.get("prenorm")(Same(None, None), Twice(None, None), Same(None, None), Thrice(None, None))
+    assert len(block.parts()) == 4
+    n, h = 5, 24
+    ctx = make_ctx(torch.float32, n, [0] * n, list(range(n)), None)
+    x, d = rnd((64, h), 1).to(DEV), rnd((64, h), 2).to(DEV)
+    resid = x.clone()
+    out = block.forward(ctx, 5, resid, d.clone(), cache_entry=2, write_cache=False)
+    mid = x[:n] + d[:n]
+    assert torch.allclose(resid[:n], 3 * mid, rtol=1e-6) and torch.allclose(out[:n], 9 * mid, rtol=1e-6)
+    assert torch.equal(resid[n:], x[n:])
+
+
+def test_a_toy_feed_forward_with_routing_and_a_toy_position_encoding():
+    """Two more kinds of part defined here and registered without touching the library: a
+    feed-forward that routes every row to one of three experts by float32 router logits, and a
+    position encoding that adds a learned row to the embedding (the attention then rotates nothing).
+    The model built from them gives the plain result whole, token by token, and in a batch."""
+    from x0ne_engine_b200 import Engine
+    from x0ne_engine_b200.config import LayerSpec, ModelSpec, PartSpec, RunEntry
+    from x0ne_engine_b200.engine import tensor_needs_of_spec
+    from x0ne_engine_b200.parts import FEED_FORWARDS, POSITIONS, FeedForward, PositionEncoding
+    from x0ne_engine_b200.weights import RandomInit, TensorNeed, make_tensor
+
+    class TopOneExperts(FeedForward):
+        """e = argmax(x R^T) in float32;  out = relu(x A_e^T) B_e^T"""
+
+        def __init__(self, spec, env):
+            super().__init__(spec, env)
+            self.h, self.i, self.e = int(spec["hidden_size"]), int(spec["intermediate_size"]), int(spec["experts"])
+
+        @staticmethod
+        def tensor_needs(spec):
+            h, i, e, nm = int(spec["hidden_size"]), int(spec["intermediate_size"]), int(spec["experts"]), spec["names"]
+            return ([TensorNeed(nm["router"], (e, h))] + [TensorNeed(f"{nm['experts']}.{k}.a", (i, h)) for k in range(e)]
+                    + [TensorNeed(f"{nm['experts']}.{k}.b", (h, i)) for k in range(e)])
+
+        def bind(self, tensors):
+            nm = self.spec["names"]
+            self.router = tensors[nm["router"]]
+            self.a = torch.stack([tensors[f"{nm['experts']}.{k}.a"] for k in range(self.e)])
+            self.b = torch.stack([tensors[f"{nm['experts']}.{k}.b"] for k in range(self.e)])
+
+        def forward(self, ctx, x, n_rows):
+            out = ctx.ws.buffer("delta", (ctx.ws.max_rows, self.h), self.env.dtype)
+            xs = x[:n_rows].float()
+            pick = (xs @ self.router.float().T).argmax(-1)
+            hid = torch.relu(torch.einsum("rh,rih->ri", xs, self.a[pick].float()))
+            out[:n_rows] = torch.einsum("ri,rhi->rh", hid, self.b[pick].float()).to(self.env.dtype)
+            return out
+
+    class LearnedPositions(PositionEncoding):
+        @staticmethod
+        def tensor_needs(spec):
+            return [TensorNeed(spec["names"]["table"], (int(spec["positions"]), int(spec["hidden_size"])))]
+
+        def bind(self, tensors):
+            self.rows = tensors[self.spec["names"]["table"]]
+
+        def on_embedding(self, ctx, resid, n_rows):
+            resid[:n_rows] += self.rows[ctx.row_pos[:n_rows].long()].float()
+
+    FEED_FORWARDS.register("toy_top_one", TopOneExperts)
+    POSITIONS.register("toy_learned", LearnedPositions)
+    try:
+        h, vocab, heads, kvh, hd, inter, experts = 40, 61, 4, 2, 16, 24, 3
+        norm = lambda name: PartSpec("rmsnorm", dict(size=h, eps=1e-5, names=dict(weight=name)))   # noqa: E731
+        layers = []
+        for l in range(2):
+            att = PartSpec("gqa_attention", dict(hidden_size=h, q_heads=heads, kv_heads=kvh, head_dim=hd, qk_norm_eps=None,
+                                                 window=None, position=None, scale=None,
+                                                 names=dict(q=f"l{l}.q", k=f"l{l}.k", v=f"l{l}.v", o=f"l{l}.o")))
+            ffn = PartSpec("toy_top_one", dict(hidden_size=h, intermediate_size=inter, experts=experts,
+                                               names=dict(router=f"l{l}.router", experts=f"l{l}.experts")))
+            layers.append(LayerSpec(block="prenorm", mixer_norm=norm(f"l{l}.n1"), mixer=att, ffn_norm=norm(f"l{l}.n2"), ffn=ffn))
+        spec = ModelSpec(architecture="ToyRoutedForCausalLM", vocab_size=vocab, hidden_size=h, max_position_embeddings=64,
+                         embedding=PartSpec("token_embedding", dict(vocab_size=vocab, hidden_size=h, names=dict(weight="emb"))),
+                         positions={"learned": PartSpec("toy_learned", dict(positions=64, hidden_size=h, names=dict(table="pos")))},
+                         layers=tuple(layers), run_order=(RunEntry(0), RunEntry(1)), final_norm=norm("fn"),
+                         head=PartSpec("lm_head", dict(vocab_size=vocab, hidden_size=h, tied=False, names=dict(weight="head"))))
+        needs = tensor_needs_of_spec(spec)
+        assert {"pos", "l0.router", "l1.experts.2.b"} <= {n.name for n in needs}
+        init = RandomInit(seed=11, linear_std=0.25, norm_jitter=0.1)
+        cpu = {n.name: make_tensor(n, init, torch.float32, "cpu") for n in needs}
+        eng = Engine(spec, {k: v.to(DEV) for k, v in cpu.items()}, "float32", DEV, max_tokens=512)
+        w = {k: v.double().numpy() for k, v in cpu.items()}
+
+        def plain(ids):
+            n = len(ids)
+            x = w["emb"][ids] + w["pos"][:n]
+            used = set()
+            for l in range(2):
+                nx = P.rmsnorm(x, w[f"l{l}.n1"], 1e-5)
+                q = (nx @ w[f"l{l}.q"].T).reshape(n, heads, hd)
+                k = (nx @ w[f"l{l}.k"].T).reshape(n, kvh, hd)
+                v = (nx @ w[f"l{l}.v"].T).reshape(n, kvh, hd)
+                x = x + P.attention(q, k, v).reshape(n, heads * hd) @ w[f"l{l}.o"].T
+                nx = P.rmsnorm(x, w[f"l{l}.n2"], 1e-5)
+                pick = (nx @ w[f"l{l}.router"].T).argmax(-1)
+                used |= set(pick.tolist())
+                x = x + np.stack([np.maximum(nx[t] @ w[f"l{l}.experts.{e}.a"].T, 0) @ w[f"l{l}.experts.{e}.b"].T
+                                  for t, e in enumerate(pick)])
+            return P.rmsnorm(x, w["fn"], 1e-5) @ w["head"].T, used
+
+        a, b = [3, 14, 15, 9, 2, 6, 5, 35, 8, 9, 7, 60], [1, 1, 2, 3, 5, 8, 13]
+        want_a, used = plain(a)
+        want_b, _ = plain(b)
+        assert len(used) > 1                              # the router really sends rows to different experts
+        sa, sb = eng.new_sequence(), eng.new_sequence()
+        got = eng.step([sa, sb], [a[:6], b[:3]], [list(range(6)), list(range(3))]).cpu().numpy()
+        assert np.abs(got[:6] - want_a[:6]).max() / np.abs(want_a).max() < 1e-4
+        assert np.abs(got[6:] - want_b[:3]).max() / np.abs(want_b).max() < 1e-4
+        for t in range(3, len(b)):                        # one token each; the shorter request ends first
+            got = eng.step([sa, sb], [[a[3 + t]], [b[t]]]).cpu().numpy()
+            assert np.abs(got[0] - want_a[3 + t]).max() / np.abs(want_a).max() < 1e-4
+            assert np.abs(got[1] - want_b[t]).max() / np.abs(want_b).max() < 1e-4
+        eng.free_sequence(sb)
+        for t in range(3 + len(b), len(a)):
+            got = eng.step([sa], [[a[t]]]).cpu().numpy()
+            assert np.abs(got[0] - want_a[t]).max() / np.abs(want_a).max() < 1e-4
+        eng.free_sequence(sa)
+    finally:
+        FEED_FORWARDS.unregister("toy_top_one")
+        POSITIONS.unregister("toy_learned")
