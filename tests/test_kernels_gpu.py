@@ -433,6 +433,36 @@ def test_decode_attention_bf16(q_heads, kv_heads, hd, window, splits):
     assert int(counters.abs().sum()) == 0
 
 
+@pytest.mark.parametrize("splits", [1, 3])
+def test_decode_attention_bf16_long_contexts(splits):
+    """Contexts past 128 pages per block (the page numbers a block keeps in shared memory) and a
+    far key that decides the output: position 8200 of 9000 carries a score far above the rest."""
+    o = ops()
+    q_heads, kv_heads, hd = 4, 2, 64
+    ctxs = [8191, 8193, 9000]
+    n = len(ctxs)
+    pages = 141
+    storage, table, view = make_cache(kv_heads, hd, n * pages, n, torch.bfloat16, pages)
+    fill_cache(storage, torch.bfloat16, 52, 0.3)
+    far = 8200
+    page = int(table[2, far // 64])
+    storage[page, 0, :, far % 64] = 6.0                          # key of both kv heads at the far position
+    slots = torch.arange(n, dtype=torch.int32, device=DEV)
+    pos = torch.tensor([c - 1 for c in ctxs], dtype=torch.int32, device=DEV)
+    q = rnd((n, q_heads * hd), torch.bfloat16, 53)
+    q[2] = q[2].abs() + 1.0                                      # score of the far key: about 64 * 6 * 1.8 / 8
+    out = torch.full_like(q, 55.0)
+    scratch = torch.zeros(o.attention_decode_scratch_bytes(n, q_heads, kv_heads, hd, splits), dtype=torch.uint8, device=DEV)
+    o.attention_decode_bf16(q, out, view, slots, pos, n, q_heads, 1 / math.sqrt(hd), 0, splits, scratch)
+    ref = torch.empty_like(q)
+    o.attention_rows(q, ref, view, slots, pos, n, q_heads, 1 / math.sqrt(hd), 0)
+    vmax = float(storage.float().abs().max())
+    assert (out.float() - ref.float()).abs().max() / vmax < 2 * BF16_EPS
+    want = storage[page, 1, :, far % 64].float()                 # [kv_heads, hd]: the far position's values
+    got = out[2].float().reshape(kv_heads, q_heads // kv_heads, hd)
+    assert (got - want[:, None, :]).abs().max() < 2 * BF16_EPS * vmax
+
+
 # ------------------------------------------------------------------------------------------ sampler
 def test_sampler_argmax_ties_nan_and_feedback():
     o = ops()
