@@ -28,13 +28,18 @@ __device__ __forceinline__ void mma16816(float* c, uint32_t a0, uint32_t a1, uin
 }
 
 #define SM_WARPS 8
-// ring depths (chunks per thread) of the variants for up to 8 rows; two blocks fit on an SM
-#ifndef X0NE_SMALLM_DEPTH_PLAIN
-#define X0NE_SMALLM_DEPTH_PLAIN 9
-#endif
-#ifndef X0NE_SMALLM_DEPTH_SWIGLU
-#define X0NE_SMALLM_DEPTH_SWIGLU 5
-#endif
+// Ring depth (chunks per thread) of a variant: the deepest with which two blocks still fit on an
+// SM (228 KB, 1 KB of it reserved per block), since what a thread has in flight is what hides the
+// memory latency.  Up to 8 rows: 9 chunks, 5 with the SwiGLU epilogue (two weight sets).
+constexpr int smallm_depth(int mt, bool swiglu) {
+    const int sets = swiglu ? 2 : 1;
+    const int slots = sets * 2 + mt;
+    const int part = SM_WARPS * sets * mt * 128 * 4;
+    const int depth = ((228 * 1024) / 2 - 1024 - part) / (slots * SM_WARPS * 32 * 16);
+    return depth < 2 ? 2 : depth;
+}
+static_assert(smallm_depth(1, false) == 9 && smallm_depth(1, true) == 5 && smallm_depth(2, false) == 6 && smallm_depth(2, true) == 4,
+              "ring depths");
 
 // 16 bytes global -> shared, asynchronously; `bytes` = 0 writes zeros instead (out-of-range rows or k).
 __device__ __forceinline__ void cp_async16_zfill(void* dst, const void* src, int bytes) {
@@ -192,7 +197,7 @@ template <int MT, typename OutT, bool SWIGLU>
 static int launch_smallm(const bf16* W, const bf16* X, OutT* Y, int M, int N, int K, int ldy, int sms, cudaStream_t stream) {
     constexpr int SETS = SWIGLU ? 2 : 1;
     constexpr int SLOTS = SETS * 2 + MT;
-    constexpr int DEPTH = SWIGLU ? X0NE_SMALLM_DEPTH_SWIGLU : (MT == 1 ? X0NE_SMALLM_DEPTH_PLAIN : 4);
+    constexpr int DEPTH = smallm_depth(MT, SWIGLU);
     constexpr int SMEM = DEPTH * SLOTS * SM_WARPS * 32 * 16 + SM_WARPS * SETS * MT * 128 * 4;
     const int n_tiles = (N + 15) / 16;
     static int per_sm = 0;     // blocks of this variant that fit on one SM

@@ -308,7 +308,8 @@ def attention_decode_bf16(q: torch.Tensor, out: torch.Tensor, cache: PagedCacheA
 # ---------------------------------------------------------------------------------------------
 # bfloat16 small-M weight-streaming product (module `fast`)
 # ---------------------------------------------------------------------------------------------
-SMALL_M_LIMIT = 16
+SMALL_M_LIMIT = 8           # rows up to which the weight-streaming kernel beats the library product
+SMALL_M_LIMIT_FUSED = 16    # with the SwiGLU epilogue it also saves a kernel and a round trip of gate and up
 _sm_count = {}
 
 
@@ -320,8 +321,9 @@ def _sms(device) -> int:
     return n
 
 
-def gemm_smallm_takes(w: torch.Tensor, m: int) -> bool:
-    return w.dtype == torch.bfloat16 and 0 < m <= SMALL_M_LIMIT and w.shape[1] % 8 == 0
+def gemm_smallm_takes(w: torch.Tensor, m: int, swiglu: bool = False) -> bool:
+    limit = SMALL_M_LIMIT_FUSED if swiglu else SMALL_M_LIMIT
+    return w.dtype == torch.bfloat16 and 0 < m <= limit and w.shape[1] % 8 == 0
 
 
 def gemm_bf16_smallm(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, m: int, swiglu: bool = False) -> None:
