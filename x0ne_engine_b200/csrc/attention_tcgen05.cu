@@ -82,28 +82,6 @@ __device__ __forceinline__ void tc_st32(uint32_t taddr, const float* v) {
           "r"(__float_as_uint(v[31]))
         : "memory");
 }
-// Two 32-column loads, one wait.
-__device__ __forceinline__ void tc_ld64(uint32_t taddr, float* v) {
-    uint32_t r[64];
-#define X0NE_LD32(OFF, T)                                                                                                   \
-    asm volatile(                                                                                                          \
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "   \
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"                          \
-        : "=r"(r[OFF + 0]), "=r"(r[OFF + 1]), "=r"(r[OFF + 2]), "=r"(r[OFF + 3]), "=r"(r[OFF + 4]), "=r"(r[OFF + 5]),      \
-          "=r"(r[OFF + 6]), "=r"(r[OFF + 7]), "=r"(r[OFF + 8]), "=r"(r[OFF + 9]), "=r"(r[OFF + 10]), "=r"(r[OFF + 11]),    \
-          "=r"(r[OFF + 12]), "=r"(r[OFF + 13]), "=r"(r[OFF + 14]), "=r"(r[OFF + 15]), "=r"(r[OFF + 16]), "=r"(r[OFF + 17]), \
-          "=r"(r[OFF + 18]), "=r"(r[OFF + 19]), "=r"(r[OFF + 20]), "=r"(r[OFF + 21]), "=r"(r[OFF + 22]), "=r"(r[OFF + 23]), \
-          "=r"(r[OFF + 24]), "=r"(r[OFF + 25]), "=r"(r[OFF + 26]), "=r"(r[OFF + 27]), "=r"(r[OFF + 28]), "=r"(r[OFF + 29]), \
-          "=r"(r[OFF + 30]), "=r"(r[OFF + 31])                                                                             \
-        : "r"(T) : "memory")
-    X0NE_LD32(0, taddr);
-    X0NE_LD32(32, taddr + 32);
-#undef X0NE_LD32
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-    for (int i = 0; i < 64; ++i) v[i] = __uint_as_float(r[i]);
-}
-
 // The running maximum a row's exponentials refer to is only raised when the new maximum exceeds it
 // by more than this many powers of two: then the accumulator in tensor memory has to be rescaled,
 // which is a read-modify-write of the whole row.  Until then p = 2^(s - reference) stays below 2^8.

@@ -21,11 +21,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-#ifdef X0NE_MBAR_POLL
-        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-#else
         "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-#endif
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok) : "r"(tc_smem(bar)), "r"(parity) : "memory");
     return ok != 0;
