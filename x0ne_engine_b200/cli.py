@@ -3,6 +3,7 @@
 Commands and their options follow the reference's own programs where it has them:
 
   core-bench <model dir> [--lengths short,1k,4k] [--decode N] [--reps N] [--batch B] [--dtype D]
+      [--random-weights SEED]
       time to first token, prefill and decode rates per prompt length, one line
       `x0ne-bench-result: <JSON>` (x0ne-core/oracle/examples/core-bench.rs:6-16,420-436).
   roofline --config config.json --gpu <GB/s> --prompt P --generated N [--tok-s X] [--batch B]
@@ -85,7 +86,10 @@ def cmd_core_bench(a) -> int:
     lens = [_length_tokens(n, cfg.max_position_embeddings - a.decode) for n in names]
     max_ctx = min(cfg.max_position_embeddings, max(lens) + a.decode)
     t0 = time.time()
-    m = Model.from_folder(a.model, dtype=a.dtype, max_batch=a.batch, max_ctx=max_ctx)
+    if a.random_weights is not None:      # the folder needs only its config.json
+        m = Model.random(cfg, seed=a.random_weights, dtype=a.dtype, max_batch=a.batch, max_ctx=max_ctx)
+    else:
+        m = Model.from_folder(a.model, dtype=a.dtype, max_batch=a.batch, max_ctx=max_ctx)
     torch.cuda.synchronize()
     load_s = time.time() - t0
     results = []
@@ -301,6 +305,8 @@ def main(argv=None) -> int:
     b.add_argument("--reps", type=int, default=5)
     b.add_argument("--batch", type=int, default=1)
     b.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
+    b.add_argument("--random-weights", type=int, default=None, metavar="SEED",
+                   help="random weights made on the device from config.json alone (no safetensors needed)")
     b.set_defaults(fn=cmd_core_bench)
 
     r = sub.add_parser("roofline")

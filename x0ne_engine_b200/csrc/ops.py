@@ -74,6 +74,11 @@ def _check(lib, code: int, what: str) -> None:
 
 
 def _stream() -> c_void_p:
+    """The current stream of the current device, as a raw handle (the private accessor is some
+    forty times cheaper than building a torch.cuda.Stream object for every launch)."""
+    raw = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+    if raw is not None:
+        return c_void_p(raw(torch.cuda.current_device()))
     return c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
