@@ -348,3 +348,39 @@ def test_library_is_loaded_and_there_is_no_cpu_path():
     assert any("libx0ne_core" in p for p in libs) and any("libx0ne_fast" in p for p in libs)
     with pytest.raises(RuntimeError, match="no CPU path"):
         Engine.from_folder(model_folder("A"), dtype="float32", device="cpu")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_layers_of_the_large_shape_against_the_plain_implementation(dtype):
+    """Two layers with the sizes of the 8B shape (width 4096, 32 q heads over 8 kv heads of 128,
+    feed-forward 12288; the vocabulary cut to 5,000 so that the plain run stays short), random
+    weights made on the device: a prompt whole, then three tokens one by one, against the plain
+    implementation on the same values.  The sizes are the ones the kernels are tuned for, which the
+    tiny configurations never reach (k loops of 4096 and 12288, 32 heads, 192-row products)."""
+    import plain_impl as P
+    from x0ne_engine_b200 import Engine, Qwen3Config
+    from x0ne_engine_b200.engine import tensor_needs_of_spec
+    from x0ne_engine_b200.weights import RandomInit, make_tensor
+    cfg = Qwen3Config(hidden_size=4096, intermediate_size=12288, num_hidden_layers=2, num_attention_heads=32,
+                      num_key_value_heads=8, head_dim=128, vocab_size=5000, max_position_embeddings=4096,
+                      rms_norm_eps=1e-6, rope_theta=1000000.0, tie_word_embeddings=False, dtype="float32")
+    eng = Engine.random(cfg, seed=5, dtype=dtype, device="cuda:0", linear_std=0.02, norm_jitter=0.1, max_tokens=512)
+    init = RandomInit(5, 0.02, 0.1)
+    w = {}
+    for need in tensor_needs_of_spec(cfg.to_spec()):       # the same values, made again and taken to the host
+        t = make_tensor(need, init, torch.float32, "cuda:0")
+        if dtype == "bfloat16" and t.dim() == 2:
+            t = t.bfloat16().float()                       # what a bfloat16 engine holds of a float32 matrix
+        w[need.name] = t.cpu().numpy()
+    pc = dict(hidden=4096, inter=12288, layers=2, q_heads=32, kv_heads=8, head_dim=128, vocab=5000, eps=1e-6, theta=1e6,
+              tied=False, max_pos=4096)
+    ids = prompts_for(5000, [200], seed=21)[0]
+    want = P.forward(pc, w, ids)
+    rows = [0, 63, 64, 191, 196]
+    s = eng.new_sequence()
+    got = eng.step([s], [ids[:197]], [rows]).cpu().numpy()
+    check(dtype, got, want[rows], "prompt of 197")
+    for t in range(197, 200):
+        got = eng.step([s], [[ids[t]]]).cpu().numpy()
+        check(dtype, got, want[t:t + 1], f"token {t}")
+    eng.free_sequence(s)
