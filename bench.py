@@ -141,7 +141,6 @@ def main() -> int:
     import torch
 
     import x0ne_engine_b200 as x
-    from x0ne_engine_b200.csrc import ops
     from x0ne_engine_b200.engine.decode import DeviceBatch
     from x0ne_engine_b200.engine.generate import Row
     from x0ne_engine_b200.sampling import SamplingParams

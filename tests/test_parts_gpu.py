@@ -1,7 +1,5 @@
 """Each part of a layer alone against its plain function, and a toy mixer with state of its own that is
 registered, built and stepped without a change to the library's files."""
-import math
-
 import numpy as np
 import pytest
 import torch

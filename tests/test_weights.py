@@ -10,7 +10,7 @@ import torch
 import plain_impl as P
 from x0ne_engine_b200 import RandomInit, WeightsError, write_model_folder
 from x0ne_engine_b200.engine.model import optional_duplicates_of_spec, tensor_needs_of_spec
-from x0ne_engine_b200.weights import (SafetensorsError, TensorNeed, check, held_dtype, load_folder, make_tensor,
+from x0ne_engine_b200.weights import (SafetensorsError, TensorNeed, held_dtype, load_folder, make_tensor,
                                       open_folder, write_file)
 from helpers import model_folder, tiny_a, tiny_b
 

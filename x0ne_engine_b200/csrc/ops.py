@@ -8,7 +8,7 @@ fails; nothing here computes on the CPU or through another library.
 from __future__ import annotations
 
 import ctypes
-from ctypes import POINTER, Structure, c_float, c_int, c_int32, c_int64, c_void_p
+from ctypes import Structure, c_float, c_int, c_int32, c_int64, c_void_p
 from typing import Optional
 
 import torch

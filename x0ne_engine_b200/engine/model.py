@@ -2,12 +2,11 @@
 norm and the head.  Nothing here names an architecture."""
 from __future__ import annotations
 
-from dataclasses import dataclass
 from typing import Dict, List, Mapping, Optional
 
 import torch
 
-from ..config.spec import ModelSpec, PartSpec
+from ..config.spec import ModelSpec
 from ..parts import base as P
 from ..parts.embedding import LMHead, TokenEmbedding
 from ..weights.loader import TensorNeed

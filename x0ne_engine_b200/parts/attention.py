@@ -2,7 +2,7 @@
 from __future__ import annotations
 
 import math
-from typing import List, Mapping, Optional
+from typing import List, Mapping
 
 import torch
 

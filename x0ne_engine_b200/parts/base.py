@@ -23,7 +23,7 @@ tensors, by name, with shapes) and `bind(tensors)`, and call the kind's `registe
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Any, Callable, Dict, List, Mapping, Optional, Tuple
+from typing import Any, Dict, List, Mapping, Optional, Tuple
 
 import torch
 

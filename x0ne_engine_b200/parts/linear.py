@@ -7,8 +7,6 @@ library engine delegates these products to cuBLAS (x0ne-core/runtime/src/gpu.rs:
 """
 from __future__ import annotations
 
-from typing import Optional
-
 import torch
 
 from ..csrc import ops
