@@ -233,7 +233,8 @@ def cmd_kernel_bench(a) -> int:
         def fn():
             v = views[i[0] % copies]
             i[0] += 1
-            ops.attention_decode_bf16(q, out, v, slots, pos, B, qh, 1 / math.sqrt(hd), 0, splits, scratch)
+            ops.attention_decode_bf16(q, out, v, slots, pos, B, qh, 1 / math.sqrt(hd), 0, splits,
+                                      scratch if (a.scratch_merge or splits > ops.ATTENTION_DECODE_CLUSTER_SPLITS) else None)
         print(f"splits {splits}", file=sys.stderr)
         timed(fn, B * ctx * 2 * kvh * hd * 2, 4.0 * B * qh * hd * ctx)
         return 0
@@ -333,6 +334,8 @@ def main(argv=None) -> int:
     k.add_argument("--k", type=int, default=4096)
     k.add_argument("--batch", type=int, default=8)
     k.add_argument("--context", type=int, default=3072)
+    k.add_argument("--scratch-merge", action="store_true",
+                   help="attention_decode: merge the splits through global scratch even where a cluster could")
     k.add_argument("--q-heads", type=int, default=32)
     k.add_argument("--kv-heads", type=int, default=8)
     k.add_argument("--head-dim", type=int, default=128)

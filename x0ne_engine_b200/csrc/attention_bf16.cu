@@ -340,11 +340,35 @@ struct DecodeArgs {
     int32_t window;
     int32_t splits;
     float scale_log2;
+    int32_t cluster_merge;  // merge the splits inside a thread-block cluster (needs no scratch; splits <= 8)
 };
 
 #define DEC_MAX_PAGES 128
 
-template <int HD, int STAGES>
+// Shared memory of another block of the cluster.
+__device__ __forceinline__ uint32_t dsmem_addr(const void* local, int rank) {
+    uint32_t r;
+    asm("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_u32(local)), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ float ld_dsmem(uint32_t addr) {
+    float v;
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ float4 ld_dsmem4(uint32_t addr) {
+    float4 v;
+    asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// CLUSTER: the blocks of one (sequence, kv head) are one thread-block cluster and merge their
+// partial results through each other's shared memory (at most 8 splits); otherwise they go through
+// global scratch and the last block to arrive merges.
+template <int HD, int STAGES, bool CLUSTER>
 __global__ void __launch_bounds__(128) attention_decode_kernel(DecodeArgs a, PagedCache cache) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     constexpr int LD = HD + PADE;
@@ -490,6 +514,7 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(DecodeArgs a, Pag
     // merge the 4 warps through shared memory (the K/V stages are free now)
     float* mo = reinterpret_cast<float*>(ks);            // [4][16][HD]
     float* mml = mo + 4 * 16 * HD;                       // [4][16][2]
+    float* xml = mml + 4 * 16 * 2;                       // [16][2]: this block's (m, l) for the cluster; its o is mo[0]
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
         const int r = (lane >> 2) + 8 * h;
@@ -521,6 +546,12 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(DecodeArgs a, Pag
         }
         if (a.splits == 1) {
             a.out[(qrow0 + r) * HD + d] = __float2bfloat16_rn(acc / L);
+        } else if (CLUSTER) {
+            mo[r * HD + d] = acc;      // over the first warp's value of the same element, which only this thread read
+            if (d == 0) {
+                xml[r * 2] = M;
+                xml[r * 2 + 1] = L;
+            }
         } else {
             a.part_o[((qrow0 + r) * a.splits + split) * HD + d] = acc;
             if (d == 0) {
@@ -530,6 +561,29 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(DecodeArgs a, Pag
         }
     }
     if (a.splits == 1) return;
+    if constexpr (CLUSTER) {
+        // Every block of the cluster takes a share of the output and sums the splits in their order.
+        cluster_sync_all();
+        for (int e = split * 128 + tid; e < nheads * (HD / 4); e += 128 * a.splits) {
+            const int r = e / (HD / 4), d = (e % (HD / 4)) * 4;
+            float M = -INFINITY;
+            for (int sp = 0; sp < a.splits; ++sp) M = fmaxf(M, ld_dsmem(dsmem_addr(xml + r * 2, sp)));
+            float L = 0.f;
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int sp = 0; sp < a.splits; ++sp) {
+                const float ms = ld_dsmem(dsmem_addr(xml + r * 2, sp));
+                const float f = ms == -INFINITY ? 0.f : exp2f(ms - M);
+                L += ld_dsmem(dsmem_addr(xml + r * 2 + 1, sp)) * f;
+                const float4 v = ld_dsmem4(dsmem_addr(mo + r * HD + d, sp));
+                acc.x += v.x * f; acc.y += v.y * f; acc.z += v.z * f; acc.w += v.w * f;
+            }
+            const float il = 1.0f / L;
+            bf16* dst = a.out + (qrow0 + r) * HD + d;
+            *reinterpret_cast<uint2*>(dst) = make_uint2(pack_bf16(acc.x * il, acc.y * il), pack_bf16(acc.z * il, acc.w * il));
+        }
+        cluster_sync_all();      // nobody leaves while its shared memory may still be read
+        return;
+    }
 
     // last arriver merges the splits in their fixed order
     __threadfence();
@@ -604,15 +658,16 @@ static int launch_prefill(const PrefillArgs& a, const PagedCache& cache, int n_t
 }
 
 #define DECODE_STAGES 3
-template <int HD>
-static int launch_decode(const DecodeArgs& a, const PagedCache& cache, int n_rows, cudaStream_t stream) {
+#define DECODE_CLUSTER_MAX 8      // the largest cluster every launch may ask for
+template <int HD, bool CLUSTER>
+static int launch_decode_variant(const DecodeArgs& a, const PagedCache& cache, int n_rows, cudaStream_t stream) {
     size_t smem = (size_t)(16 + 4 * DECODE_STAGES * 2 * 16) * (HD + PADE) * sizeof(bf16);
-    const size_t merge = (size_t)(4 * 16 * HD + 4 * 16 * 2) * sizeof(float);
+    const size_t merge = (size_t)(4 * 16 * HD + 4 * 16 * 2 + 16 * 2) * sizeof(float);
     if (smem < 16 * (HD + PADE) * sizeof(bf16) + merge) smem = 16 * (HD + PADE) * sizeof(bf16) + merge;
     static bool configured = false;
     if (!configured) {
-        cudaFuncSetAttribute(attention_decode_kernel<HD, DECODE_STAGES>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
-        cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<HD, DECODE_STAGES>,
+        cudaFuncSetAttribute(attention_decode_kernel<HD, DECODE_STAGES, CLUSTER>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
+        cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<HD, DECODE_STAGES, CLUSTER>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) {
             x0ne_set_error("attention_decode: cannot set %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
@@ -622,8 +677,18 @@ static int launch_decode(const DecodeArgs& a, const PagedCache& cache, int n_row
     }
     const int G = a.q_heads / cache.kv_heads;
     dim3 grid(a.splits, cache.kv_heads * ((G + 15) / 16), n_rows);
-    x0ne_launch(attention_decode_kernel<HD, DECODE_STAGES>, dim3(grid), dim3(128), smem, stream, a, cache);
+    if (CLUSTER)
+        x0ne_launch_clusters(attention_decode_kernel<HD, DECODE_STAGES, CLUSTER>, dim3(grid), dim3(128), a.splits, smem, stream, a, cache);
+    else
+        x0ne_launch(attention_decode_kernel<HD, DECODE_STAGES, CLUSTER>, dim3(grid), dim3(128), smem, stream, a, cache);
     X0NE_LAUNCH_CHECK();
+}
+
+template <int HD>
+static int launch_decode(const DecodeArgs& a, const PagedCache& cache, int n_rows, cudaStream_t stream) {
+    if (a.cluster_merge && a.splits > 1 && a.splits <= DECODE_CLUSTER_MAX)
+        return launch_decode_variant<HD, true>(a, cache, n_rows, stream);
+    return launch_decode_variant<HD, false>(a, cache, n_rows, stream);
 }
 
 #define DISPATCH_HD(HDV, CALL)                     \
@@ -696,7 +761,9 @@ X0NE_API int x0ne_attention_decode_bf16(const void* q, void* out, PagedCache cac
     a.window = window;
     a.splits = splits;
     a.scale_log2 = scale * LOG2E;
-    if (splits > 1) {
+    if (splits > 1 && scratch == nullptr && splits <= DECODE_CLUSTER_MAX) {
+        a.cluster_merge = 1;      // no scratch given: the splits of a (sequence, kv head) merge inside their cluster
+    } else if (splits > 1) {
         const int64_t need = x0ne_attention_decode_scratch_bytes(n_rows, q_heads, cache.kv_heads, cache.head_dim, splits);
         X0NE_REQUIRE(scratch != nullptr && scratch_bytes >= need, "attention_decode: scratch of %lld bytes, %lld needed",
                      (long long)scratch_bytes, (long long)need);

@@ -286,11 +286,15 @@ def attention_decode_scratch_bytes(n_rows: int, q_heads: int, kv_heads: int, hea
                                                        c_int(head_dim), c_int(splits)))
 
 
+ATTENTION_DECODE_CLUSTER_SPLITS = 8     # splits that can merge inside one thread-block cluster
+
+
 def attention_decode_bf16(q: torch.Tensor, out: torch.Tensor, cache: PagedCacheArg, row_slot: torch.Tensor,
                           row_pos: torch.Tensor, n_rows: int, q_heads: int, scale: float, window: int, splits: int,
                           scratch: Optional[torch.Tensor]) -> None:
     """Split-KV flash decoding: one query row per sequence.  `scratch` (uint8, zero when first
-    used; the kernel leaves its counters at zero) holds the partial results when splits > 1."""
+    used; the kernel leaves its counters at zero) holds the partial results when splits > 1; without
+    it (and with at most 8 splits) the splits merge inside a thread-block cluster instead."""
     lib = _lib("fast")
     _need(q, torch.bfloat16, "q")
     _need(out, torch.bfloat16, "attention output")

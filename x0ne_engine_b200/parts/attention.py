@@ -19,13 +19,9 @@ def run_attention(ctx, q, out, view, n_rows, q_heads, scale, window):
     if not ops.fast_attention_takes(view, q.dtype):
         ops.attention_rows(q, out, view, ctx.row_slot, ctx.row_pos, n_rows, q_heads, scale, window)
     elif ctx.decode:
+        # up to 8 splits merge inside a thread-block cluster and need no scratch
         splits = decode_splits(ctx, n_rows, view.kv_heads, q_heads)
-        scratch = None
-        if splits > 1:
-            need = ops.attention_decode_scratch_bytes(n_rows, q_heads, view.kv_heads, view.head_dim, splits)
-            scratch = ctx.ws.zeroed("attn.decode_scratch", need)
-        ops.attention_decode_bf16(q, out, view, ctx.row_slot, ctx.row_pos, n_rows, q_heads, scale, window, splits,
-                                  scratch)
+        ops.attention_decode_bf16(q, out, view, ctx.row_slot, ctx.row_pos, n_rows, q_heads, scale, window, splits, None)
     else:
         kernel = ops.attention_prefill_tcgen05 if ops.attention_tc_takes(view, q.dtype) else ops.attention_prefill_bf16
         kernel(q, out, view, ctx.tile_seq, ctx.tile_row0, ctx.n_tiles, ctx.seq_first_row, ctx.seq_slot, ctx.seq_pos0,
@@ -34,11 +30,14 @@ def run_attention(ctx, q, out, view, n_rows, q_heads, scale, window):
 
 def decode_splits(ctx, n_rows: int, kv_heads: int, q_heads: int) -> int:
     """Into how many blocks each (sequence, kv head) of a decode pass is split: as many as fit on
-    the GPU at once, so that the launch is one wave, and no more than the longest context has pages."""
+    the GPU at once, so that the launch is one wave, no more than the longest context has pages, and
+    no more than a thread-block cluster holds (the splits then merge through shared memory; measured
+    at batch 1 to 4, eight splits in a cluster beat 16 or 32 through global scratch)."""
     group_chunks = (q_heads // kv_heads + 15) // 16
     blocks = max(1, n_rows * kv_heads * group_chunks)
     pages = max(1, (ctx.max_context + 63) // 64)
-    return int(max(1, min(pages, (ops.attention_decode_blocks_per_sm() * ctx.sm_count) // blocks, 32)))
+    return int(max(1, min(pages, (ops.attention_decode_blocks_per_sm() * ctx.sm_count) // blocks,
+                          ops.ATTENTION_DECODE_CLUSTER_SPLITS)))
 
 
 class GQAttention(Mixer):
