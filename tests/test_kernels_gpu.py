@@ -366,6 +366,32 @@ def run_tc_attention(q_heads, kv_heads, hd, window, lens, pos0, seq_slots, seed=
     return out, ref, float(storage.float().abs().max()), q, storage, table, slots, pos
 
 
+@pytest.mark.parametrize("m", [9, 16, 17, 33, 64])
+@pytest.mark.parametrize("n,k", [(128, 256), (200, 264), (1024, 4096), (6144, 512), (4096, 12288)])
+@pytest.mark.parametrize("out", ["bf16", "f32", "swiglu"])
+def test_skinny_tcgen05_product(m, n, k, out):
+    """The tcgen05 product for 9 to 64 rows (K cut over a cluster, partial sums added through shared
+    memory) against float64: widths that are no multiples of the tiles, every output kind, and the
+    same bits on a second call."""
+    o = ops()
+    swiglu = out == "swiglu"
+    x = rnd((m, k), torch.bfloat16, 90)
+    w = rnd(((2 if swiglu else 1) * n, k), torch.bfloat16, 91, 1.0 / math.sqrt(k))
+    y = torch.full((m, n), 7.0, dtype=torch.float32 if out == "f32" else torch.bfloat16, device=DEV)
+    assert o.gemm_skinny_tc_takes(w, m)
+    o.gemm_bf16_skinny_tcgen05(x, w, y, m, swiglu=swiglu)
+    o.check_tc_status(x.device)
+    ref = x.double() @ w.double().T
+    if swiglu:
+        g, u = ref[:, :n], ref[:, n:]
+        ref = g / (1 + torch.exp(-g)) * u
+    tol = 1e-5 if out == "f32" else BF16_EPS
+    assert float((y.double() - ref).abs().max() / ref.abs().max()) < tol
+    y2 = torch.empty_like(y)
+    o.gemm_bf16_skinny_tcgen05(x, w, y2, m, swiglu=swiglu)
+    assert torch.equal(y, y2)
+
+
 @pytest.mark.parametrize("q_heads,kv_heads,hd", [(8, 2, 64), (4, 1, 128), (3, 3, 64), (10, 5, 128)])
 @pytest.mark.parametrize("window", [0, 3, 64, 100])
 def test_prefill_attention_tcgen05_equals_plain_kernel(q_heads, kv_heads, hd, window):

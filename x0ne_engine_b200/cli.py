@@ -184,7 +184,7 @@ def cmd_kernel_bench(a) -> int:
                           "copies": copies}))
 
     if a.kernel in ("gemm_smallm", "gemm_smallm_swiglu", "gemm_library", "gemm_tc", "gemm_tc_swiglu", "gemm_tc1",
-                    "gemm_tc1_swiglu"):
+                    "gemm_tc1_swiglu", "gemm_skinny", "gemm_skinny_swiglu"):
         swiglu = a.kernel.endswith("_swiglu")
         rows = 2 * a.n if swiglu else a.n
         wbytes = rows * a.k * 2
@@ -199,6 +199,8 @@ def cmd_kernel_bench(a) -> int:
             i[0] += 1
             if a.kernel == "gemm_library":
                 torch.mm(x[:a.m], w.t(), out=y[:a.m])
+            elif a.kernel.startswith("gemm_skinny"):
+                ops.gemm_bf16_skinny_tcgen05(x, w, y, a.m, swiglu=swiglu)
             elif a.kernel.startswith("gemm_tc"):
                 ops.gemm_bf16_tcgen05(x, w, y, a.m, swiglu=swiglu, pair=not a.kernel.startswith("gemm_tc1"))
             else:
@@ -225,7 +227,7 @@ def cmd_kernel_bench(a) -> int:
         class Ctx:
             max_context = ctx
             sm_count = torch.cuda.get_device_properties(0).multi_processor_count
-        splits = a.splits or decode_splits(Ctx, B, kvh, qh)
+        splits = a.splits or decode_splits(Ctx, B, kvh, qh, hd)
         scratch = torch.zeros(max(1, ops.attention_decode_scratch_bytes(B, qh, kvh, hd, splits)), dtype=torch.uint8,
                               device=dev)
         i = [0]

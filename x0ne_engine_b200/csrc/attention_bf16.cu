@@ -734,6 +734,42 @@ X0NE_API int x0ne_attention_prefill_tile_rows() { return 64 * PREFILL_MT; }
 // size `splits` so that a launch is one wave.
 X0NE_API int x0ne_attention_decode_blocks_per_sm() { return DECODE_STAGES <= 2 ? 3 : (DECODE_STAGES == 3 ? 2 : 1); }
 
+// How many clusters of `splits` blocks of the decode kernel the GPU holds at once (they do not pack
+// its GPCs completely, so this is less than resident blocks / splits); 0 if unknown.  Callers keep
+// (sequences x kv heads x group chunks) within it so that a launch is one wave.
+template <int HD>
+static int decode_max_clusters(int splits) {
+    size_t smem = (size_t)(16 + 4 * DECODE_STAGES * 2 * 16) * (HD + PADE) * sizeof(bf16);
+    const size_t merge = (size_t)(4 * 16 * HD + 4 * 16 * 2 + 16 * 2) * sizeof(float);
+    if (smem < 16 * (HD + PADE) * sizeof(bf16) + merge) smem = 16 * (HD + PADE) * sizeof(bf16) + merge;
+    auto kernel = attention_decode_kernel<HD, DECODE_STAGES, true>;
+    cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return 0;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(splits, 1024, 1);
+    cfg.blockDim = dim3(128);
+    cfg.dynamicSmemBytes = smem;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = splits;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    return n;
+}
+
+X0NE_API int x0ne_attention_decode_max_clusters(int head_dim, int splits) {
+    if (splits < 1 || splits > DECODE_CLUSTER_MAX) return 0;
+    DISPATCH_HD(head_dim, return decode_max_clusters<HD_>(splits));
+    return 0;
+}
+
 // Scratch the decode kernel needs for `n_rows` sequences with `splits` splits, in bytes:
 // partial outputs, partial (m, l), and the arrival counters (which must start at zero).
 X0NE_API int64_t x0ne_attention_decode_scratch_bytes(int n_rows, int q_heads, int kv_heads, int head_dim, int splits) {

@@ -35,7 +35,7 @@ MODULES: Dict[str, List[str]] = {
     "core": ["elementwise.cu", "attention_generic.cu", "gemm_f32.cu", "sampling.cu"],
     "fast": ["attention_bf16.cu", "gemm_bf16.cu", "fast_common.cu"],
     "noalloc": ["attention_decode_noalloc.cu"],
-    "tc": ["gemm_tcgen05.cu", "attention_tcgen05.cu", "fast_common.cu"],
+    "tc": ["gemm_tcgen05.cu", "gemm_skinny_tcgen05.cu", "attention_tcgen05.cu", "fast_common.cu"],
 }
 HEADERS = ["common.cuh"]
 # files a module's sources include besides the headers (they change its hash too)

@@ -279,6 +279,17 @@ def attention_decode_blocks_per_sm() -> int:
     return int(_lib("fast").x0ne_attention_decode_blocks_per_sm())
 
 
+_max_clusters = {}
+
+
+def attention_decode_max_clusters(head_dim: int, splits: int) -> int:
+    """Clusters of `splits` blocks of the decode kernel that run at once on this GPU (0: unknown)."""
+    key = (torch.cuda.current_device(), head_dim, splits)
+    if key not in _max_clusters:
+        _max_clusters[key] = int(_lib("fast").x0ne_attention_decode_max_clusters(c_int(head_dim), c_int(splits)))
+    return _max_clusters[key]
+
+
 def attention_decode_scratch_bytes(n_rows: int, q_heads: int, kv_heads: int, head_dim: int, splits: int) -> int:
     lib = _lib("fast")
     lib.x0ne_attention_decode_scratch_bytes.restype = c_int64
@@ -417,6 +428,50 @@ def gemm_bf16_tcgen05(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, m: int,
     _check(lib, lib.x0ne_gemm_bf16_tcgen05(_ptr(w), _ptr(x), _ptr(y), c_int(m), c_int(n), c_int(k), c_int(n),
                                            c_int(kind), c_int(1 if pair else 0), _ptr(gemm_tc_status(w.device)),
                                            _stream()), "gemm_bf16_tcgen05")
+
+
+SKINNY_MIN_ROWS, SKINNY_MAX_ROWS = 9, 64
+
+
+def gemm_skinny_tc_takes(w: torch.Tensor, m: int) -> bool:
+    """Whether the tcgen05 product for few rows takes this shape (more rows than the weight-streaming
+    kernel is best at, few enough for one accumulator tile)."""
+    return w.dtype == torch.bfloat16 and SKINNY_MIN_ROWS <= m <= SKINNY_MAX_ROWS and w.shape[1] % 8 == 0
+
+
+def gemm_skinny_tc_wins(w: torch.Tensor, m: int, swiglu: bool = False) -> bool:
+    """Where the engine uses it: always with the SwiGLU epilogue (it saves a kernel and the round
+    trip of gate and up), for long rows (K at least twice N, the down projection: every block then
+    streams long enough to pay for the cluster's merge), and up to 16 rows for every matrix;
+    measured at 16 and 64 rows: at 64 the library product is faster on the squarer matrices."""
+    big = w.numel() >= (1 << 20)      # below about 2 MB a product is launch latency whatever runs it
+    return gemm_skinny_tc_takes(w, m) and big and (swiglu or m <= 16 or w.shape[1] >= 2 * w.shape[0])
+
+
+def gemm_bf16_skinny_tcgen05(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, m: int, swiglu: bool = False) -> None:
+    """y[:m] = x[:m] @ w.T for up to 64 rows on tcgen05, K cut over the blocks of a cluster that add
+    their partial sums through shared memory; y is bfloat16 or float32.  With `swiglu`, w is the
+    packed [gate; up] weight and y[:m] = silu(x gate^T) * (x up^T).  Failures of its bounded waits
+    show in `gemm_tc_status`."""
+    global tc_used
+    lib = _lib("tc")
+    _need(x, torch.bfloat16, "gemm input")
+    _need(w, torch.bfloat16, "gemm weight")
+    _need(y, y.dtype, "gemm output")
+    rows, k = w.shape
+    n = rows // 2 if swiglu else rows
+    if x.shape[-1] != k or y.shape[-1] != n or x.numel() < m * k or y.numel() < m * n or (swiglu and rows % 2):
+        raise KernelError(f"gemm_skinny_tc: shapes x {tuple(x.shape)} w {tuple(w.shape)} y {tuple(y.shape)} m {m}")
+    if y.dtype == torch.float32 and not swiglu:
+        kind = 1
+    elif y.dtype == torch.bfloat16:
+        kind = 2 if swiglu else 0
+    else:
+        raise KernelError(f"gemm_skinny_tc: no output kind for {y.dtype} (swiglu={swiglu})")
+    tc_used = True
+    x_rows = x.numel() // k      # rows really behind x: the copies may read them all (their results are not used)
+    _check(lib, lib.x0ne_gemm_bf16_skinny_tcgen05(_ptr(w), _ptr(x), c_int(x_rows), _ptr(y), c_int(m), c_int(n), c_int(k), c_int(n), c_int(kind),
+                                                  _ptr(gemm_tc_status(x.device)), _stream()), "gemm_bf16_skinny_tcgen05")
 
 
 def attention_tc_takes(cache: PagedCacheArg, dtype: torch.dtype) -> bool:

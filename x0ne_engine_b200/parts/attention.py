@@ -20,7 +20,7 @@ def run_attention(ctx, q, out, view, n_rows, q_heads, scale, window):
         ops.attention_rows(q, out, view, ctx.row_slot, ctx.row_pos, n_rows, q_heads, scale, window)
     elif ctx.decode:
         # up to 8 splits merge inside a thread-block cluster and need no scratch
-        splits = decode_splits(ctx, n_rows, view.kv_heads, q_heads)
+        splits = decode_splits(ctx, n_rows, view.kv_heads, q_heads, view.head_dim)
         ops.attention_decode_bf16(q, out, view, ctx.row_slot, ctx.row_pos, n_rows, q_heads, scale, window, splits, None)
     else:
         kernel = ops.attention_prefill_tcgen05 if ops.attention_tc_takes(view, q.dtype) else ops.attention_prefill_bf16
@@ -28,16 +28,24 @@ def run_attention(ctx, q, out, view, n_rows, q_heads, scale, window):
                q_heads, scale, window)
 
 
-def decode_splits(ctx, n_rows: int, kv_heads: int, q_heads: int) -> int:
-    """Into how many blocks each (sequence, kv head) of a decode pass is split: as many as fit on
-    the GPU at once, so that the launch is one wave, no more than the longest context has pages, and
-    no more than a thread-block cluster holds (the splits then merge through shared memory; measured
-    at batch 1 to 4, eight splits in a cluster beat 16 or 32 through global scratch)."""
+def decode_splits(ctx, n_rows: int, kv_heads: int, q_heads: int, head_dim: int = 128) -> int:
+    """Into how many blocks each (sequence, kv head) of a decode pass is split: the most for which
+    all blocks run at once (one wave), no more than the longest context has pages, and no more than
+    a thread-block cluster holds (the splits merge through shared memory; measured at batch 1 to 4,
+    eight splits in a cluster beat 16 or 32 through global scratch).  How many clusters of a size
+    fit is asked of the runtime: they do not pack the GPU completely (288 blocks in clusters of 3
+    or 4 took two waves)."""
     group_chunks = (q_heads // kv_heads + 15) // 16
-    blocks = max(1, n_rows * kv_heads * group_chunks)
+    units = max(1, n_rows * kv_heads * group_chunks)
     pages = max(1, (ctx.max_context + 63) // 64)
-    return int(max(1, min(pages, (ops.attention_decode_blocks_per_sm() * ctx.sm_count) // blocks,
-                          ops.ATTENTION_DECODE_CLUSTER_SPLITS)))
+    for splits in range(min(pages, ops.ATTENTION_DECODE_CLUSTER_SPLITS), 1, -1):
+        fit = ops.attention_decode_max_clusters(head_dim, splits)
+        if fit <= 0:      # unknown: assume seven eighths of the resident blocks
+            resident = ops.attention_decode_blocks_per_sm() * ctx.sm_count
+            fit = (resident - resident // 8) // splits
+        if units <= fit:
+            return splits
+    return 1
 
 
 class GQAttention(Mixer):

@@ -29,6 +29,8 @@ class Linear:
             ops.gemm_f32_nt(x, w, out, m)
         elif ops.gemm_smallm_takes(w, m):
             ops.gemm_bf16_smallm(x, w, out, m)
+        elif ops.gemm_skinny_tc_wins(w, m):
+            ops.gemm_bf16_skinny_tcgen05(x, w, out, m)
         elif w.dtype == torch.bfloat16:
             if m > 0:
                 if out.dtype == torch.bfloat16:
