@@ -29,7 +29,9 @@ class Linear:
             ops.gemm_f32_nt(x, w, out, m)
         elif ops.gemm_smallm_takes(w, m):
             ops.gemm_bf16_smallm(x, w, out, m)
-        elif ops.gemm_skinny_tc_wins(w, m):
+        elif out.dtype == torch.bfloat16 and ops.gemm_skinny_tc_wins(w, m):
+            # (not for the float32 logits: the vocabulary's 1,187 tiles of 128 rows are 4.01 waves of
+            # blocks, and the library product is faster there: 203 us against 247 us at 12 rows)
             ops.gemm_bf16_skinny_tcgen05(x, w, out, m)
         elif w.dtype == torch.bfloat16:
             if m > 0:
