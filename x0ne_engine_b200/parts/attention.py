@@ -28,24 +28,33 @@ def run_attention(ctx, q, out, view, n_rows, q_heads, scale, window):
                q_heads, scale, window)
 
 
+# what a decode attention block costs besides walking its pages (table look-ups, first slice, merges),
+# in pages' worth of time: about 3 us against 0.3 us per page
+DECODE_BLOCK_FIXED_PAGES = 10
+
+
 def decode_splits(ctx, n_rows: int, kv_heads: int, q_heads: int, head_dim: int = 128) -> int:
-    """Into how many blocks each (sequence, kv head) of a decode pass is split: the most for which
-    all blocks run at once (one wave), no more than the longest context has pages, and no more than
-    a thread-block cluster holds (the splits merge through shared memory; measured at batch 1 to 4,
-    eight splits in a cluster beat 16 or 32 through global scratch).  How many clusters of a size
-    fit is asked of the runtime: they do not pack the GPU completely (288 blocks in clusters of 3
-    or 4 took two waves)."""
+    """Into how many blocks each (sequence, kv head) of a decode pass is split.  The splits of one
+    are a thread-block cluster (at most 8) and merge through shared memory.  With `fit(s)` clusters
+    of s blocks running at once (asked of the runtime: clusters do not pack the GPU completely,
+    296 blocks but only 71 clusters of 4), a launch takes ceil(units / fit(s)) waves of blocks that
+    each walk pages / s pages and cost a fixed start and merge besides; the split with the shortest
+    total wins.  So a small batch is split until it fills the GPU once, and a batch of 48
+    sequences, whose 384 blocks would be 1.3 waves, is split in two (three shorter waves)."""
     group_chunks = (q_heads // kv_heads + 15) // 16
     units = max(1, n_rows * kv_heads * group_chunks)
     pages = max(1, (ctx.max_context + 63) // 64)
-    for splits in range(min(pages, ops.ATTENTION_DECODE_CLUSTER_SPLITS), 1, -1):
+    best, best_cost = 1, None
+    for splits in range(1, min(pages, ops.ATTENTION_DECODE_CLUSTER_SPLITS) + 1):
         fit = ops.attention_decode_max_clusters(head_dim, splits)
         if fit <= 0:      # unknown: assume seven eighths of the resident blocks
             resident = ops.attention_decode_blocks_per_sm() * ctx.sm_count
-            fit = (resident - resident // 8) // splits
-        if units <= fit:
-            return splits
-    return 1
+            fit = max(1, (resident - resident // 8) // splits)
+        waves = -(-units // fit)
+        cost = waves * (pages / splits + DECODE_BLOCK_FIXED_PAGES)
+        if best_cost is None or cost < best_cost - 1e-9:
+            best, best_cost = splits, cost
+    return best
 
 
 class GQAttention(Mixer):
