@@ -384,3 +384,53 @@ def test_layers_of_the_large_shape_against_the_plain_implementation(dtype):
         got = eng.step([s], [[ids[t]]]).cpu().numpy()
         check(dtype, got, want[t:t + 1], f"token {t}")
     eng.free_sequence(s)
+
+
+ODD_CONFIGS = [
+    # hidden, inter, layers, q heads, kv heads, head_dim, vocab, eps, theta, tied
+    (100, 172, 2, 6, 3, 80, 257, 1e-6, 1e4, True),        # width no multiple of 8: the products go to the library
+    (136, 264, 1, 7, 7, 16, 1000, 2e-5, 5e5, False),      # as many kv heads as q heads
+    (72, 200, 3, 10, 2, 112, 333, 1e-6, 1e6, False),      # group of five, head size 112
+    (64, 96, 2, 2, 1, 144, 129, 1e-5, 1e4, True),         # head size past 128: the plain attention kernel in both dtypes
+    (192, 328, 2, 12, 4, 64, 515, 1e-6, 2e4, False),      # head size 64: the tcgen05 attention kernel
+]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("shape", ODD_CONFIGS, ids=[f"h{c[0]}_hd{c[5]}_{c[3]}over{c[4]}" for c in ODD_CONFIGS])
+def test_sizes_at_the_edges_of_what_the_kernels_take(shape, dtype):
+    """Head sizes in steps of 16 up to past the tensor-core kernels' limit, odd widths and
+    vocabularies, any grouping: every kernel either takes the size or hands it to one that does;
+    a prompt whole, two unequal prompts in one step, then tokens one by one, against the plain run."""
+    import plain_impl as P
+    from x0ne_engine_b200 import Engine, Qwen3Config
+    from x0ne_engine_b200.engine import tensor_needs_of_spec
+    from x0ne_engine_b200.weights import RandomInit, make_tensor
+    h, inter, layers, qh, kvh, hd, vocab, eps, theta, tied = shape
+    cfg = Qwen3Config(hidden_size=h, intermediate_size=inter, num_hidden_layers=layers, num_attention_heads=qh,
+                      num_key_value_heads=kvh, head_dim=hd, vocab_size=vocab, max_position_embeddings=512,
+                      rms_norm_eps=eps, rope_theta=theta, tie_word_embeddings=tied, dtype="float32")
+    eng = Engine.random(cfg, seed=31, dtype=dtype, device="cuda:0", linear_std=0.05, norm_jitter=0.1, max_tokens=1024)
+    init = RandomInit(31, 0.05, 0.1)
+    w = {}
+    for need in tensor_needs_of_spec(cfg.to_spec()):
+        t = make_tensor(need, init, torch.float32, "cpu")
+        if dtype == "bfloat16" and t.dim() == 2:
+            t = t.bfloat16().float()
+        w[need.name] = t.numpy()
+    pc = dict(hidden=h, inter=inter, layers=layers, q_heads=qh, kv_heads=kvh, head_dim=hd, vocab=vocab, eps=eps,
+              theta=theta, tied=tied, max_pos=512)
+    a, b = prompts_for(vocab, [150, 40], seed=33)
+    want_a, want_b = P.forward(pc, w, a), P.forward(pc, w, b)
+    sa, sb = eng.new_sequence(), eng.new_sequence()
+    got = eng.step([sa, sb], [a[:140], b[:33]], [[0, 63, 64, 127, 128, 139], [0, 32]]).cpu().numpy()
+    check(dtype, got[:6], want_a[[0, 63, 64, 127, 128, 139]], "long prompt")
+    check(dtype, got[6:], want_b[[0, 32]], "short prompt")
+    for t in range(7):
+        got = eng.step([sa, sb], [[a[140 + t]], [b[33 + t]]]).cpu().numpy()
+        check(dtype, got[:1], want_a[140 + t:141 + t], f"long, token {t}")
+        check(dtype, got[1:], want_b[33 + t:34 + t], f"short, token {t}")
+    eng.free_sequence(sb)
+    for t in range(147, 150):
+        check(dtype, eng.step([sa], [[a[t]]]).cpu().numpy(), want_a[t:t + 1], f"long alone, token {t}")
+    eng.free_sequence(sa)
