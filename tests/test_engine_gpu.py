@@ -364,7 +364,7 @@ def test_layers_of_the_large_shape_against_the_plain_implementation(dtype):
     cfg = Qwen3Config(hidden_size=4096, intermediate_size=12288, num_hidden_layers=2, num_attention_heads=32,
                       num_key_value_heads=8, head_dim=128, vocab_size=5000, max_position_embeddings=4096,
                       rms_norm_eps=1e-6, rope_theta=1000000.0, tie_word_embeddings=False, dtype="float32")
-    eng = Engine.random(cfg, seed=5, dtype=dtype, device="cuda:0", linear_std=0.02, norm_jitter=0.1, max_tokens=512)
+    eng = Engine.random(cfg, seed=5, dtype=dtype, device="cuda:0", linear_std=0.02, norm_jitter=0.1, max_tokens=2048)
     init = RandomInit(5, 0.02, 0.1)
     w = {}
     for need in tensor_needs_of_spec(cfg.to_spec()):       # the same values, made again and taken to the host
@@ -384,6 +384,19 @@ def test_layers_of_the_large_shape_against_the_plain_implementation(dtype):
         got = eng.step([s], [[ids[t]]]).cpu().numpy()
         check(dtype, got, want[t:t + 1], f"token {t}")
     eng.free_sequence(s)
+    # twelve sequences at once (three prompts, four copies each, interleaved): the products for 9 to
+    # 64 rows and the decode attention in clusters run at these sizes only
+    prompts = prompts_for(5000, [5, 9, 12], seed=22)
+    wants = [P.forward(pc, w, p) for p in prompts]
+    order = [0, 1, 2] * 4
+    slots = [eng.new_sequence() for _ in order]
+    eng.step(slots, [prompts[i][:-2] for i in order], [[] for _ in order])
+    for back in (2, 1):
+        got = eng.step(slots, [[prompts[i][-back]] for i in order]).cpu().numpy()
+        for row, i in enumerate(order):
+            check(dtype, got[row:row + 1], wants[i][len(prompts[i]) - back][None], f"copy {row} of prompt {i}, {back} from the end")
+    for sl in slots:
+        eng.free_sequence(sl)
 
 
 ODD_CONFIGS = [
