@@ -17,7 +17,7 @@
 // accumulate side by side, and the epilogue writes silu(gate) * up (x0ne-core/kernels/cuda/
 // swiglu.cu:5-11 without the intermediate bfloat16 rounding).
 //
-// No TMA multicast is used.  Every barrier wait is bounded (about a second); when one runs out the
+// Every block fetches its own operands.  Every barrier wait is bounded (about a second); when one runs out the
 // kernel records where in `status`, skips the rest, still frees its tensor memory, and returns.
 #include "tcgen05.cuh"
 
@@ -201,7 +201,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
 // shared memory.  Per flop, half as many bytes cross from L2 to shared memory as with single
 // blocks, and a stage is 32 KB, so six stages fit.
 //   * "full" barriers live in the first block and count the bytes of both blocks' copies (the
-//     second block's copies name the first block's barrier; no copy is multicast);
+//     second block's copies name the first block's barrier; each block fetches its own operands);
 //   * tcgen05.commit arrives on the "empty" and "accumulator ready" barriers of both blocks;
 //   * the epilogue threads of both blocks arrive on the first block's "accumulator drained" barrier.
 // With SwiGLU the first block's W rows are the gate rows and the second block's the up rows, so the
