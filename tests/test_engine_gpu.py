@@ -447,3 +447,35 @@ def test_sizes_at_the_edges_of_what_the_kernels_take(shape, dtype):
     for t in range(147, 150):
         check(dtype, eng.step([sa], [[a[t]]]).cpu().numpy(), want_a[t:t + 1], f"long alone, token {t}")
     eng.free_sequence(sa)
+
+
+def test_long_prompt_at_the_large_shape_bfloat16_against_the_32_bit_path():
+    """1,500 tokens through two layers of the 8B shape: here the bfloat16 engine runs its
+    large-pass kernels (tcgen05 attention over 12 row tiles, the fused tcgen05 gate/up product from
+    768 rows), which the plain implementation is too slow to check; the 32-bit path, which the other
+    tests tie to the plain implementation, stands in for it on the same bfloat16-rounded matrices."""
+    from x0ne_engine_b200 import Engine, Qwen3Config
+    from x0ne_engine_b200.engine import tensor_needs_of_spec
+    from x0ne_engine_b200.weights import RandomInit, make_tensor
+    cfg = Qwen3Config(hidden_size=4096, intermediate_size=12288, num_hidden_layers=2, num_attention_heads=32,
+                      num_key_value_heads=8, head_dim=128, vocab_size=5000, max_position_embeddings=4096,
+                      rms_norm_eps=1e-6, rope_theta=1000000.0, tie_word_embeddings=False, dtype="float32")
+    init = RandomInit(6, 0.02, 0.1)
+    tensors = {}
+    for need in tensor_needs_of_spec(cfg.to_spec()):
+        t = make_tensor(need, init, torch.float32, "cuda:0")
+        tensors[need.name] = t.bfloat16().float() if t.dim() == 2 else t
+    ids = prompts_for(5000, [1503], seed=23)[0]
+    rows = [0, 127, 128, 767, 768, 1023, 1499]
+    got = {}
+    for dtype in ("float32", "bfloat16"):
+        held = {k: (v.bfloat16() if dtype == "bfloat16" and v.dim() == 2 else v) for k, v in tensors.items()}
+        eng = Engine(cfg.to_spec(), held, dtype, "cuda:0", max_tokens=2048)
+        s = eng.new_sequence()
+        out = [eng.step([s], [ids[:1500]], [rows]).cpu().numpy()]
+        out += [eng.step([s], [[t]]).cpu().numpy() for t in ids[1500:]]
+        eng.free_sequence(s)
+        got[dtype] = np.concatenate(out)
+        del eng, held
+        torch.cuda.empty_cache()
+    assert_close_bf16(got["bfloat16"], got["float32"], "1,500 tokens at the large shape")
