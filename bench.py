@@ -36,15 +36,33 @@ def peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     src = "fallback"
     hbm, tf, tf_s = FALLBACK_HBM_GBS, FALLBACK_BF16_TFLOPS, None
+    def num(v, default):
+        """A number, also when the file wraps it ({"value": ...}) or lists several (their median)."""
+        if isinstance(v, dict):
+            for key in ("value", "median", "mean", "gbs", "tflops"):
+                if key in v:
+                    return num(v[key], default)
+            return default
+        if isinstance(v, (list, tuple)) and v:
+            vals = sorted(num(x, default) for x in v)
+            return vals[len(vals) // 2]
+        try:
+            return float(v)
+        except (TypeError, ValueError):
+            return default
+
     try:
         with open(path) as f:
             d = json.load(f)
-        hbm = float(d.get("hbm_gbs", hbm))
-        tf = float(d.get("bf16_tflops", tf))
-        tf_s = d.get("bf16_tflops_sustained")
-        src = "measured"
+        if isinstance(d, dict) and ("hbm_gbs" in d or "bf16_tflops" in d):
+            hbm = num(d.get("hbm_gbs"), hbm)
+            tf = num(d.get("bf16_tflops"), tf)
+            tf_s = num(d.get("bf16_tflops_sustained"), None) if "bf16_tflops_sustained" in d else None
+            src = "measured"
     except (OSError, ValueError):
         pass
+    if not (hbm > 0 and tf > 0):
+        hbm, tf, src = FALLBACK_HBM_GBS, FALLBACK_BF16_TFLOPS, "fallback"
     return dict(hbm_gbs=hbm, bf16_tflops=tf, bf16_tflops_sustained=tf_s, source=src)
 
 
