@@ -317,6 +317,10 @@ __global__ void __launch_bounds__(ATC_THREADS, 2) attention_prefill_tc_kernel(co
             // The halves exchange their maxima rounded up to bfloat16 (a reference may lie above the
             // true maximum; it must only be the same for the whole row).
             const __nv_bfloat16 mine = __float2bfloat16_ru(fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])));
+            // The other half must have read the maximum of the page before, and the scores come a
+            // page ahead, so nothing else orders that: every thread reads it before it arrives on
+            // p_ready, so wait for that phase (it completes about when this thread arrived itself).
+            if (i > 0 && !(ok = mbar_wait(&sh->p_ready, (i - 1) & 1, status, 18))) break;
             sh->xmax[half][r] = mine;
             mbar_arrive(&sh->pair[sw]);
             ATC_T(2);

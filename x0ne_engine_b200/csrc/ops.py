@@ -391,7 +391,7 @@ def check_tc_status(device) -> None:
         codes = [b for b in range(32) if st >> b & 1]
         raise KernelError(f"a tcgen05 kernel gave up waiting on a barrier (codes {codes}; products: 1 copy, 2 MMA, "
                           "3 epilogue, 4 accumulator; attention: 5 queries, 6 keys, 13 and 15 values, 7 probabilities, "
-                          "8, 11 and 14 output, 10, 12 and 17 scores, 16 the other half of the row; 9: misaligned "
+                          "8, 11 and 14 output, 10, 12 and 17 scores, 16 and 18 the other half of the row; 9: misaligned "
                           "shared memory); its output is not valid")
 
 
