@@ -48,11 +48,38 @@ class SampleIOArg(Structure):
 _libs = {}
 
 
+_P, _I, _F, _L = c_void_p, c_int, c_float, c_int64
+# Argument types of the entry points, declared once per library: ctypes then converts plain Python
+# numbers itself, which is about a third of the cost of building a c_int or c_void_p per argument
+# and per call (1.4 us against 3.8 us for ten arguments).  Pointers are passed as integers.
+_SIGNATURES = {
+    "x0ne_embedding": [_P, _I, _P, _P, _I, _I, _I, _P],
+    "x0ne_add_rmsnorm": [_P, _P, _P, _P, _I, _P, _I, _I, _F, _P],
+    "x0ne_qk_norm_rope_kv_write": [_P, _I, _P, _P, _P, _I, _P, None, _P, _P, _I, _I, _F, _I, _P, _I, _P],
+    "x0ne_swiglu": [_P, _P, _I, _I, _I, _P],
+    "x0ne_attention_rows": [_P, _P, _I, None, _P, _P, _I, _I, _F, _I, _P],
+    "x0ne_gemm_f32_nt": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
+    "x0ne_attention_prefill_bf16": [_P, _P, None, _P, _P, _I, _P, _P, _P, _I, _F, _I, _P],
+    "x0ne_attention_decode_bf16": [_P, _P, None, _P, _P, _I, _I, _F, _I, _I, _P, _L, _P],
+    "x0ne_gemm_bf16_smallm": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
+    "x0ne_attention_prefill_tcgen05": [_P, _P, _I, None, _P, _P, _I, _P, _P, _P, _I, _F, _I, _P, _P],
+    "x0ne_gemm_bf16_tcgen05": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _P],
+    "x0ne_gemm_bf16_skinny_tcgen05": [_P, _P, _I, _P, _I, _I, _I, _I, _I, _P, _P],
+    "x0ne_sample": ["io", _I, _P],
+}
+
+
 def _lib(name: str) -> ctypes.CDLL:
     lib = _libs.get(name)
     if lib is None:
         lib = _build.load(name)
         lib.x0ne_last_error.restype = ctypes.c_char_p
+        for fn_name, args in _SIGNATURES.items():
+            fn = getattr(lib, fn_name, None)
+            if fn is not None:
+                # None: the cache view, by value; "io": the sampler's arguments, by value
+                fn.argtypes = [PagedCacheArg if a is None else SampleIOArg if a == "io" else a for a in args]
+                fn.restype = c_int
         _libs[name] = lib
     return lib
 
@@ -73,17 +100,17 @@ def _check(lib, code: int, what: str) -> None:
         raise KernelError(f"{what}: {msg.decode() if msg else 'error'} (code {code})")
 
 
-def _stream() -> c_void_p:
+def _stream() -> int:
     """The current stream of the current device, as a raw handle (the private accessor is some
     forty times cheaper than building a torch.cuda.Stream object for every launch)."""
     raw = getattr(torch._C, "_cuda_getCurrentRawStream", None)
     if raw is not None:
-        return c_void_p(raw(torch.cuda.current_device()))
-    return c_void_p(torch.cuda.current_stream().cuda_stream)
+        return raw(torch.cuda.current_device())
+    return torch.cuda.current_stream().cuda_stream
 
 
-def _ptr(t: Optional[torch.Tensor]) -> c_void_p:
-    return c_void_p(0 if t is None else t.data_ptr())
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
 
 
 def _need(t: torch.Tensor, dtype, what: str) -> None:
@@ -104,8 +131,8 @@ def embedding(table: torch.Tensor, tokens: torch.Tensor, resid: torch.Tensor, n_
     vocab, hidden = table.shape
     if resid.shape[-1] != hidden or resid.numel() < n_rows * hidden or tokens.numel() < n_rows:
         raise KernelError("embedding: buffers are smaller than the rows asked for")
-    _check(lib, lib.x0ne_embedding(_ptr(table), c_int(dtype_tag(table.dtype)), _ptr(tokens), _ptr(resid),
-                                   c_int(n_rows), c_int(hidden), c_int(vocab), _stream()), "embedding")
+    _check(lib, lib.x0ne_embedding(_ptr(table), dtype_tag(table.dtype), _ptr(tokens), _ptr(resid),
+                                   n_rows, hidden, vocab, _stream()), "embedding")
 
 
 def add_rmsnorm(resid: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, out: torch.Tensor,
@@ -128,8 +155,8 @@ def add_rmsnorm(resid: torch.Tensor, delta: Optional[torch.Tensor], weight: torc
         raise KernelError("add_rmsnorm: residual smaller than the rows asked for")
     if resid.shape[-1] != hidden or out.shape[-1] != hidden or out.numel() < n_rows * hidden:
         raise KernelError("add_rmsnorm: widths differ or output too small")
-    _check(lib, lib.x0ne_add_rmsnorm(_ptr(resid), _ptr(delta), _ptr(weight), _ptr(out), c_int(dtype_tag(out.dtype)),
-                                     _ptr(rows), c_int(n_rows), c_int(hidden), c_float(eps), _stream()), "add_rmsnorm")
+    _check(lib, lib.x0ne_add_rmsnorm(_ptr(resid), _ptr(delta), _ptr(weight), _ptr(out), dtype_tag(out.dtype),
+                                     _ptr(rows), n_rows, hidden, eps, _stream()), "add_rmsnorm")
 
 
 def qk_norm_rope_kv_write(qkv: torch.Tensor, q_norm: Optional[torch.Tensor], k_norm: Optional[torch.Tensor],
@@ -166,9 +193,9 @@ def qk_norm_rope_kv_write(qkv: torch.Tensor, q_norm: Optional[torch.Tensor], k_n
             raise KernelError("rope: the table is not [positions, rotary_dim]")
         table_positions = rope_table.shape[0]
     _check(lib, lib.x0ne_qk_norm_rope_kv_write(
-        _ptr(qkv), c_int(dtype_tag(qkv.dtype)), _ptr(q_norm), _ptr(k_norm), _ptr(inv_freq), c_int(rotary_dim),
-        _ptr(q_out), cache, _ptr(row_slot), _ptr(row_pos), c_int(n_rows), c_int(q_heads), c_float(eps),
-        c_int(1 if write_kv else 0), _ptr(rope_table), c_int(table_positions), _stream()), "qk_norm_rope_kv_write")
+        _ptr(qkv), dtype_tag(qkv.dtype), _ptr(q_norm), _ptr(k_norm), _ptr(inv_freq), rotary_dim,
+        _ptr(q_out), cache, _ptr(row_slot), _ptr(row_pos), n_rows, q_heads, eps,
+        1 if write_kv else 0, _ptr(rope_table), table_positions, _stream()), "qk_norm_rope_kv_write")
 
 
 def attention_rows(q: torch.Tensor, out: torch.Tensor, cache: PagedCacheArg, row_slot: torch.Tensor,
@@ -182,8 +209,8 @@ def attention_rows(q: torch.Tensor, out: torch.Tensor, cache: PagedCacheArg, row
     width = q_heads * cache.head_dim
     if q.shape[-1] != width or out.shape[-1] != width or q.numel() < n_rows * width or out.numel() < n_rows * width:
         raise KernelError("attention: q or output do not match the head counts and rows")
-    _check(lib, lib.x0ne_attention_rows(_ptr(q), _ptr(out), c_int(dtype_tag(q.dtype)), cache, _ptr(row_slot),
-                                        _ptr(row_pos), c_int(n_rows), c_int(q_heads), c_float(scale), c_int(window),
+    _check(lib, lib.x0ne_attention_rows(_ptr(q), _ptr(out), dtype_tag(q.dtype), cache, _ptr(row_slot),
+                                        _ptr(row_pos), n_rows, q_heads, scale, window,
                                         _stream()), "attention_rows")
 
 
@@ -194,7 +221,7 @@ def swiglu(gate_up: torch.Tensor, out: torch.Tensor, n_rows: int) -> None:
     inter = out.shape[-1]
     if gate_up.shape[-1] != 2 * inter or gate_up.numel() < n_rows * 2 * inter or out.numel() < n_rows * inter:
         raise KernelError("swiglu: widths or rows do not match")
-    _check(lib, lib.x0ne_swiglu(_ptr(gate_up), _ptr(out), c_int(dtype_tag(out.dtype)), c_int(n_rows), c_int(inter),
+    _check(lib, lib.x0ne_swiglu(_ptr(gate_up), _ptr(out), dtype_tag(out.dtype), n_rows, inter,
                                 _stream()), "swiglu")
 
 
@@ -207,8 +234,8 @@ def gemm_f32_nt(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, m: int) -> No
     n, k = w.shape
     if a.shape[-1] != k or c.shape[-1] != n or a.numel() < m * k or c.numel() < m * n:
         raise KernelError(f"gemm_f32: shapes a {tuple(a.shape)} w {tuple(w.shape)} c {tuple(c.shape)} m {m}")
-    _check(lib, lib.x0ne_gemm_f32_nt(_ptr(a), _ptr(w), _ptr(c), c_int(m), c_int(n), c_int(k), c_int(k), c_int(k),
-                                     c_int(n), _stream()), "gemm_f32_nt")
+    _check(lib, lib.x0ne_gemm_f32_nt(_ptr(a), _ptr(w), _ptr(c), m, n, k, k, k,
+                                     n, _stream()), "gemm_f32_nt")
 
 
 def sample(logits: torch.Tensor, n_rows: int, out_token: torch.Tensor, *, temperature=None, top_p=None, seed=None,
@@ -234,7 +261,7 @@ def sample(logits: torch.Tensor, n_rows: int, out_token: torch.Tensor, *, temper
     io = SampleIOArg(_ptr(logits), _ptr(temperature), _ptr(top_p), _ptr(seed), _ptr(draw_counter),
                      _ptr(stop_ids if n_stop else None), _ptr(finished), _ptr(budget), _ptr(out_token),
                      _ptr(next_token), _ptr(next_pos), logits.stride(0), logits.shape[1], n_stop)
-    _check(lib, lib.x0ne_sample(io, c_int(n_rows), _stream()), "sample")
+    _check(lib, lib.x0ne_sample(io, n_rows, _stream()), "sample")
 
 
 # ---------------------------------------------------------------------------------------------
@@ -265,9 +292,9 @@ def attention_prefill_bf16(q: torch.Tensor, out: torch.Tensor, cache: PagedCache
     for first in range(0, n_tiles, 65535):
         n = min(65535, n_tiles - first)
         _check(lib, lib.x0ne_attention_prefill_bf16(
-            _ptr(q), _ptr(out), cache, c_void_p(tile_seq.data_ptr() + 4 * first),
-            c_void_p(tile_row0.data_ptr() + 4 * first), c_int(n), _ptr(seq_first_row), _ptr(seq_slot), _ptr(seq_pos0),
-            c_int(q_heads), c_float(scale), c_int(window), _stream()), "attention_prefill_bf16")
+            _ptr(q), _ptr(out), cache, tile_seq.data_ptr() + 4 * first,
+            tile_row0.data_ptr() + 4 * first, n, _ptr(seq_first_row), _ptr(seq_slot), _ptr(seq_pos0),
+            q_heads, scale, window, _stream()), "attention_prefill_bf16")
 
 
 def attention_prefill_tile_rows() -> int:
@@ -321,8 +348,8 @@ def attention_decode_bf16(q: torch.Tensor, out: torch.Tensor, cache: PagedCacheA
         _need(scratch, torch.uint8, "decode scratch")
         nbytes = scratch.numel()
     _check(lib, lib.x0ne_attention_decode_bf16(
-        _ptr(q), _ptr(out), cache, _ptr(row_slot), _ptr(row_pos), c_int(n_rows), c_int(q_heads), c_float(scale),
-        c_int(window), c_int(splits), _ptr(scratch), c_int64(nbytes), _stream()), "attention_decode_bf16")
+        _ptr(q), _ptr(out), cache, _ptr(row_slot), _ptr(row_pos), n_rows, q_heads, scale,
+        window, splits, _ptr(scratch), nbytes, _stream()), "attention_decode_bf16")
 
 
 # ---------------------------------------------------------------------------------------------
@@ -363,8 +390,8 @@ def gemm_bf16_smallm(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, m: int, 
         kind = 2 if swiglu else 0
     else:
         raise KernelError(f"gemm_smallm: no output kind for {y.dtype} (swiglu={swiglu})")
-    _check(lib, lib.x0ne_gemm_bf16_smallm(_ptr(w), _ptr(x), _ptr(y), c_int(m), c_int(n), c_int(k), c_int(n),
-                                          c_int(kind), c_int(_sms(w.device)), _stream()), "gemm_bf16_smallm")
+    _check(lib, lib.x0ne_gemm_bf16_smallm(_ptr(w), _ptr(x), _ptr(y), m, n, k, n,
+                                          kind, _sms(w.device), _stream()), "gemm_bf16_smallm")
 
 
 # ---------------------------------------------------------------------------------------------
@@ -425,8 +452,8 @@ def gemm_bf16_tcgen05(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, m: int,
         raise KernelError(f"gemm_tc: no output kind for {y.dtype} (swiglu={swiglu})")
     global tc_used
     tc_used = True
-    _check(lib, lib.x0ne_gemm_bf16_tcgen05(_ptr(w), _ptr(x), _ptr(y), c_int(m), c_int(n), c_int(k), c_int(n),
-                                           c_int(kind), c_int(1 if pair else 0), _ptr(gemm_tc_status(w.device)),
+    _check(lib, lib.x0ne_gemm_bf16_tcgen05(_ptr(w), _ptr(x), _ptr(y), m, n, k, n,
+                                           kind, 1 if pair else 0, _ptr(gemm_tc_status(w.device)),
                                            _stream()), "gemm_bf16_tcgen05")
 
 
@@ -470,7 +497,7 @@ def gemm_bf16_skinny_tcgen05(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, 
         raise KernelError(f"gemm_skinny_tc: no output kind for {y.dtype} (swiglu={swiglu})")
     tc_used = True
     x_rows = x.numel() // k      # rows really behind x: the copies may read them all (their results are not used)
-    _check(lib, lib.x0ne_gemm_bf16_skinny_tcgen05(_ptr(w), _ptr(x), c_int(x_rows), _ptr(y), c_int(m), c_int(n), c_int(k), c_int(n), c_int(kind),
+    _check(lib, lib.x0ne_gemm_bf16_skinny_tcgen05(_ptr(w), _ptr(x), x_rows, _ptr(y), m, n, k, n, kind,
                                                   _ptr(gemm_tc_status(x.device)), _stream()), "gemm_bf16_skinny_tcgen05")
 
 
@@ -500,7 +527,7 @@ def attention_prefill_tcgen05(q: torch.Tensor, out: torch.Tensor, cache: PagedCa
     for first in range(0, n_tiles, 65535):
         n = min(65535, n_tiles - first)
         _check(lib, lib.x0ne_attention_prefill_tcgen05(
-            _ptr(q), _ptr(out), c_int(q.shape[0]), cache, c_void_p(tile_seq.data_ptr() + 4 * first),
-            c_void_p(tile_row0.data_ptr() + 4 * first), c_int(n), _ptr(seq_first_row), _ptr(seq_slot), _ptr(seq_pos0),
-            c_int(q_heads), c_float(scale), c_int(window), _ptr(gemm_tc_status(q.device)), _stream()),
+            _ptr(q), _ptr(out), q.shape[0], cache, tile_seq.data_ptr() + 4 * first,
+            tile_row0.data_ptr() + 4 * first, n, _ptr(seq_first_row), _ptr(seq_slot), _ptr(seq_pos0),
+            q_heads, scale, window, _ptr(gemm_tc_status(q.device)), _stream()),
             "attention_prefill_tcgen05")
