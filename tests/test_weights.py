@@ -155,3 +155,20 @@ def test_helper_folders_differ_in_every_size():
     a, b = P.read_config(model_folder("A")), P.read_config(model_folder("B"))
     assert all(a[k] != b[k] for k in a if k != "kv_heads")
     assert a["q_heads"] // a["kv_heads"] != b["q_heads"] // b["kv_heads"]
+
+
+def test_a_file_written_tensor_by_tensor_reads_back_and_refuses_what_was_not_planned(tmp_path):
+    """The streaming writer fixes the header from a plan and takes the tensors one at a time."""
+    import torch
+    from x0ne_engine_b200.weights import write_file_streaming
+    a = torch.arange(12, dtype=torch.float32).reshape(3, 4)
+    b = (torch.arange(10, dtype=torch.float32) / 3).bfloat16().reshape(2, 5)
+    path = str(tmp_path / "model.safetensors")
+    write_file_streaming(path, [("a", torch.float32, (3, 4)), ("b", torch.bfloat16, (2, 5))], iter([a, b]))
+    got = P.read_safetensors(path)
+    assert np.array_equal(got["a"], a.numpy()) and np.array_equal(got["b"], b.float().numpy())
+    src = open_folder(str(tmp_path))
+    assert sorted(src.names()) == ["a", "b"]
+    with pytest.raises(SafetensorsError, match="planned"):
+        write_file_streaming(path, [("a", torch.float32, (3, 4))], iter([b]))
+    assert np.array_equal(P.read_safetensors(path)["a"], a.numpy())       # a failed write leaves the old file

@@ -17,12 +17,12 @@ import json
 import math
 import os
 from dataclasses import dataclass
-from typing import Dict, Iterable, Iterator, Tuple
+from typing import Iterable, Iterator, Tuple
 
 import torch
 
 from .loader import TensorNeed
-from .safetensors_io import write_file
+from .safetensors_io import write_file_streaming
 
 _GOLDEN = 0x9E3779B97F4A7C15
 _M1 = 0xBF58476D1CE4E5B9
@@ -106,7 +106,7 @@ def make_tensors(needs: Iterable[TensorNeed], init: RandomInit, dtype: torch.dty
         yield need, make_tensor(need, init, dtype, device)
 
 
-def write_model_folder(folder: str, config, init: RandomInit = RandomInit(), needs=None) -> None:
+def write_model_folder(folder: str, config, init: RandomInit = RandomInit(), needs=None, device=None) -> None:
     """Writes config.json and model.safetensors of a randomly initialised model.
 
     `config` is an architecture's configuration object (`to_dict`, `to_spec`, `dtype`).  The
@@ -116,9 +116,12 @@ def write_model_folder(folder: str, config, init: RandomInit = RandomInit(), nee
     os.makedirs(folder, exist_ok=True)
     dtype = {"bfloat16": torch.bfloat16, "float32": torch.float32}[config.dtype]
     needs = list(needs if needs is not None else tensor_needs_of_spec(config.to_spec()))
-    tensors: Dict[str, torch.Tensor] = {}
-    for need, t in make_tensors(needs, init, dtype, "cpu"):
-        tensors[need.name] = t
-    write_file(os.path.join(folder, "model.safetensors"), tensors)
+    # The values depend on (seed, name, index) only, so they are made where that is fastest (an
+    # 8B model takes a quarter of an hour on the host and seconds on a GPU) and written one tensor
+    # at a time.
+    device = device if device is not None else ("cuda" if torch.cuda.is_available() else "cpu")
+    plan = [(n.name, dtype, n.shape) for n in needs]
+    write_file_streaming(os.path.join(folder, "model.safetensors"), plan,
+                         (t for _, t in make_tensors(needs, init, dtype, device)))
     with open(os.path.join(folder, "config.json"), "w") as f:
         json.dump(config.to_dict(), f, indent=1)

@@ -189,6 +189,35 @@ def open_folder(folder: str) -> TensorSource:
     return TensorSource(metas, offsets)
 
 
+def write_file_streaming(path: str, plan, tensors) -> None:
+    """Writes one safetensors file without holding it in memory: `plan` lists (name, dtype, shape)
+    in file order, which fixes the header; `tensors` then yields the tensors in that order (from
+    any device), and each is written and dropped."""
+    header, at = {}, 0
+    plan = list(plan)
+    for name, dtype, shape in plan:
+        if dtype not in _NAMES:
+            raise SafetensorsError(f"tensor {name!r}: dtype {dtype} cannot be written")
+        n = 1
+        for d in shape:
+            n *= int(d)
+        nbytes = n * torch.empty((), dtype=dtype).element_size()
+        header[name] = {"dtype": _NAMES[dtype], "shape": [int(d) for d in shape], "data_offsets": [at, at + nbytes]}
+        at += nbytes
+    raw = json.dumps(header, separators=(",", ":")).encode()
+    raw += b" " * (-len(raw) % 8)
+    tmp = path + ".tmp"
+    with open(tmp, "wb") as f:
+        f.write(struct.pack("<Q", len(raw)))
+        f.write(raw)
+        for (name, dtype, shape), t in zip(plan, tensors):
+            t = t.detach().to("cpu").contiguous()
+            if t.dtype != dtype or tuple(t.shape) != tuple(int(d) for d in shape):
+                raise SafetensorsError(f"tensor {name!r}: got {t.dtype} {tuple(t.shape)}, planned {dtype} {tuple(shape)}")
+            f.write(memoryview(t.reshape(-1).view(torch.uint8).numpy()))
+    os.replace(tmp, path)
+
+
 def write_file(path: str, tensors: Mapping[str, torch.Tensor]) -> None:
     """Writes tensors (moved to the CPU) as one safetensors file, names in the given order."""
     header = {}
