@@ -479,3 +479,58 @@ def test_long_prompt_at_the_large_shape_bfloat16_against_the_32_bit_path():
         del eng, held
         torch.cuda.empty_cache()
     assert_close_bf16(got["bfloat16"], got["float32"], "1,500 tokens at the large shape")
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_short_prompt_passes_replayed_from_graphs_give_the_same_bits(name):
+    """Short bfloat16 prompt passes are launched with a padded row count and, from the second pass
+    of a kind on, replayed from a CUDA graph.  Against an engine that launches every pass itself:
+    the same bits for the prompts' logits and for a decoded token after them (so the cache holds
+    the same values), for lengths that share a graph, batches, and further pieces of a prompt."""
+    eng, _ = engine(name, "bfloat16")
+    base, _ = engine(name, "bfloat16", pass_graphs=False)
+    assert eng.pass_graphs and not base.pass_graphs
+    rounds = [[100], [120], [70], [126], [20], [30], [17], [5], [5], [6], [100, 20], [90, 30], [33, 3, 40], [35, 2, 39],
+              [100], [65]]
+    before = eng.pass_graph_replays
+    for k, lengths in enumerate(rounds):
+        prompts = prompts_for(eng.vocab_size, lengths, seed=100 + k)
+        got = []
+        for e in (eng, base):
+            slots = [e.new_sequence() for _ in lengths]
+            try:
+                first = e.step(slots, prompts).cpu().numpy()
+                nxt = e.step(slots, [[int(np.argmax(r))] for r in first]).cpu().numpy()
+            finally:
+                for s in slots:
+                    e.free_sequence(s)
+            got.append((first, nxt))
+        assert np.array_equal(got[0][0], got[1][0]), f"prompts of {lengths}: {first_difference(got[0][0], got[1][0])}"
+        assert np.array_equal(got[0][1], got[1][1]), f"token after {lengths}: {first_difference(got[0][1], got[1][1])}"
+    assert eng.pass_graph_replays - before >= 6 and base.pass_graph_replays == 0
+    # further pieces of a prompt: two sequences whose second pieces share a graph
+    outs = []
+    for e in (eng, base):
+        res = []
+        for a, b, seed in ((40, 30, 7), (45, 28, 8), (41, 29, 9)):
+            ids = prompts_for(e.vocab_size, [a + b], seed=seed)[0]
+            s = e.new_sequence()
+            try:
+                e.step([s], [ids[:a]], [[]])
+                res.append(e.step([s], [ids[a:]]).cpu().numpy())
+            finally:
+                e.free_sequence(s)
+        outs.append(res)
+    for x, y in zip(*outs):
+        assert np.array_equal(x, y)
+    # and against the plain implementation, through a replayed graph
+    folder = engine(name, "bfloat16")[1]
+    ids = prompts_for(eng.vocab_size, [100], seed=3)[0]
+    n0 = eng.pass_graph_replays
+    s = eng.new_sequence()
+    try:
+        got = eng.step([s], [ids]).cpu().numpy()
+    finally:
+        eng.free_sequence(s)
+    assert eng.pass_graph_replays == n0 + 1
+    check("bfloat16", got, plain_logits(folder, ids, bf16_matrices=True)[-1:], "a replayed prompt pass")

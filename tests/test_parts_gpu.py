@@ -201,6 +201,28 @@ def test_a_toy_mixer_with_state_of_its_own_is_registered_built_and_stepped():
         rows += [eng.step([s], [[t]]).cpu().numpy()[0] for t in ids[4:]]
         eng.free_sequence(s)
         assert np.abs(np.stack(rows) - want[3:]).max() / np.abs(want).max() < 1e-4
+        # The toy reads its rows' slots back on the host, so it does not promise to be replayable:
+        # the engine then pads no pass and captures no graph, and the generation loop (asked for
+        # graphs, as by default) launches every step itself.  Greedy tokens in bfloat16 follow the
+        # plain recurrence where its two best logits are clearly apart.
+        from x0ne_engine_b200 import Model
+        assert not DecayMixer.replayable and not eng.replayable
+        from x0ne_engine_b200.weights.loader import held_dtype
+        held = {n.name: cpu[n.name].to(DEV).to(held_dtype(n, torch.float32, torch.bfloat16)) for n in needs}
+        eng16 = Engine(spec, held, "bfloat16", DEV, max_tokens=256)
+        model = Model(eng16, max_batch=2)
+        prompts = [ids[:7], [ids[i] for i in (4, 1, 0, 8, 2, 6, 3, 5, 7, 9, 1, 2)]]    # 7 and 12 rows
+        out = model.generate(prompts, max_tokens=6)
+        assert eng16.pass_graph_replays == 0 and model._generator._runner.graph_replays == 0
+        assert model._generator._runner.eager_steps > 0
+        for prompt, toks in zip(prompts, out.tokens):
+            seq = list(prompt)
+            for t in toks:
+                row = plain(seq)[-1]
+                best = np.sort(row)[::-1]
+                if best[0] - best[1] > 0.05 * np.abs(row).max():
+                    assert t == int(np.argmax(row))
+                seq.append(t)
     finally:
         MIXERS.unregister("toy_decay")
 

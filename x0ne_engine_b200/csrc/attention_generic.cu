@@ -78,7 +78,7 @@ __global__ void attention_rows_kernel(const T* __restrict__ q, T* __restrict__ o
         m = m_new;
     }
     T* o = out + ((int64_t)row * q_heads + head) * hd;
-    const float inv = 1.0f / l;
+    const float inv = l > 0.f ? 1.0f / l : 0.f;      // a row with no readable key (a padding row) gets zeros
 #pragma unroll
     for (int i = 0; i < ATT_MAX_I; ++i) {
         const int d = lane + 32 * i;

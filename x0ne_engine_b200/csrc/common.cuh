@@ -150,8 +150,10 @@ struct PagedCache {
     int32_t n_pages;            // pages in the pool, for the bounds check
 };
 
-// Element offset of (slot, pos, kv head, which = 0 for K / 1 for V); -1 if there is no page.
+// Element offset of (slot, pos, kv head, which = 0 for K / 1 for V); -1 if there is no page, or if
+// the slot is negative (a padding row that belongs to no sequence).
 __device__ __forceinline__ int64_t cache_row_offset(const PagedCache& c, int slot, int pos, int kv_head, int which) {
+    if (slot < 0 || pos < 0) return -1;
     const int lp = (pos / c.page_size) % c.ring_pages;
     const int page = c.page_table[(int64_t)slot * c.table_stride + lp];
     if (page < 0 || page >= c.n_pages) return -1;

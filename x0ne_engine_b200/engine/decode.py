@@ -33,7 +33,7 @@ class DeviceBatch:
     def __init__(self, engine: Engine, max_batch: int, cuda_graph: bool = True):
         self.engine = engine
         self.max_batch = max_batch
-        self.cuda_graph = cuda_graph
+        self.cuda_graph = cuda_graph and engine.replayable      # a part that may not be replayed: every step is launched
         dev = engine.device
         i32 = dict(dtype=torch.int32, device=dev)
         self.tokens = torch.zeros(max_batch, **i32)

@@ -13,6 +13,7 @@ sequences of unequal length share a pass and padding never exists.
 """
 from __future__ import annotations
 
+from collections import OrderedDict
 from dataclasses import dataclass
 from typing import Dict, List, Optional, Sequence, Tuple
 
@@ -31,6 +32,23 @@ DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.f
           torch.bfloat16: torch.bfloat16, torch.float32: torch.float32}
 
 
+# Prompt passes of at most this many rows are launch-bound on the host (about 300 launches
+# against a few milliseconds of device work), so their launches are kept as CUDA graphs.
+PASS_GRAPH_MAX_ROWS = 1024
+PASS_GRAPH_MAX_WANT = 16
+PASS_GRAPHS_KEPT = 24
+
+
+def padded_rows(n: int) -> int:
+    """The row count a short bfloat16 prompt pass is launched with: itself up to 8, then the next
+    multiple of 16 up to 64, then the next multiple of 64.  Passes that agree in it (and in their
+    attention tiles and wanted rows) launch the same kernels on the same grids."""
+    if n <= 8:
+        return n
+    step = 16 if n <= 64 else 64
+    return -(-n // step) * step
+
+
 class StepError(ValueError):
     """A step the engine refuses before any launch: bad ids, bad slots, no room."""
 
@@ -47,7 +65,7 @@ class StepContext:
     cache: SequenceCache
     decode: bool                # every sequence brings exactly one token
     n_seqs: int = 0
-    max_seq_rows: int = 0       # most rows one sequence brings to this pass
+    max_seq_rows: int = 0       # upper bound on the rows one sequence brings to this pass
     max_context: int = 0        # upper bound on the keys any row reads
     seq_first_row: Optional[torch.Tensor] = None   # int32 [n_seqs + 1]
     seq_slot: Optional[torch.Tensor] = None        # int32 [n_seqs]
@@ -70,7 +88,7 @@ def require_gpu(device) -> torch.device:
 class Engine:
     def __init__(self, spec: ModelSpec, tensors: Dict[str, torch.Tensor], dtype, device="cuda:0",
                  max_tokens: int = 8192, max_seq_len: Optional[int] = None, max_step_tokens: Optional[int] = None,
-                 max_slots: Optional[int] = None):
+                 max_slots: Optional[int] = None, pass_graphs: bool = True):
         self.device = require_gpu(device)
         self.dtype = DTYPES[dtype]
         self.spec = spec
@@ -92,6 +110,14 @@ class Engine:
         self._stage_at = 0
         self._seq_dev = torch.zeros((3, self.max_step_tokens + 1), dtype=torch.int32, device=self.device)
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
+        # short bfloat16 prompt passes: padded to a few row counts, their launches kept as graphs
+        self.replayable = self.model.replayable()
+        self.pass_graphs = bool(pass_graphs)
+        self._pass_graphs: "OrderedDict[tuple, torch.cuda.CUDAGraph]" = OrderedDict()
+        self._pass_seen: Dict[tuple, int] = {}
+        self._pass_logits: Optional[torch.Tensor] = None
+        self._capture_stream: Optional[torch.cuda.Stream] = None
+        self.pass_graph_replays = 0
         if self.dtype == torch.bfloat16:
             from ..csrc import ops
             self._tile_rows = ops.attention_prefill_tile_rows()
@@ -215,10 +241,18 @@ class Engine:
     def _run_pass(self, toks, rslot, rpos, want_rows, want_dest, logits, decode, slots, starts, lens, first_row,
                   r0, r1) -> None:
         n = len(toks)
+        # A short bfloat16 prompt pass is launched with a padded row count; the rows past n carry
+        # slot -1, belong to no sequence and no tile, write no cache and are wanted by nobody.
+        short = self.replayable and self.dtype == torch.bfloat16 and not decode and n <= PASS_GRAPH_MAX_ROWS
+        rows = padded_rows(n) if short and padded_rows(n) <= self.ws.max_rows else n
         stage, si = self._stage_buffer()
         stage[0, :n] = torch.from_numpy(toks.astype(np.int32))
         stage[1, :n] = torch.from_numpy(rslot)
         stage[2, :n] = torch.from_numpy(rpos)
+        if rows > n:
+            stage[0, n:rows] = 0
+            stage[1, n:rows] = -1
+            stage[2, n:rows] = 0
         nw = len(want_rows)
         if nw:
             stage[3, :nw] = torch.from_numpy(want_rows.astype(np.int32))
@@ -245,20 +279,89 @@ class Engine:
         seq_host[1, :ns] = sslot
         seq_host[2, :ns] = spos0
         self._seq_dev[:, :ns + 1].copy_(torch.from_numpy(seq_host))
+        max_seq_rows, max_context = int(counts.max()), int(rpos.max()) + 1
+        if short:
+            # the host-side numbers a part may size its launches by are rounded up, so that passes
+            # with the same key below make the same launches
+            max_seq_rows = padded_rows(max_seq_rows)
+            max_context = -(-max_context // PAGE_SIZE) * PAGE_SIZE
         ctx = StepContext(
-            n_rows=n, tokens=self._meta_dev[0], row_slot=self._meta_dev[1], row_pos=self._meta_dev[2],
+            n_rows=rows, tokens=self._meta_dev[0], row_slot=self._meta_dev[1], row_pos=self._meta_dev[2],
             dtype=self.dtype, ws=self.ws, cache=self.cache, decode=decode, n_seqs=ns,
-            max_seq_rows=int(np.max(np.diff(sfirst))), max_context=int(rpos.max()) + 1,
+            max_seq_rows=max_seq_rows, max_context=max_context,
             seq_first_row=self._seq_dev[0], seq_slot=self._seq_dev[1], seq_pos0=self._seq_dev[2],
             n_tiles=n_tiles, tile_seq=self._meta_dev[4], tile_row0=self._meta_dev[5], sm_count=self.sm_count)
-        if nw == 0:
+        in_order = nw == logits.shape[0] and np.array_equal(want_dest, np.arange(nw))
+        if short and self.pass_graphs and nw <= PASS_GRAPH_MAX_WANT and (nw == 0 or in_order):
+            self._run_short_pass(ctx, (rows, n_tiles, ns, nw, max_seq_rows, max_context), nw, logits)
+        elif nw == 0:
             self.model.forward(ctx, None, 0, None)
-        elif nw == logits.shape[0] and np.array_equal(want_dest, np.arange(nw)):
+        elif in_order:
             self.model.forward(ctx, self._meta_dev[3], nw, logits)
         else:
             out = torch.empty((nw, self.vocab_size), dtype=torch.float32, device=self.device)
             self.model.forward(ctx, self._meta_dev[3], nw, out)
             logits[torch.from_numpy(want_dest).to(self.device)] = out
+
+    def _run_short_pass(self, ctx: StepContext, key: tuple, nw: int, logits: torch.Tensor) -> None:
+        """Launches a short prompt pass, from a CUDA graph once its key has been seen before.
+
+        Everything that differs between two passes with the same key (tokens, slots, positions,
+        tiles, the sequences' first rows, the page table) is in device arrays at fixed addresses
+        that the launches read, so the launches themselves are the same and can be replayed.  The
+        first pass of a key runs eagerly (it also lets libraries and the workspace finish their lazy
+        set-up), the second is captured and replayed, later ones are replayed.  The launches and
+        their inputs are the same either way, so the results are the same bits.
+        """
+        from ..csrc import ops
+        out = None
+        if nw:
+            if self._pass_logits is None:
+                self._pass_logits = torch.empty((PASS_GRAPH_MAX_WANT, self.vocab_size), dtype=torch.float32,
+                                                device=self.device)
+            out = self._pass_logits[:nw]
+        want = self._meta_dev[3] if nw else None
+        entry = self._pass_graphs.get(key)
+        if entry is None:
+            seen = self._pass_seen.get(key, 0) + 1
+            self._pass_seen[key] = seen
+            if seen >= 2:
+                entry = self._capture_pass(key, ctx, want, nw, out)
+        if entry is None:
+            self.model.forward(ctx, want, nw, out)
+        else:
+            graph, uses_tc = entry
+            self._pass_graphs.move_to_end(key)
+            graph.replay()
+            self.pass_graph_replays += 1
+            ops.tc_used = ops.tc_used or uses_tc          # so that the step still reads the status word
+        if nw:
+            logits.copy_(out)
+
+    def _capture_pass(self, key: tuple, ctx: StepContext, want, nw: int, out):
+        from ..csrc import ops
+        if self._capture_stream is None:
+            self._capture_stream = torch.cuda.Stream(self.device)
+            self._graph_pool = torch.cuda.graph_pool_handle()
+        cur, side = torch.cuda.current_stream(self.device), self._capture_stream
+        graph = torch.cuda.CUDAGraph()
+        was_used, ops.tc_used = ops.tc_used, False
+        side.wait_stream(cur)
+        with torch.cuda.stream(side):
+            graph.capture_begin(pool=self._graph_pool, capture_error_mode="thread_local")
+            try:
+                self.model.forward(ctx, want, nw, out)
+            finally:
+                graph.capture_end()
+        cur.wait_stream(side)
+        entry = (graph, ops.tc_used)
+        ops.tc_used = was_used
+        self._pass_graphs[key] = entry
+        while len(self._pass_graphs) > PASS_GRAPHS_KEPT:
+            self._pass_graphs.popitem(last=False)
+        if len(self._pass_seen) > 4096:
+            self._pass_seen.clear()
+        return entry
 
     # ------------------------------------------------------------------ facts for reports
     def describe(self) -> str:

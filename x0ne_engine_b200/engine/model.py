@@ -73,6 +73,11 @@ class CausalLM:
             out += b.parts()
         return out + [self.final_norm, self.head]
 
+    def replayable(self) -> bool:
+        """Whether every part and block promises that its launches can be replayed from a CUDA graph
+        and that it takes padding rows (see `parts.Part.replayable`)."""
+        return all(p.replayable for p in self.parts()) and all(b.replayable for b in self.blocks)
+
     def cache_needs(self) -> List[P.CacheNeed]:
         """One CacheNeed per run-order entry."""
         return [P.MIXERS.get(self.spec.layers[e.layer].mixer.kind).cache_need(self.spec.layers[e.layer].mixer)

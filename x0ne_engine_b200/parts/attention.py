@@ -71,6 +71,7 @@ class GQAttention(Mixer):
     (None: all keys), position (name of a position encoding of the model, or None), scale (None:
     1/sqrt(head_dim)), names.{q, k, v, o, q_norm, k_norm}.
     """
+    replayable = True
 
     def __init__(self, spec, env):
         super().__init__(spec, env)

@@ -18,7 +18,8 @@ sees the model's name or its config.json.  The kinds:
                      residual: `forward(ctx, entry, resid, delta)` returns the pending delta.
 
 To add a part: subclass the kind, implement `tensor_needs(spec)` (static: the checkpoint
-tensors, by name, with shapes) and `bind(tensors)`, and call the kind's `register`.
+tensors, by name, with shapes) and `bind(tensors)`, and call the kind's `register`.  A part that
+may be replayed from a CUDA graph says so with `replayable = True` (see `Part`).
 """
 from __future__ import annotations
 
@@ -55,6 +56,15 @@ class BuildEnv:
 
 
 class Part:
+    # True promises three things of every call the engine makes during a pass: it only queues work
+    # on the current stream (nothing is read back, no tensor made in it is used after it returns);
+    # its launches depend on the host only through the numbers of the StepContext (n_rows, n_seqs,
+    # n_tiles, max_seq_rows, max_context, decode); and rows whose slot is -1 are rows of no
+    # sequence (they read and write nothing that is kept per sequence).  If every part of a model
+    # promises this, the engine pads short passes with such rows and replays the launches of
+    # decode steps and of short prompt passes from CUDA graphs; else it launches every pass itself.
+    replayable = False
+
     def __init__(self, spec: PartSpec, env: BuildEnv):
         self.spec = spec
         self.env = env
@@ -101,6 +111,7 @@ class PositionEncoding(Part):
 
 class Block:
     """Arrangement of one layer's parts; built by the engine from a LayerSpec."""
+    replayable = False      # as for Part
 
     def __init__(self, mixer_norm: Norm, mixer: Mixer, ffn_norm: Norm, ffn: FeedForward):
         self.mixer_norm, self.mixer, self.ffn_norm, self.ffn = mixer_norm, mixer, ffn_norm, ffn

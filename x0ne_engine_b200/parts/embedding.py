@@ -16,6 +16,7 @@ class TokenEmbedding(Part):
     """resid[r] = float32(table[token[r]]); an id outside the table gives a zero row
     (x0ne-core/kernels/cuda/embedding.cu:5-17).  Parameters: vocab_size, hidden_size,
     names.weight."""
+    replayable = True
 
     def __init__(self, spec, env):
         super().__init__(spec, env)
@@ -37,6 +38,7 @@ class LMHead(Part):
     """logits = normed W^T in float32 for the wanted rows only; W is the embedding table when the
     model is tied (x0ne-core/runtime/src/engine.rs:823-835).  Parameters: vocab_size,
     hidden_size, tied, names.weight."""
+    replayable = True
 
     def __init__(self, spec, env):
         super().__init__(spec, env)

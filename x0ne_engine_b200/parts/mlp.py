@@ -17,6 +17,7 @@ class SwiGLU(FeedForward):
     up rows: x0ne-core/runtime/src/weights.rs:218-219), the activation
     g / (1 + expf(-g)) * u (x0ne-core/kernels/cuda/swiglu.cu:5-11), one product with down.
     Parameters: hidden_size, intermediate_size, names.{gate, up, down}."""
+    replayable = True
 
     def __init__(self, spec, env):
         super().__init__(spec, env)

@@ -15,6 +15,7 @@ class RMSNorm(Norm):
     """out = r * rsqrt(mean(r^2) + eps) * w with r = resid + delta, in float32; eps inside the
     root, the weight multiplies directly (x0ne-core/kernels/cuda/rmsnorm.cu:11-20).
     Parameters: size, eps, names.weight."""
+    replayable = True
 
     def __init__(self, spec, env):
         super().__init__(spec, env)

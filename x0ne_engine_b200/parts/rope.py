@@ -21,6 +21,7 @@ class Rope(PositionEncoding):
     (i, i + rotary_dim/2) turns by pos * inv_freq[i] (x0ne-core/kernels/cuda/rope.cu:28-31).
     The rotation itself runs inside the mixer's fused kernel; this part owns the table.
     Parameters: head_dim, rotary_dim, theta."""
+    replayable = True
 
     def __init__(self, spec, env):
         super().__init__(spec, env)
@@ -50,6 +51,7 @@ class Rope(PositionEncoding):
 
 class NoPosition(PositionEncoding):
     """No position encoding: mixers leave q and k unrotated."""
+    replayable = True
 
 
 POSITIONS.register("rope", Rope)
