@@ -10,7 +10,7 @@ up to 2,048 generated tokens: mean 3,072), so the prompt fed before them has 3,0
 with K = 2,047 that is the benchmark's own run.  `value` is decoded tokens a second (batch * K /
 time); `e2e` is the same rate through `Model.generate` with host token lists in and out;
 `prefill` is one 2,048-token prompt through the step function; `points` has decode at batch 1
-and 64; `roofline` places the decode step against the bytes it must read.  One JSON line is
+and 64 and the milliseconds a 128-token prompt takes through the step function; `roofline` places the decode step against the bytes it must read.  One JSON line is
 printed.  This library runs on one GPU: for --gpus above 1 a line says so and the exit code is 2.
 """
 from __future__ import annotations
@@ -220,21 +220,24 @@ def main() -> int:
             runner.close()
 
     # ---- prefill: one prompt of T tokens through the step function, logits at its last place
+    def time_prompt(n_tokens):
+        ids = synthetic_ids(n_tokens, cfg.vocab_size, 20261104)
+        times = []
+        for i in range(W + 3):
+            slot = eng.new_sequence(n_tokens)
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            s.record()
+            eng.step([slot], [ids])
+            e.record()
+            torch.cuda.synchronize()
+            if i >= W:
+                times.append(s.elapsed_time(e))
+            eng.free_sequence(slot)
+        return statistics.median(times)
+
     T = args.prefill_tokens
-    ids = synthetic_ids(T, cfg.vocab_size, 20261104)
-    pre_ms = []
-    for i in range(W + 3):
-        slot = eng.new_sequence(T)
-        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        torch.cuda.synchronize()
-        s.record()
-        eng.step([slot], [ids])
-        e.record()
-        torch.cuda.synchronize()
-        if i >= W:
-            pre_ms.append(s.elapsed_time(e))
-        eng.free_sequence(slot)
-    pre = statistics.median(pre_ms)
+    pre = time_prompt(T)
     flops = (2.0 * T * cfg.linear_params_per_layer * layers + 2.0 * cfg.vocab_size * cfg.hidden_size
              + 4.0 * cfg.num_attention_heads * cfg.head_dim * T * (T + 1) / 2 * layers)
     prefill = {"value": T / (pre / 1e3), "tokens": T, "ms": pre,
@@ -252,6 +255,8 @@ def main() -> int:
             r = decode_run(b, k, W, max(1, mean_ctx - k // 2 - W))
             points[f"decode_b{b}"] = r["tok_s"]
             print(f"[bench] decode b{b}: {r['tok_s']:.0f} tok/s, {r['ms'] / k:.3f} ms/step", file=sys.stderr, flush=True)
+        # a short prompt through the step function (its launches come from a graph after the second pass)
+        points["prompt_t128_ms"] = time_prompt(128)
 
     # ---- end to end through the Python entry point: host token lists in, host token lists out
     e2e = None
