@@ -346,16 +346,18 @@ class Engine:
         cur, side = torch.cuda.current_stream(self.device), self._capture_stream
         graph = torch.cuda.CUDAGraph()
         was_used, ops.tc_used = ops.tc_used, False
-        side.wait_stream(cur)
-        with torch.cuda.stream(side):
-            graph.capture_begin(pool=self._graph_pool, capture_error_mode="thread_local")
-            try:
-                self.model.forward(ctx, want, nw, out)
-            finally:
-                graph.capture_end()
-        cur.wait_stream(side)
-        entry = (graph, ops.tc_used)
-        ops.tc_used = was_used
+        try:
+            side.wait_stream(cur)
+            with torch.cuda.stream(side):
+                graph.capture_begin(pool=self._graph_pool, capture_error_mode="thread_local")
+                try:
+                    self.model.forward(ctx, want, nw, out)
+                finally:
+                    graph.capture_end()
+            cur.wait_stream(side)
+            entry = (graph, ops.tc_used)
+        finally:
+            ops.tc_used = was_used
         self._pass_graphs[key] = entry
         while len(self._pass_graphs) > PASS_GRAPHS_KEPT:
             self._pass_graphs.popitem(last=False)
