@@ -278,6 +278,27 @@ def cmd_kernel_bench(a) -> int:
         copies = 1
         timed(lambda: ops.add_rmsnorm(resid, delta, w, out, rows, 1e-6), rows * h * (4 + 4 + 2 + 2))
         return 0
+    if a.kernel == "qk_norm_rope":
+        # a.m rows of one sequence at positions 0 .. m-1: q/k head norm, rotation from the table, K/V into the pages
+        hd, kvh, qh, rows = a.head_dim, a.kv_heads, a.q_heads, a.m
+        pages_per = (rows + 63) // 64
+        store = torch.zeros(pages_per, 2, kvh, 64, hd, device=dev, dtype=torch.bfloat16)
+        table = torch.arange(pages_per, dtype=torch.int32, device=dev).reshape(1, pages_per).contiguous()
+        view = ops.PagedCacheArg(store.data_ptr(), table.data_ptr(), 2 * kvh * 64 * hd, pages_per, pages_per, 64, kvh,
+                                 hd, pages_per)
+        qkv = torch.randn(rows, (qh + 2 * kvh) * hd, device=dev).bfloat16()
+        q_out = torch.empty(rows, qh * hd, device=dev, dtype=torch.bfloat16)
+        ones = torch.ones(hd, device=dev)
+        inv_freq = (1e6 ** (-torch.arange(0, hd, 2, device=dev, dtype=torch.float32) / hd)).contiguous()
+        ang = torch.arange(rows, device=dev, dtype=torch.float32)[:, None] * inv_freq[None, :]
+        rope_table = torch.cat([ang.cos(), ang.sin()], dim=1).contiguous()
+        slot = torch.zeros(rows, dtype=torch.int32, device=dev)
+        pos = torch.arange(rows, dtype=torch.int32, device=dev)
+        copies = 1
+        moved = rows * ((qh + 2 * kvh) * hd * 2 + qh * hd * 2 + 2 * kvh * hd * 2)
+        timed(lambda: ops.qk_norm_rope_kv_write(qkv, ones, ones, inv_freq, hd, q_out, view, slot, pos, rows, qh, 1e-6,
+                                                True, rope_table), moved)
+        return 0
     print(f"unknown kernel {a.kernel!r}", file=sys.stderr)
     return 2
 
