@@ -275,7 +275,7 @@ def main() -> int:
 
     achieved = main_run["bytes_per_step"] / (main_run["ms"] / K / 1e3) / 1e9
     out = {
-        "metric": "decode tok/s at batch 8 (Qwen3-8B shape, random bf16 weights), 4,096-token context",
+        "metric": f"decode tok/s at batch {B} (Qwen3-8B shape, random bf16 weights), {ctx:,}-token context",
         "value": main_run["tok_s"], "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W,
         "ms_per_step": main_run["ms"] / K, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "ours",
