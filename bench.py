@@ -261,17 +261,38 @@ def main() -> int:
     # ---- end to end through the Python entry point: host token lists in, host token lists out
     e2e = None
     if not args.no_e2e:
+        from x0ne_engine_b200.engine.generate import GenerationStats, percentiles
         prompts = [synthetic_ids(prompt_len, cfg.vocab_size, 0x0C0E5EED + i) for i in range(B)]
         n_new = K + W + 1
-        model.generate(prompts, max_tokens=4, stop_token_ids=())            # warm the batch's graph
-        st = model._generator.stats
-        d0, t0s = st.decode_tokens, st.decode_seconds
-        model.generate(prompts, max_tokens=n_new, stop_token_ids=())
-        dt, dn = st.decode_seconds - t0s, st.decode_tokens - d0
-        e2e = {"value": dn / dt, "unit": "tokens/s",
-               "h2d_bytes_per_step": round(B * prompt_len * 4 / n_new + 0.0, 1), "d2h_bytes_per_step": 4 * B,
-               "note": "decode rate inside Model.generate: (tokens after the first) / (time after the first); prompt "
-                       "ids go up once per batch, each step reads back one int32 per live sequence"}
+
+        def through_generate(n_tokens):
+            model._generator.stats = st = GenerationStats()
+            out = model.generate(prompts, max_tokens=n_tokens, stop_token_ids=())
+            return out.tokens, st
+
+        through_generate(4)                                                   # warms the batch's graph
+        first, _ = through_generate(n_new)
+        tokens, st = through_generate(n_new)
+        if tokens != first:
+            # two greedy runs of the same prompts must give the same tokens, or the timing is of
+            # something else than generation (x0ne-core/oracle/examples/core-perf.rs:85-89)
+            print("bench.py: two runs of the same greedy generation gave different tokens; no number is reported",
+                  file=sys.stderr)
+            return 3
+        gaps = st.token_gaps
+        print(f"[bench] e2e: {st.decode_tokens / st.decode_seconds:.0f} tok/s over {len(gaps)} steps; gaps ms: first "
+              f"{[round(g * 1e3, 2) for g in gaps[:4]]} p50 {percentiles(gaps)['p50'] * 1e3:.3f} max {max(gaps) * 1e3:.3f}",
+              file=sys.stderr, flush=True)
+        e2e = {"value": st.decode_tokens / st.decode_seconds, "unit": "tokens/s",
+               "h2d_bytes_per_step": round(B * prompt_len * 4 / n_new + 0.0, 1), "d2h_bytes_per_step": 4 * (B + 1),
+               "steps": len(gaps), "token_gap_ms": {k: (v * 1e3 if k != "n" else v) for k, v in percentiles(gaps).items()},
+               "note": "decode rate inside Model.generate: (tokens after the first) / (time from the first token's "
+                       "arrival to the last one's); prompt ids go up once per batch, each step reads back one int32 "
+                       "per live sequence and one status word"}
+        long_steps = 192
+        if K < long_steps and prompt_len + long_steps + 1 <= ctx:
+            _, st = through_generate(long_steps + 1)
+            e2e["long"] = {"value": st.decode_tokens / st.decode_seconds, "steps": len(st.token_gaps)}
 
     achieved = main_run["bytes_per_step"] / (main_run["ms"] / K / 1e3) / 1e9
     out = {

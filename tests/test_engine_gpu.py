@@ -150,6 +150,71 @@ def test_unequal_batches_one_after_another_reuse_slots(name, lengths, steps, dty
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name,lengths", [("A", [5, 70, 17, 33, 90, 60]), ("B", [1, 130, 30, 64, 7]), ("C", [70, 3, 129, 64, 65])])
+@pytest.mark.parametrize("pass_rows", [64, 65, 100])
+def test_a_step_larger_than_one_pass_cuts_sequences_mid_prompt(name, lengths, pass_rows, dtype):
+    """With `max_step_tokens` below a step's total, the flattened rows are cut into passes at row
+    numbers that fall inside prompts: a sequence's first rows run in one pass, its later rows in the
+    next (from the cache the first left), wanted rows lie in several passes and are asked for out of
+    order and twice.  Three batches in a row on a cache that holds one.  Every logits row must be the
+    request's own alone-and-whole row (same bits in float32) and the plain implementation's; then one
+    token each is decoded and compared the same way."""
+    need = sum((n + 1 + 63) // 64 * 64 for n in lengths)
+    eng, folder = engine(name, dtype, max_tokens=need, max_step_tokens=pass_rows)
+    ref, _ = engine(name, dtype)                       # an engine that runs every step in one pass
+    assert eng.max_step_tokens == pass_rows and sum(lengths) > 2 * pass_rows
+    cfg, _ = plain_model(folder)
+    for batch in range(3):
+        prompts = prompts_for(cfg["vocab"], lengths, seed=40 + batch)
+        nxt = prompts_for(cfg["vocab"], [1] * len(lengths), seed=50 + batch)
+        want = []
+        for i, p in enumerate(prompts):                # last place first, a middle place twice, the first place
+            places = [len(p) - 1, len(p) // 2, 0, len(p) // 2] if len(p) > 2 else [len(p) - 1, 0]
+            want.append(places if (i + batch) % 2 == 0 else sorted(set(places)))
+        slots = [eng.new_sequence() for _ in prompts]
+        got = eng.step(slots, prompts, want).cpu().numpy()
+        after = eng.step(slots, nxt).cpu().numpy()
+        for s in slots:
+            eng.free_sequence(s)
+        assert eng.cache.slots.held() == 0
+        at = 0
+        for i, p in enumerate(prompts):
+            base = whole(ref, p + nxt[i])
+            plain = plain_logits(folder, p + nxt[i], bf16_matrices=dtype == "bfloat16")
+            rows = got[at:at + len(want[i])]
+            at += len(want[i])
+            same_cut(dtype, rows, base[want[i]], f"{name} batch {batch} request {i} prompt rows, passes of {pass_rows}")
+            check(dtype, rows, plain[want[i]], f"{name} batch {batch} request {i} prompt rows vs plain")
+            same_cut(dtype, after[i:i + 1], base[-1:], f"{name} batch {batch} request {i} next token")
+            check(dtype, after[i:i + 1], plain[-1:], f"{name} batch {batch} request {i} next token vs plain")
+        assert at == len(got)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_generation_with_other_stop_tokens_on_the_same_model(dtype):
+    """The decode graphs of a batch size are captured once and serve every later batch: a call with
+    stop tokens, then one without, then one with other stop tokens, on the same model, each against
+    the free run cut at its stops (a graph that kept the first call's stop list would end rows that
+    the host still holds live)."""
+    from x0ne_engine_b200 import Model
+    folder = model_folder("A", "float32" if dtype == "float32" else "bfloat16")
+    prompts = prompts_for(plain_model(folder)[0]["vocab"], [9, 4, 21, 6], seed=28)
+    fresh = Model.from_folder(folder, dtype=dtype, max_batch=4, max_ctx=128)
+    free = fresh.generate(prompts, max_tokens=20, stop_token_ids=()).tokens
+    m = Model.from_folder(folder, dtype=dtype, max_batch=4, max_ctx=128)
+    first_stop, other_stops = free[0][2], (free[1][4], free[2][1], free[3][7])
+
+    def cut(f, stops):
+        ends = [f.index(t) for t in stops if t in f]
+        return f[:min(ends)] if ends else f
+
+    for stops in ((first_stop,), (), other_stops, tuple(range(200, 230)), (first_stop,)):
+        out = m.generate(prompts, max_tokens=20, stop_token_ids=stops)
+        assert out.tokens == [cut(f, stops) for f in free], f"stops {stops}"
+        assert m.engine.cache.slots.held() == 0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 def test_long_decoding(dtype):
     """Hundreds of single-token steps across many pages, two sequences of different age."""
     eng, folder = engine("C", dtype)

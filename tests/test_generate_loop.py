@@ -129,3 +129,55 @@ def test_each_request_gets_its_own_params_and_seed():
     out = g.generate([[1], [2]], params)
     assert [len(c.tokens) for c in out] == [1, 3]
     assert runner.rows[0].seed == 3 and 0 <= runner.rows[1].seed < 1 << 53
+
+
+def test_token_gaps_are_stamped_per_step_and_summarised():
+    """One host timestamp per decode step: the gaps between them (the first from the prompts' picks)
+    are kept, and decode time runs to the last token's arrival."""
+    from x0ne_engine_b200.engine.generate import GenerationStats, percentiles
+    ticks = iter([0.0, 1.0, 1.5, 1.75, 4.0, 9.0])
+    rows = [Row(0, [1], SamplingParams(max_tokens=4), 4, 0), Row(1, [2], SamplingParams(max_tokens=2), 2, 0)]
+    stats = GenerationStats()
+    run_batch(Scripted({0: [5, 6, 7, 8], 1: [5, 6]}), rows, stats, clock=lambda: next(ticks))
+    assert stats.token_gaps == [0.5, 0.25, 2.25] and stats.decode_steps == 3 and stats.decode_tokens == 2 + 1 + 1
+    assert stats.prefill_seconds == 1.0 and stats.decode_seconds == 3.0
+    assert stats.gap_percentiles() == {"p50": 0.5, "p90": 2.25, "p99": 2.25, "max": 2.25, "n": 3}
+    assert percentiles([]) is None
+    assert percentiles(list(range(1, 101)), (50, 90, 99))["p99"] == 99
+
+
+def test_the_device_gets_the_batch_s_common_stop_tokens_padded_to_a_fixed_length():
+    from x0ne_engine_b200.engine.decode import STOP_IDS_ON_DEVICE, device_stop_ids
+    row = lambda stops: Row(0, [1], SamplingParams(stop_token_ids=stops), 4, 0)   # noqa: E731
+    pad = lambda ids: list(ids) + [-1] * (STOP_IDS_ON_DEVICE - len(ids))          # noqa: E731
+    assert device_stop_ids([row((7, 3)), row((3, 7, 7))]) == pad([3, 7])
+    assert device_stop_ids([row(()), row(())]) == pad([])
+    assert device_stop_ids([row((7,)), row((8,))]) == pad([])                     # rows differ: the host decides alone
+    assert device_stop_ids([row(tuple(range(STOP_IDS_ON_DEVICE + 1)))]) == pad([])
+    assert len(device_stop_ids([row(tuple(range(STOP_IDS_ON_DEVICE)))])) == STOP_IDS_ON_DEVICE
+
+
+def test_a_status_word_behind_the_picks_fails_the_step_it_came_with():
+    """The decode loop reads, behind each step's picks, the word in which the tensor-core kernels
+    report a wait that ran out.  With buffers filled by hand: steps whose word is zero give their
+    picks; the step whose word is not zero raises, names itself, and clears the device's word."""
+    import torch
+    from x0ne_engine_b200.csrc.ops import KernelError
+    from x0ne_engine_b200.engine.decode import DeviceBatch
+
+    class Arrived:
+        def synchronize(self):
+            pass
+
+    b = DeviceBatch.__new__(DeviceBatch)
+    b._out_event = [Arrived(), Arrived()]
+    b._out_host = [torch.tensor([11, 12, 13, 0, 99], dtype=torch.int32), torch.tensor([21, 22, 1 << 2, 0, 0], dtype=torch.int32)]
+    b._batch_first = 6
+    b.status = torch.tensor([1 << 2], dtype=torch.int32)
+    assert b._read(6, 3) == [11, 12, 13]                     # the prompts' step of this batch: word 0
+    with pytest.raises(KernelError, match=r"decode step 1 of this batch.*codes \[2\]"):
+        b._read(7, 2)                                        # picks 21, 22 and a word that is not zero
+    assert int(b.status[0]) == 0
+    b._out_host[0][3] = 1 << 5
+    with pytest.raises(KernelError, match=r"the prompts' step of this batch.*codes \[5\]"):
+        b._read(6, 3)

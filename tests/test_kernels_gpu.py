@@ -555,3 +555,79 @@ def test_sampler_rows_do_not_depend_on_batch_mates():
         o.sample(logits[r:r + 1].contiguous(), 1, one, temperature=t[r:r + 1].contiguous(),
                  top_p=p[r:r + 1].contiguous(), seed=seeds[r:r + 1].contiguous())
         assert int(one[0]) == int(out[r])
+
+
+@pytest.mark.parametrize("hd,dtype", [(64, torch.bfloat16), (128, torch.bfloat16), (48, torch.bfloat16), (32, torch.float32)])
+def test_attention_kernels_on_a_ring_that_has_lapped(hd, dtype):
+    """A windowed cache keeps a ring of 3 pages: logical page (pos / 64) % 3.  A sequence is at
+    position 400, so the ring has lapped twice; the places of its newest page past position 400
+    still hold keys of positions 208..255 (made huge here: a read past the causal bound would
+    show), and key 330 scores far above everything: with a window of 70 the rows at 380..399 see
+    it and give its value, the row at 400 must not (it lies just outside, in a page that is still
+    in the ring).  Every attention kernel that takes the shape: a chunk of 21 rows through the
+    prefill kernels, the last row through the decode kernel, all rows through the plain kernel,
+    against float64 on the positions in order."""
+    o = ops()
+    q_heads, kv_heads, window, last, ring = 4, 2, 70, 400, 3
+    n_pages, table_stride = 7, 4
+    g = torch.Generator().manual_seed(61)
+    K = (torch.randn((last + 1, kv_heads, hd), generator=g) * 0.3).to(dtype)
+    V = torch.randn((last + 1, kv_heads, hd), generator=g).to(dtype)
+    far = 330
+    K[far] = 6.0                                            # against positive queries: the largest score by far
+    storage = torch.zeros((n_pages, 2, kv_heads, 64, hd), dtype=dtype, device=DEV)
+    table = torch.full((2, table_stride), -1, dtype=torch.int32, device=DEV)
+    table[1, :ring] = torch.tensor([5, 2, 6], dtype=torch.int32)
+    table[0, :ring] = torch.tensor([0, 1, 3], dtype=torch.int32)
+    newest = last // 64
+    for pos in range((newest - ring + 1) * 64, (newest + 1) * 64):
+        page = int(table[1, (pos // 64) % ring])
+        if pos <= last:
+            storage[page, 0, :, pos % 64] = K[pos].to(DEV)
+            storage[page, 1, :, pos % 64] = V[pos].to(DEV)
+        else:                                               # what the lap before left there
+            storage[page, 0, :, pos % 64] = 50.0
+            storage[page, 1, :, pos % 64] = -99.0
+    view = o.PagedCacheArg(storage.data_ptr(), table.data_ptr(), 2 * kv_heads * 64 * hd, table_stride, ring, 64, kv_heads,
+                           hd, n_pages)
+    first_pos = 380
+    n = last - first_pos + 1
+    q = (torch.rand((n, q_heads * hd), generator=g) * 0.5 + 0.25).to(dtype).to(DEV)
+    slots = torch.full((n,), 1, dtype=torch.int32, device=DEV)
+    pos = torch.arange(first_pos, last + 1, dtype=torch.int32, device=DEV)
+    scale = 1 / math.sqrt(hd)
+
+    want = torch.zeros((n, q_heads, hd), dtype=torch.float64)
+    for r in range(n):
+        p = first_pos + r
+        lo = p - window + 1
+        for h in range(q_heads):
+            kh = h // (q_heads // kv_heads)
+            sc = (K[lo:p + 1, kh].double() @ q[r].reshape(q_heads, hd)[h].double().cpu()) * scale
+            want[r, h] = torch.softmax(sc, 0) @ V[lo:p + 1, kh].double()
+    want = want.reshape(n, q_heads * hd)
+    assert (want[:-1].reshape(n - 1, q_heads, hd) - V[far].double().repeat_interleave(2, 0)).abs().max() < 0.05   # they see key 330
+    assert (want[-1].reshape(q_heads, hd) - V[far].double().repeat_interleave(2, 0)).abs().max() > 0.5            # row 400 does not
+    tol = (1e-5 if dtype == torch.float32 else BF16_EPS) * float(V.float().abs().max())
+
+    out = torch.full_like(q, 55.0)
+    o.attention_rows(q, out, view, slots, pos, n, q_heads, scale, window)
+    assert (out.double().cpu() - want).abs().max() < tol, "plain kernel"
+    if dtype != torch.bfloat16:
+        return
+    mk = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)   # noqa: E731
+    tile_seq, tile_row0, n_tiles = tiles_for([0, n])
+    kernels = [("mma.sync prefill", o.attention_prefill_bf16)]
+    if o.attention_tc_takes(view, dtype):
+        kernels.append(("tcgen05 prefill", o.attention_prefill_tcgen05))
+    for name, kernel in kernels:
+        out = torch.full_like(q, 55.0)
+        kernel(q, out, view, tile_seq, tile_row0, n_tiles, mk([0, n]), mk([1]), mk([first_pos]), q_heads, scale, window)
+        o.check_tc_status(q.device)
+        assert (out.double().cpu() - want).abs().max() < tol, name
+    for splits in (1, 2):
+        for k in (n - 1, n - 2):                            # the row that must not see key 330, and one that does
+            out1 = torch.full((1, q_heads * hd), 55.0, dtype=dtype, device=DEV)
+            o.attention_decode_bf16(q[k:k + 1].contiguous(), out1, view, slots[k:k + 1].contiguous(),
+                                    pos[k:k + 1].contiguous(), 1, q_heads, scale, window, splits, None)
+            assert (out1.double().cpu() - want[k:k + 1]).abs().max() < tol, f"decode kernel, {splits} splits, row {k}"

@@ -294,6 +294,8 @@ def test_a_model_with_a_windowed_layer_has_two_cache_groups_and_matches_the_plai
     tdt = torch.float32 if dtype == "float32" else torch.bfloat16
     init = RandomInit(seed=11, linear_std=0.1, norm_jitter=0.1)
     cpu = {n.name: make_tensor(n, init, tdt, "cpu") for n in tensor_needs_of_spec(spec)}
+    if dtype == "float32":        # see below; in bfloat16 the effect lies under the tolerance, so the data stay as they were
+        cpu["model.embed_tokens.weight"][5] *= 6.0
     from x0ne_engine_b200.weights.loader import held_dtype
     dev = {n.name: cpu[n.name].to(DEV).to(held_dtype(n, tdt, tdt)) for n in tensor_needs_of_spec(spec)}
     eng = Engine(spec, dev, dtype, DEV, max_tokens=1024)
@@ -304,15 +306,30 @@ def test_a_model_with_a_windowed_layer_has_two_cache_groups_and_matches_the_plai
 
     w = {k: v.double().numpy() for k, v in cpu.items()}
     pc = dict(q_heads=4, kv_heads=2, head_dim=16, eps=1e-6, theta=1e4)
-    ids = np.random.default_rng(3).integers(0, 90, 300).tolist()
+    # Token 5 (its embedding row scaled up, so that it dominates the residual of its positions)
+    # stands at 150, 189 and 190: position 189 still sees key 150, the window's oldest, position 190
+    # must not, although that key's page is still in the ring.  The per-head norms of q and k bound
+    # every score, so one key more moves the logits by about a thousandth here: ten times the 32-bit
+    # tolerance.  (The kernels alone are tested on a lapped ring with a key that decides the output.)
+    special = 5
+    ids = np.random.default_rng(3).integers(6, 90, 300).tolist()
+    for at in (150, 189, 190):
+        ids[at] = special
     pos = np.arange(len(ids))
-    x = w["model.embed_tokens.weight"][ids]
-    for l, win_l in ((0, None), (1, window)):
-        p = f"model.layers.{l}."
-        x = x + P.attention_block(P.rmsnorm(x, w[p + "input_layernorm.weight"], 1e-6), w, p + "self_attn.", pc, pos,
-                                  window=win_l)
-        x = x + P.swiglu_mlp(P.rmsnorm(x, w[p + "post_attention_layernorm.weight"], 1e-6), w, p + "mlp.")
-    want = P.rmsnorm(x, w["model.norm.weight"], 1e-6) @ w["model.embed_tokens.weight"].T
+
+    def plain(window_of_layer_1):
+        x = w["model.embed_tokens.weight"][ids]
+        for l, win_l in ((0, None), (1, window_of_layer_1)):
+            p = f"model.layers.{l}."
+            x = x + P.attention_block(P.rmsnorm(x, w[p + "input_layernorm.weight"], 1e-6), w, p + "self_attn.", pc, pos,
+                                      window=win_l)
+            x = x + P.swiglu_mlp(P.rmsnorm(x, w[p + "post_attention_layernorm.weight"], 1e-6), w, p + "mlp.")
+        return P.rmsnorm(x, w["model.norm.weight"], 1e-6) @ w["model.embed_tokens.weight"].T
+
+    want = plain(window)
+    wider = plain(window + 1)
+    assert dtype != "float32" or np.abs(wider[190] - want[190]).max() > 5e-4 * np.abs(want[190]).max(), \
+        "the key just outside the window does not matter enough for this test to see it"
 
     def close(got, ref, what):
         err = np.max(np.abs(got - ref) / np.max(np.abs(ref), axis=-1, keepdims=True))

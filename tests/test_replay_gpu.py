@@ -18,14 +18,18 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def run_trace(folder, dtype, steps, max_tokens, tmp_path, vocab):
+def run_trace(folder, dtype, steps, max_tokens, tmp_path, vocab, extra=()):
+    from x0ne_engine_b200.engine.replay import check_manifest
     out = tmp_path / f"out_{dtype}_{len(list(tmp_path.iterdir()))}"
     text = "".join(json.dumps(s) + "\n" for s in steps)
     r = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", folder, "--dtype", dtype,
-                        "--out", str(out), "--max-tokens", str(max_tokens)], input=text, capture_output=True, text=True,
-                       timeout=600)
+                        "--out", str(out), "--max-tokens", str(max_tokens), *extra], input=text, capture_output=True,
+                       text=True, timeout=600)
     assert r.returncode == 0, r.stderr[-2000:]
     assert [l for l in r.stdout.splitlines() if l.startswith("done ")] == [f"done {s['step']}" for s in steps]
+    man = check_manifest(str(out))                     # every file present, of its shape's length, with its SHA-256
+    assert man["dtype"] == dtype and man["vocab_size"] == vocab
+    assert [f["step"] for f in man["files"]] == [s["step"] for s in steps if any(e.get("want") for e in s["entries"])]
     res = {}
     for s in steps:
         n = sum(len(e.get("want", [])) for e in s["entries"])
@@ -107,6 +111,39 @@ def test_replay_three_ways(name, lengths, dtype, tmp_path):
             if dtype == "float32":
                 assert np.array_equal(got[step][j], whole[k][pos]), f"step {step} {k} position {pos}"
             close(got[step][j][None], plain[k][pos][None], f"{name} batched {k} position {pos}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_replay_with_steps_cut_into_passes(dtype, tmp_path):
+    """`--max-step-tokens 64`: the batch's prompts (307 rows) run as five passes that cut requests
+    mid-prompt; logits are wanted in every pass.  Against the same trace run in one pass per step
+    (same bits in float32) and the plain implementation; then two tokens each, decoded."""
+    name, lengths = "B", [34, 97, 101, 75]
+    folder = model_folder(name, "float32" if dtype == "float32" else "bfloat16")
+    vocab = plain_model(folder)[0]["vocab"]
+    reqs = {f"r{i}": ids for i, ids in enumerate(prompts_for(vocab, lengths, seed=31))}
+    want = {k: [len(v) - 3, 0, len(v) // 2] for k, v in reqs.items()}
+    steps = [{"step": 0, "entries": [{"id": k, "tokens": v[:-2], "want": want[k]} for k, v in reqs.items()], "end": []}]
+    for j in (2, 1):
+        steps.append({"step": len(steps), "entries": [{"id": k, "tokens": [v[-j]], "want": [0]} for k, v in reqs.items()],
+                      "end": list(reqs) if j == 1 else []})
+    room = sum(r64(n) for n in lengths)
+    cut = run_trace(folder, dtype, steps, room, tmp_path, vocab, extra=("--max-step-tokens", "64"))
+    one = run_trace(folder, dtype, steps, room, tmp_path, vocab)
+    close = assert_close_f32 if dtype == "float32" else assert_close_bf16
+    for step in cut:
+        if dtype == "float32":
+            assert np.array_equal(cut[step], one[step]), f"step {step}: passes of 64 differ from one pass"
+        else:
+            assert np.max(np.abs(cut[step] - one[step]) / np.max(np.abs(one[step]), axis=-1, keepdims=True)) <= BF16_SELF_TOL
+    at = 0
+    for k, v in reqs.items():
+        plain = plain_logits(folder, v)
+        close(cut[0][at:at + 3], plain[want[k]], f"{k} prompt rows")
+        at += 3
+    for j, step in ((2, 1), (1, 2)):
+        for i, (k, v) in enumerate(reqs.items()):
+            close(cut[step][i][None], plain_logits(folder, v)[len(v) - j][None], f"{k}, {j} from the end")
 
 
 def test_replay_refuses_an_unknown_architecture(tmp_path):

@@ -642,15 +642,15 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(DecodeArgs a, Pag
 template <int HD>
 static int launch_prefill(const PrefillArgs& a, const PagedCache& cache, int n_tiles, cudaStream_t stream) {
     const size_t smem = (size_t)(64 * PREFILL_MT + 4 * 64) * (HD + PADE) * sizeof(bf16);
-    static bool configured = false;
-    if (!configured) {
+    static OncePerDevice configured;
+    if (configured.need()) {
         cudaFuncSetAttribute(attention_prefill_kernel<HD, PREFILL_MT>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
         cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel<HD, PREFILL_MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) {
             x0ne_set_error("attention_prefill: cannot set %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
             return (int)e;
         }
-        configured = true;
+        configured.done();
     }
     dim3 grid(a.q_heads, n_tiles);
     x0ne_launch(attention_prefill_kernel<HD, PREFILL_MT>, dim3(grid), dim3(128), smem, stream, a, cache);
@@ -664,8 +664,8 @@ static int launch_decode_variant(const DecodeArgs& a, const PagedCache& cache, i
     size_t smem = (size_t)(16 + 4 * DECODE_STAGES * 2 * 16) * (HD + PADE) * sizeof(bf16);
     const size_t merge = (size_t)(4 * 16 * HD + 4 * 16 * 2 + 16 * 2) * sizeof(float);
     if (smem < 16 * (HD + PADE) * sizeof(bf16) + merge) smem = 16 * (HD + PADE) * sizeof(bf16) + merge;
-    static bool configured = false;
-    if (!configured) {
+    static OncePerDevice configured;
+    if (configured.need()) {
         cudaFuncSetAttribute(attention_decode_kernel<HD, DECODE_STAGES, CLUSTER>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
         cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<HD, DECODE_STAGES, CLUSTER>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -673,7 +673,7 @@ static int launch_decode_variant(const DecodeArgs& a, const PagedCache& cache, i
             x0ne_set_error("attention_decode: cannot set %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
             return (int)e;
         }
-        configured = true;
+        configured.done();
     }
     const int G = a.q_heads / cache.kv_heads;
     dim3 grid(a.splits, cache.kv_heads * ((G + 15) / 16), n_rows);

@@ -24,6 +24,9 @@ X0NE_API int x0ne_attention_decode_bf16_noalloc(const void* q, void* out, PagedC
     if (int e = check_common(cache, q_heads, "attention_decode_noalloc")) return e;
     X0NE_REQUIRE(n_rows >= 0 && n_rows <= 65535, "attention_decode_noalloc: %d rows in one launch (limit 65535)", n_rows);
     X0NE_REQUIRE(splits >= 1 && splits <= 64, "attention_decode_noalloc: %d splits (1 to 64)", splits);
+    // everything the launch itself would refuse is refused here, before the counters are touched
+    X0NE_REQUIRE(window >= 0, "attention_decode_noalloc: negative window");
+    X0NE_REQUIRE(n_rows == 0 || (q && out && row_slot && row_pos), "attention_decode_noalloc: null q, output or row tables");
     if (n_rows == 0) return 0;
     const int64_t need =
         splits > 1 ? x0ne_attention_decode_scratch_bytes(n_rows, q_heads, cache.kv_heads, cache.head_dim, splits) : 0;

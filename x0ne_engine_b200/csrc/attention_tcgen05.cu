@@ -443,15 +443,15 @@ static int launch_attn_tc(const CUtensorMap& map_q, const CUtensorMap& map_kv, c
                           int n_tiles, int* status, cudaStream_t stream) {
     constexpr int NB = HD / 64;
     const size_t smem = (size_t)NB * 128 * 128 + 4 * (size_t)NB * 64 * 128 + 128 * 128 + sizeof(AttnTcShared);
-    static bool configured = false;
-    if (!configured) {
+    static OncePerDevice configured;
+    if (configured.need()) {
         cudaFuncSetAttribute(attention_prefill_tc_kernel<HD>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
         cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) {
             x0ne_set_error("attention_prefill_tc: cannot set %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
             return (int)e;
         }
-        configured = true;
+        configured.done();
     }
     x0ne_launch(attention_prefill_tc_kernel<HD>, dim3(a.q_heads, n_tiles), dim3(ATC_THREADS), smem, stream, map_q, map_kv, a,
                 cache, status);

@@ -59,6 +59,26 @@ __device__ __forceinline__ void pdl_prologue() {
 
 bool x0ne_pdl_enabled();
 
+// Set-up that the runtime keeps per device (a kernel's shared-memory attribute, occupancy numbers)
+// is done once per device, by the first call with that device current: `need()` says whether it
+// is still to do, `done()` records it.  Two host threads making the first call on a device at the
+// same moment would both do it, which is harmless (the same values are set twice).
+struct OncePerDevice {
+    unsigned char set[64] = {};
+    static int device() {
+        int d = 0;
+        return cudaGetDevice(&d) == cudaSuccess && d >= 0 && d < 64 ? d : -1;
+    }
+    bool need() const {
+        const int d = device();
+        return d < 0 || !set[d];
+    }
+    void done() {
+        const int d = device();
+        if (d >= 0) set[d] = 1;
+    }
+};
+
 template <typename... KArgs, typename... Args>
 static inline cudaError_t x0ne_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
                                       Args... args) {
@@ -103,37 +123,44 @@ template <typename T> __device__ __forceinline__ T from_f32(float x);
 template <> __device__ __forceinline__ float from_f32<float>(float x) { return x; }
 template <> __device__ __forceinline__ bf16 from_f32<bf16>(float x) { return __float2bfloat16_rn(x); }
 
-__device__ __forceinline__ float warp_sum(float v) {
+// Reductions.  One butterfly over the lanes of a warp and one two-level form over a block, both
+// with the combining operation as a parameter; every lane / thread gets the result, and the order
+// in which values meet depends on lane and warp numbers only, never on the data or on what else
+// runs (the fixed-order rule of x0ne-core/kernels/cuda/common.cuh:1).
+struct OpSum {
+    template <typename V> __device__ __forceinline__ V operator()(V a, V b) const { return a + b; }
+};
+struct OpMax {
+    __device__ __forceinline__ float operator()(float a, float b) const { return fmaxf(a, b); }
+    __device__ __forceinline__ int operator()(int a, int b) const { return a > b ? a : b; }
+    __device__ __forceinline__ unsigned long long operator()(unsigned long long a, unsigned long long b) const {
+        return a > b ? a : b;
+    }
+};
+
+template <typename V, typename Op>
+__device__ __forceinline__ V warp_reduce(V v, Op op) {
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    for (int width = 32; width > 1; width >>= 1) v = op(v, __shfl_xor_sync(0xffffffffu, v, width >> 1));
     return v;
 }
 
-__device__ __forceinline__ float warp_max(float v) {
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
-    return v;
-}
-
-// Sum over the block (blockDim.x a multiple of 32, at most 1024); every thread gets it.
-// `sh` holds 32 floats.  The order is fixed by blockDim alone.
-__device__ __forceinline__ float block_sum(float v, float* sh) {
-    v = warp_sum(v);
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
-    __syncthreads();
+// Over the block (blockDim.x a multiple of 32, at most 1024).  `sh` holds 32 values of V;
+// `neutral` fills the places of warps the block does not have.
+template <typename V, typename Op>
+__device__ __forceinline__ V block_reduce(V v, V* sh, Op op, V neutral) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+    v = warp_reduce(v, op);
+    __syncthreads();              // `sh` may still be read by a reduction before this one
     if (lane == 0) sh[warp] = v;
     __syncthreads();
-    return warp_sum(lane < nw ? sh[lane] : 0.f);
+    return warp_reduce(lane < n_warps ? sh[lane] : neutral, op);
 }
 
-__device__ __forceinline__ float block_max(float v, float* sh) {
-    v = warp_max(v);
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
-    __syncthreads();
-    if (lane == 0) sh[warp] = v;
-    __syncthreads();
-    return warp_max(lane < nw ? sh[lane] : -INFINITY);
-}
+__device__ __forceinline__ float warp_sum(float v) { return warp_reduce(v, OpSum()); }
+__device__ __forceinline__ float warp_max(float v) { return warp_reduce(v, OpMax()); }
+__device__ __forceinline__ float block_sum(float v, float* sh) { return block_reduce(v, sh, OpSum(), 0.f); }
+__device__ __forceinline__ float block_max(float v, float* sh) { return block_reduce(v, sh, OpMax(), -INFINITY); }
 
 // The paged cache of one run-order entry.  A page holds `page_size` positions of every kv
 // head, K then V: [2][kv_heads][page_size][head_dim].  A sequence's logical page

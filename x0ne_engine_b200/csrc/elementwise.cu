@@ -71,28 +71,35 @@ X0NE_API int x0ne_embedding(const void* table, int dt, const int32_t* tokens, fl
 // rows[i] (used to norm only the rows whose logits are wanted).
 // One block per row; the sum of squares is a fixed-order block sum.
 // ----------------------------------------------------------------------------------------
+// General form, any width: each thread owns every blockDim-th element.  The row after the add is
+// parked in shared memory between the two sweeps when it fits there (`keep` floats of dynamic
+// shared memory, 0 if it does not), so the residual is read once.
 template <typename T>
-__global__ void add_rmsnorm_kernel(float* __restrict__ resid, const T* __restrict__ delta,
-                                   const float* __restrict__ w, T* __restrict__ out,
-                                   const int32_t* __restrict__ rows, int hidden, float eps) {
-    __shared__ float sh[32];
+__global__ void add_rmsnorm_any_kernel(float* __restrict__ resid, const T* __restrict__ delta,
+                                       const float* __restrict__ w, T* __restrict__ out,
+                                       const int32_t* __restrict__ rows, int hidden, float eps, int keep) {
+    extern __shared__ float parked[];
+    __shared__ float partial[32];
     pdl_prologue();
     const int64_t src = rows ? rows[blockIdx.x] : blockIdx.x;
     float* r = resid + src * hidden;
-    const T* d = delta ? delta + src * hidden : nullptr;
-    T* o = out + (int64_t)blockIdx.x * hidden;
-    float ss = 0.f;
+    float sum_sq = 0.f;
     for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
         float v = r[i];
-        if (d) {
-            v = v + to_f32(d[i]);
+        if (delta) {
+            v = v + to_f32(delta[src * hidden + i]);     // one IEEE add, stored back
             r[i] = v;
         }
-        ss += v * v;
+        if (i < keep) parked[i] = v;
+        sum_sq = fmaf(v, v, sum_sq);
     }
-    const float total = block_sum(ss, sh);
-    const float scale = 1.0f / sqrtf(total / (float)hidden + eps);
-    for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = from_f32<T>(r[i] * scale * w[i]);
+    const float mean_sq = block_reduce(sum_sq, partial, OpSum(), 0.f) / (float)hidden;
+    const float scale = 1.0f / sqrtf(mean_sq + eps);
+    T* o = out + (int64_t)blockIdx.x * hidden;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        const float v = i < keep ? parked[i] : r[i];     // a thread reads back only what it wrote itself
+        o[i] = from_f32<T>(v * scale * w[i]);
+    }
 }
 
 // The same, for hidden % 8 == 0 and hidden <= 8 * 1024 * VEC_IT: 16-byte accesses, and the row stays
@@ -205,10 +212,12 @@ X0NE_API int x0ne_add_rmsnorm(float* resid, const void* delta, const float* w, v
         X0NE_LAUNCH_CHECK();
     }
     const int block = 256;
+    const int keep = hidden <= 10240 ? hidden : 0;        // up to 40 KB of dynamic shared memory
+    const size_t smem = (size_t)keep * sizeof(float);
     if (dt == X0NE_F32)
-        x0ne_launch(add_rmsnorm_kernel<float>, dim3(n_rows), dim3(block), 0, stream, resid, (const float*)delta, w, (float*)out, rows, hidden, eps);
+        x0ne_launch(add_rmsnorm_any_kernel<float>, dim3(n_rows), dim3(block), smem, stream, resid, (const float*)delta, w, (float*)out, rows, hidden, eps, keep);
     else if (dt == X0NE_BF16)
-        x0ne_launch(add_rmsnorm_kernel<bf16>, dim3(n_rows), dim3(block), 0, stream, resid, (const bf16*)delta, w, (bf16*)out, rows, hidden, eps);
+        x0ne_launch(add_rmsnorm_any_kernel<bf16>, dim3(n_rows), dim3(block), smem, stream, resid, (const bf16*)delta, w, (bf16*)out, rows, hidden, eps, keep);
     else
         X0NE_REQUIRE(false, "add_rmsnorm: unknown dtype tag %d", dt);
     X0NE_LAUNCH_CHECK();

@@ -194,7 +194,9 @@ static int launch_smallm(const bf16* W, const bf16* X, OutT* Y, int M, int N, in
     constexpr int DEPTH = smallm_depth(MT, SWIGLU);
     constexpr int SMEM = DEPTH * SLOTS * SM_WARPS * 32 * 16 + SM_WARPS * SETS * MT * 128 * 4;
     const int n_tiles = (N + 15) / 16;
-    static int per_sm = 0;     // blocks of this variant that fit on one SM
+    static int fit[64];        // per device: blocks of this variant that fit on one SM (0: not asked yet)
+    const int dev = OncePerDevice::device();
+    int per_sm = dev >= 0 ? fit[dev] : 0;
     if (per_sm == 0) {
         auto kernel = gemm_smallm_kernel<MT, OutT, SWIGLU, DEPTH>;
         cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
@@ -206,6 +208,7 @@ static int launch_smallm(const bf16* W, const bf16* X, OutT* Y, int M, int N, in
         int n = 0;
         if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, SM_WARPS * 32, SMEM) != cudaSuccess || n < 1) n = 1;
         per_sm = n;
+        if (dev >= 0) fit[dev] = n;
     }
     // Every block gets the same number of tiles (but for the remainder), and no more blocks are
     // launched than are resident at once: the blocks then end together.

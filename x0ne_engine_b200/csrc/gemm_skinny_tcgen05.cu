@@ -246,15 +246,15 @@ static int launch_skinny(const void* W, const void* X, int x_rows, OutT* Y, int 
     if (int e = x0ne_tc_make_map(&map_x, X, x_rows < SK_XROWS ? x_rows : SK_XROWS, K, SK_XROWS)) return e;
     if (int e = x0ne_tc_make_map(&map_w, W, SWIGLU ? 2 * (int64_t)N : N, K, SWIGLU ? 64 : 128)) return e;
     const size_t smem = (size_t)SK_STAGES * (128 * 128 + SK_XROWS * 128) + sizeof(SkShared) + 1024;
-    static bool configured = false;
-    if (!configured) {
+    static OncePerDevice configured;
+    if (configured.need()) {
         cudaFuncSetAttribute(gemm_skinny_tc_kernel<SWIGLU, OutT>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
         cudaError_t e = cudaFuncSetAttribute(gemm_skinny_tc_kernel<SWIGLU, OutT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) {
             x0ne_set_error("gemm_skinny_tc: cannot set %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
             return (int)e;
         }
-        configured = true;
+        configured.done();
     }
     constexpr int COLS = SWIGLU ? 64 : 128;
     const int tiles = (N + COLS - 1) / COLS;

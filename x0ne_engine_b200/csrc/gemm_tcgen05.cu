@@ -434,14 +434,14 @@ static int launch_tc(const void* W, const void* X, OutT* Y, int M, int N, int K,
     if (int e = x0ne_tc_make_map(&map_x, X, M, K, TC_BM)) return e;
     if (int e = x0ne_tc_make_map(&map_w, W, SWIGLU ? 2 * (int64_t)N : N, K, SWIGLU ? 128 : 256)) return e;
     const size_t smem = (size_t)TC_STAGES * (TC_BM * 128 + 256 * 128) + sizeof(TcShared) + 1024;
-    static bool configured = false;
-    if (!configured) {
+    static OncePerDevice configured;
+    if (configured.need()) {
         cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<SWIGLU, OutT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) {
             x0ne_set_error("gemm_tc: cannot set %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
             return (int)e;
         }
-        configured = true;
+        configured.done();
     }
     constexpr int BN = SWIGLU ? 128 : 256;
     const int n_tiles = (N + BN - 1) / BN, m_tiles = (M + TC_BM - 1) / TC_BM;
@@ -463,14 +463,14 @@ static int launch_tc_pair(const void* W, const void* X, OutT* Y, int M, int N, i
     if (int e = x0ne_tc_make_map(&map_x, X, M, K, 128)) return e;
     if (int e = x0ne_tc_make_map(&map_w, W, SWIGLU ? 2 * (int64_t)N : N, K, 128)) return e;
     const size_t smem = (size_t)TC2_STAGES * (128 * 128 * 2) + sizeof(Tc2Shared) + 1024;
-    static bool configured = false;
-    if (!configured) {
+    static OncePerDevice configured;
+    if (configured.need()) {
         cudaError_t e = cudaFuncSetAttribute(gemm_tc_pair_kernel<SWIGLU, OutT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) {
             x0ne_set_error("gemm_tc_pair: cannot set %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
             return (int)e;
         }
-        configured = true;
+        configured.done();
     }
     constexpr int BN = SWIGLU ? 128 : 256;
     const int n_tiles = (N + BN - 1) / BN, m_tiles = (M + 255) / 256;

@@ -42,7 +42,7 @@ class SampleIOArg(Structure):
     _fields_ = [("logits", c_void_p), ("temperature", c_void_p), ("top_p", c_void_p), ("seed", c_void_p),
                 ("draw_counter", c_void_p), ("stop_ids", c_void_p), ("finished", c_void_p), ("budget", c_void_p),
                 ("out_token", c_void_p), ("next_token", c_void_p), ("next_pos", c_void_p),
-                ("ld", c_int64), ("vocab", c_int32), ("n_stop", c_int32)]
+                ("status", c_void_p), ("ld", c_int64), ("vocab", c_int32), ("n_stop", c_int32)]
 
 
 _libs = {}
@@ -239,8 +239,11 @@ def gemm_f32_nt(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, m: int) -> No
 
 
 def sample(logits: torch.Tensor, n_rows: int, out_token: torch.Tensor, *, temperature=None, top_p=None, seed=None,
-           draw_counter=None, stop_ids=None, finished=None, budget=None, next_token=None, next_pos=None) -> None:
-    """Picks a token per logits row on the device (see sampling.cu for the rules)."""
+           draw_counter=None, stop_ids=None, finished=None, budget=None, next_token=None, next_pos=None,
+           status=None) -> None:
+    """Picks a token per logits row on the device (see sampling.cu for the rules).  `stop_ids` may
+    be padded with -1 (no token has that id).  With `status` (one int32 on the device) the kernel
+    also copies that int to out_token[n_rows], so it reaches the host with the picks."""
     lib = _lib("core")
     _need(logits, torch.float32, "logits")
     _need(out_token, torch.int32, "token output")
@@ -254,13 +257,17 @@ def sample(logits: torch.Tensor, n_rows: int, out_token: torch.Tensor, *, temper
             _need(t, dt, what)
             if t.numel() < n_rows:
                 raise KernelError(f"sample: {what} shorter than the rows asked for")
+    if status is not None:
+        _need(status, torch.int32, "status word")
+        if out_token.numel() < n_rows + 1:
+            raise KernelError("sample: no room for the status word after the picks")
     n_stop = 0
     if stop_ids is not None and stop_ids.numel() > 0:
         _need(stop_ids, torch.int32, "stop ids")
         n_stop = stop_ids.numel()
     io = SampleIOArg(_ptr(logits), _ptr(temperature), _ptr(top_p), _ptr(seed), _ptr(draw_counter),
                      _ptr(stop_ids if n_stop else None), _ptr(finished), _ptr(budget), _ptr(out_token),
-                     _ptr(next_token), _ptr(next_pos), logits.stride(0), logits.shape[1], n_stop)
+                     _ptr(next_token), _ptr(next_pos), _ptr(status), logits.stride(0), logits.shape[1], n_stop)
     _check(lib, lib.x0ne_sample(io, n_rows, _stream()), "sample")
 
 
@@ -415,11 +422,16 @@ def check_tc_status(device) -> None:
     st = int(gemm_tc_status(device)[0])
     if st != 0:
         gemm_tc_status(device).zero_()
-        codes = [b for b in range(32) if st >> b & 1]
-        raise KernelError(f"a tcgen05 kernel gave up waiting on a barrier (codes {codes}; products: 1 copy, 2 MMA, "
-                          "3 epilogue, 4 accumulator; attention: 5 queries, 6 keys, 13 and 15 values, 7 probabilities, "
-                          "8, 11 and 14 output, 10, 12 and 17 scores, 16 and 18 the other half of the row; 9: misaligned "
-                          "shared memory); its output is not valid")
+        raise KernelError(describe_tc_status(st))
+
+
+def describe_tc_status(st: int) -> str:
+    """The message for a status word that is not zero: one bit per kind of wait that ran out."""
+    codes = [b for b in range(32) if st >> b & 1]
+    return (f"a tcgen05 kernel gave up waiting on a barrier (codes {codes}; products: 1 copy, 2 MMA, "
+            "3 epilogue, 4 accumulator; attention: 5 queries, 6 keys, 13 and 15 values, 7 probabilities, "
+            "8, 11 and 14 output, 10, 12 and 17 scores, 16 and 18 the other half of the row; 9: misaligned "
+            "shared memory); its output is not valid")
 
 
 def gemm_tc_status(device) -> torch.Tensor:

@@ -23,7 +23,21 @@
 
 #define SB 1024
 
-__device__ __forceinline__ bool better(float v, int i, float bv, int bi) { return v > bv || (v == bv && i < bi); }
+// A logit and its index as one 64-bit key whose unsigned order is "larger value first, then lower
+// index": the float's bits made monotone (sign flipped for positives, all bits for negatives; -0
+// counts as +0) above the index counted down from 2^31 - 1.  The argmax of a row is then a plain
+// maximum, which the block takes with the common reduction.  NaNs are looked for separately.
+__device__ __forceinline__ unsigned long long pick_key(float v, int i) {
+    uint32_t b = __float_as_uint(v + 0.0f);
+    b = (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+    return ((unsigned long long)b << 32) | (uint32_t)(0x7fffffff - i);
+}
+__device__ __forceinline__ float key_value(unsigned long long key) {
+    uint32_t b = (uint32_t)(key >> 32);
+    b = (b & 0x80000000u) ? (b & 0x7fffffffu) : ~b;
+    return __uint_as_float(b);
+}
+__device__ __forceinline__ int key_index(unsigned long long key) { return 0x7fffffff - (int)(uint32_t)key; }
 
 // Inclusive scan of one value per thread over the block; returns this thread's inclusive
 // prefix, and the block total through `total`.  `sh` holds 33 floats.
@@ -101,6 +115,7 @@ struct SampleIO {
     int32_t* out_token;          // [rows]: the pick, -1 for a NaN row, -2 for a row already finished
     int32_t* next_token;         // [rows] or null: where the next step reads its token
     int32_t* next_pos;           // [rows] or null: advanced by one when the token will be fed
+    const int32_t* status;       // null, or one int copied to out_token[rows] (the kernels' status word)
     int64_t ld;
     int32_t vocab;
     int32_t n_stop;
@@ -109,11 +124,14 @@ struct SampleIO {
 __global__ void __launch_bounds__(SB) sample_kernel(SampleIO io) {
     __shared__ float shf[33];
     __shared__ int shi[33];
-    __shared__ float s_bv[32];
+    __shared__ unsigned long long s_key[32];
     __shared__ int s_bi[32];
     __shared__ int s_pick;
     const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     pdl_prologue();
+    // the word in which this library's tensor-core kernels report a wait that ran out travels to
+    // the host with the picks: one more int after the last row's token
+    if (row == 0 && tid == 0 && io.status) io.out_token[gridDim.x] = *io.status;
     if (io.finished && io.finished[row]) {
         if (tid == 0) io.out_token[row] = -2;
         return;
@@ -121,42 +139,28 @@ __global__ void __launch_bounds__(SB) sample_kernel(SampleIO io) {
     const float* x = io.logits + (int64_t)row * io.ld;
     const int V = io.vocab;
 
-    // ---- max, argmax, NaN
-    float bv = -INFINITY;
-    int bi = 0x7fffffff;
+    // ---- largest logit (lowest index among equals), and whether the row holds a NaN
+    // (x0ne-core/kernels/cuda/argmax.cu:4-10: a NaN anywhere means no token)
+    unsigned long long best = 0ull;
     bool nan = false;
     for (int i = tid; i < V; i += SB) {
         const float v = x[i];
         nan |= v != v;
-        if (better(v, i, bv, bi)) { bv = v; bi = i; }
+        const unsigned long long key = pick_key(v, i);
+        best = key > best ? key : best;
     }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-        if (better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
-    }
-    if (lane == 0) { s_bv[warp] = bv; s_bi[warp] = bi; }
-    if (__syncthreads_or(nan)) {
+    const bool any_nan = __syncthreads_or(nan);
+    if (any_nan) {
         if (tid == 0) {
             io.out_token[row] = -1;
             if (io.finished) io.finished[row] = 1;
         }
         return;
     }
-    if (warp == 0) {
-        bv = s_bv[lane];
-        bi = s_bi[lane];
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-            if (better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
-        }
-        if (lane == 0) { s_bv[0] = bv; s_pick = bi; }
-    }
+    best = block_reduce(best, s_key, OpMax(), 0ull);
+    if (tid == 0) s_pick = key_index(best);
     __syncthreads();
-    const float vmax = s_bv[0];
+    const float vmax = key_value(best);
 
     const float t = io.temperature ? io.temperature[row] : 0.f;
     const float top_p = io.top_p ? io.top_p[row] : 1.f;
@@ -252,17 +256,8 @@ __global__ void __launch_bounds__(SB) sample_kernel(SampleIO io) {
                 if (top_p < 1.f && e == tau) keep = rank++ < n_tie;
                 if (keep) last = i;
             }
-            // max over threads
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) last = max(last, __shfl_xor_sync(0xffffffffu, last, o));
-            if (lane == 0) s_bi[warp] = last;
-            __syncthreads();
-            if (warp == 0) {
-                last = s_bi[lane];
-#pragma unroll
-                for (int o = 16; o > 0; o >>= 1) last = max(last, __shfl_xor_sync(0xffffffffu, last, o));
-                if (lane == 0) s_pick = last;
-            }
+            last = block_reduce(last, s_bi, OpMax(), -1);
+            if (tid == 0) s_pick = last;
             __syncthreads();
         }
     }

@@ -17,8 +17,10 @@
 //
 // Rules for callers.
 //   * The first call on each device looks the array's device address up (cudaGetSymbolAddress)
-//     and sets the kernel's shared-memory attribute.  Make that first call, with the device
-//     current, before any stream capture you intend to do.
+//     and sets the kernel's shared-memory attribute for that device.  Make that first call, with
+//     the device current, before any stream capture you intend to do, and from one host thread:
+//     the look-up is not locked (two threads racing through it would store the same address, but
+//     nothing orders their stores).
 //   * All calls on a device share the one array.  Two calls that can overlap on the GPU (different
 //     streams without an ordering between them) race on it; order them.
 //   * The array keeps what the last call left.  The entry point clears the part that must start

@@ -15,6 +15,13 @@ and either way its extra pick is dropped.  So the GPU never waits for the host's
 
 When sequences finish, the live rows are compacted on the device and the graph of the smaller
 batch size is used.
+
+What a captured step reads lives at fixed device addresses for the life of the `DeviceBatch`: the
+per-row arrays, and a stop-id list of fixed length (`STOP_IDS_ON_DEVICE` entries, unused ones -1)
+that `start` refills for every batch, so a graph captured for one batch serves every later batch
+whatever its stop tokens.  The int in which this library's tensor-core kernels report a wait that
+ran out is copied by the sampler behind the step's picks and read with them; a step whose word is
+not zero raises, naming the step.
 """
 from __future__ import annotations
 
@@ -27,6 +34,21 @@ from ..cache import CacheFull
 from ..csrc import ops
 from .engine import Engine, StepContext
 from .generate import GenerationError, Row
+
+
+# Stop tokens the device itself ends a row on (all rows of a batch must share them).  A batch with
+# more, or with different ones per row, leaves them to the host, which decides every pick anyway.
+STOP_IDS_ON_DEVICE = 16
+
+
+def device_stop_ids(rows: Sequence[Row]) -> List[int]:
+    """The stop-id list the device gets for a batch: the rows' common stop tokens padded with -1 to
+    `STOP_IDS_ON_DEVICE`, or all -1 when the rows differ or have more than fit."""
+    stops = {tuple(sorted(set(r.params.stop_token_ids))) for r in rows}
+    common = stops.pop() if len(stops) == 1 else ()
+    if len(common) > STOP_IDS_ON_DEVICE:
+        common = ()
+    return list(common) + [-1] * (STOP_IDS_ON_DEVICE - len(common))
 
 
 class DeviceBatch:
@@ -42,21 +64,24 @@ class DeviceBatch:
         self.counter = torch.zeros(max_batch, **i32)
         self.finished = torch.zeros(max_batch, **i32)
         self.budget = torch.zeros(max_batch, **i32)
-        self.out_token = torch.zeros(max_batch, **i32)
+        self.out_token = torch.zeros(max_batch + 1, **i32)      # picks, then the kernels' status word
         self.temperature = torch.zeros(max_batch, dtype=torch.float32, device=dev)
         self.top_p = torch.ones(max_batch, dtype=torch.float32, device=dev)
         self.seed = torch.zeros(max_batch, dtype=torch.int64, device=dev)
         self.seq_first_row = torch.arange(max_batch + 1, **i32)
         self.want_rows = torch.arange(max_batch, **i32)
         self.logits = torch.empty((max_batch, engine.vocab_size), dtype=torch.float32, device=dev)
-        self._out_host = [torch.zeros(max_batch, dtype=torch.int32).pin_memory() for _ in range(2)]
+        self._out_host = [torch.zeros(max_batch + 1, dtype=torch.int32).pin_memory() for _ in range(2)]
         self._out_event = [torch.cuda.Event(), torch.cuda.Event()]
-        self._queued = 0                # steps queued so far in this batch (picks buffer = count % 2)
+        self._queued = 0                # steps queued so far (picks buffer = count % 2)
+        self._batch_first = 0           # value of _queued when the current batch started
+        # (the 32-bit path has no kernel that reports there: it gets a word of its own that stays zero)
+        self.status = ops.gemm_tc_status(dev) if engine.dtype == torch.bfloat16 else torch.zeros(1, **i32)
         self._ahead: Optional[List[int]] = None    # rows of the step that is queued and not read yet
         self.run_ahead = True           # queue the next step before reading the current one's picks
         self._per_row = [self.tokens, self.row_slot, self.row_pos, self.counter, self.finished, self.budget,
                          self.temperature, self.top_p, self.seed]
-        self.stop_ids: Optional[torch.Tensor] = None
+        self.stop_ids = torch.full((STOP_IDS_ON_DEVICE,), -1, **i32)
         self.graphs: Dict[int, torch.cuda.CUDAGraph] = {}
         self.slots: List[int] = []
         self.rows: Sequence[Row] = ()
@@ -96,12 +121,11 @@ class DeviceBatch:
                            [r.params.top_p for r in rows]], dtype=torch.float32).to(eng.device)
         self.temperature[:n] = fl[0]
         self.top_p[:n] = fl[1]
-        stops = {tuple(sorted(r.params.stop_token_ids)) for r in rows}
-        common = stops.pop() if len(stops) == 1 else ()
-        self.stop_ids = torch.tensor(common, dtype=torch.int32, device=eng.device) if common else None
+        self.stop_ids.copy_(torch.tensor(device_stop_ids(rows), dtype=torch.int32), non_blocking=False)
         logits = eng.step(self.slots, [r.prompt for r in rows])
         self._sample(logits, n)
         self._ahead = None
+        self._batch_first = self._queued
         return self._read(self._queue_read(n), n)
 
     def step(self, live: Sequence[int]) -> List[int]:
@@ -135,7 +159,7 @@ class DeviceBatch:
     def _sample(self, logits: torch.Tensor, n: int) -> None:
         ops.sample(logits, n, self.out_token, temperature=self.temperature, top_p=self.top_p, seed=self.seed,
                    draw_counter=self.counter, stop_ids=self.stop_ids, finished=self.finished, budget=self.budget,
-                   next_token=self.tokens, next_pos=self.row_pos)
+                   next_token=self.tokens, next_pos=self.row_pos, status=self.status)
 
     def _queue_step(self, live: List[int]) -> None:
         """Queues one decode step for `live` and the copy of its picks to the host."""
@@ -159,13 +183,22 @@ class DeviceBatch:
     def _queue_read(self, n: int) -> int:
         k = self._queued
         self._queued += 1
-        self._out_host[k % 2][:n].copy_(self.out_token[:n], non_blocking=True)
+        self._out_host[k % 2][:n + 1].copy_(self.out_token[:n + 1], non_blocking=True)
         self._out_event[k % 2].record()
         return k
 
     def _read(self, k: int, n: int) -> List[int]:
+        """The picks of queued step `k` (n rows), once they have arrived.  The int behind them is the
+        status word as it stood when that step's sampler ran; not zero means that a kernel of that
+        step, or of an earlier one not yet reported, gave up a bounded wait, so the picks are not
+        valid: the word is cleared and the step is named."""
         self._out_event[k % 2].synchronize()
-        return self._out_host[k % 2][:n].tolist()
+        got = self._out_host[k % 2][:n + 1].tolist()
+        if got[n] != 0:
+            self.status.zero_()
+            what = "the prompts' step" if k == self._batch_first else f"decode step {k - self._batch_first}"
+            raise ops.KernelError(f"{what} of this batch: {ops.describe_tc_status(got[n])}")
+        return got[:n]
 
     def _compact(self, live: List[int]) -> None:
         where = {row: k for k, row in enumerate(self.live)}
@@ -188,7 +221,7 @@ class DeviceBatch:
         """Captures the launches of one decode step of `n` rows.  The warm-up run before the capture
         would advance the sequences, so their state is saved and restored around it."""
         saved = [t[:n].clone() for t in self._per_row]
-        saved_out = self.out_token[:n].clone()
+        saved_out = self.out_token[:n].clone()      # (the status word behind them is not touched)
         torch.cuda.synchronize()
         before = ops.LAUNCHES
         self._launch(n)            # lets libraries and the workspace finish their lazy set-up
@@ -201,5 +234,6 @@ class DeviceBatch:
             t[:n] = s
         self.out_token[:n] = saved_out
         torch.cuda.synchronize()
+        self.engine.ws.frozen = True      # the graph holds the buffers' addresses
         self.graphs[n] = g
         return g

@@ -218,7 +218,12 @@ class Engine:
         row_slot = np.repeat(np.asarray(slots, dtype=np.int32), lens)
         row_pos = np.concatenate([np.arange(st, st + n, dtype=np.int32) for st, n in zip(starts, lens)])
         first_row = np.concatenate([[0], np.cumsum(lens)]).astype(np.int64)
-        want_flat = np.asarray([first_row[i] + j for i, w in enumerate(want) for j in w], dtype=np.int64)
+        asked = np.asarray([first_row[i] + j for i, w in enumerate(want) for j in w], dtype=np.int64)
+        # A place asked for twice is computed once (two rows of the final norm adding into the same
+        # residual row would race) and its logits row is repeated in the result.
+        want_flat, repeat = np.unique(asked, return_inverse=True)
+        if len(want_flat) == len(asked):
+            want_flat, repeat = asked, None
         order = np.argsort(want_flat, kind="stable")
         n_want = len(want_flat)
         logits = torch.empty((n_want, self.vocab_size), dtype=torch.float32, device=self.device)
@@ -236,6 +241,8 @@ class Engine:
         if self.dtype == torch.bfloat16:
             from ..csrc import ops
             ops.check_tc_status(self.device)
+        if repeat is not None:
+            logits = logits[torch.from_numpy(repeat).to(self.device)]
         return logits
 
     def _run_pass(self, toks, rslot, rpos, want_rows, want_dest, logits, decode, slots, starts, lens, first_row,
@@ -355,6 +362,7 @@ class Engine:
                 finally:
                     graph.capture_end()
             cur.wait_stream(side)
+            self.ws.frozen = True       # the graph holds the buffers' addresses
             entry = (graph, ops.tc_used)
         finally:
             ops.tc_used = was_used

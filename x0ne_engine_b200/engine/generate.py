@@ -96,12 +96,35 @@ def plan_batches(needs: Sequence[int], max_batch: int, capacity_tokens: int, uni
 
 @dataclass
 class GenerationStats:
+    """Sums over the batches served, and the host time at which every step's tokens landed.
+
+    `token_gaps` holds, per decode step, the seconds between the arrival of the step before it
+    (for a batch's first decode step: of the prompts' picks) and its own arrival: the inter-token
+    time a client of any sequence of the batch sees.  The library engine stamps each token the same
+    way (x0ne-core/runtime/src/engine.rs:1106-1116) and reports their percentiles."""
     batches: int = 0
     prefill_tokens: int = 0
     prefill_seconds: float = 0.0
     decode_steps: int = 0
     decode_tokens: int = 0
     decode_seconds: float = 0.0
+    token_gaps: List[float] = field(default_factory=list)
+
+    def gap_percentiles(self, which: Sequence[float] = (50, 90, 99)) -> Optional[dict]:
+        """{"p50": seconds, ...} of `token_gaps` (nearest-rank), or None when no step was decoded."""
+        return percentiles(self.token_gaps, which)
+
+
+def percentiles(values: Sequence[float], which: Sequence[float] = (50, 90, 99)) -> Optional[dict]:
+    if not values:
+        return None
+    s = sorted(values)
+    out = {}
+    for p in which:
+        rank = max(1, -(-len(s) * p // 100))            # nearest rank: ceil(p/100 * n), at least the first
+        out[f"p{p:g}"] = s[min(len(s), int(rank)) - 1]
+    out.update(max=s[-1], n=len(s))
+    return out
 
 
 def run_batch(runner: BatchRunner, rows: List[Row], stats: Optional[GenerationStats] = None,
@@ -116,14 +139,18 @@ def run_batch(runner: BatchRunner, rows: List[Row], stats: Optional[GenerationSt
             stats.batches += 1
             stats.prefill_tokens += sum(len(r.prompt) for r in rows)
             stats.prefill_seconds += t1 - t0
+        last = t1
         while live:
             picks = runner.step(live)
             if stats is not None:
+                now = clock()
                 stats.decode_steps += 1
                 stats.decode_tokens += len(live)
+                stats.token_gaps.append(now - last)
+                last = now
             live = [i for i, p in zip(live, picks) if rows[i].decide(p)]
         if stats is not None:
-            stats.decode_seconds += clock() - t1
+            stats.decode_seconds += last - t1
     finally:
         runner.close()
 

@@ -10,7 +10,10 @@ class Workspace:
     """`buffer(name, shape, dtype)` returns the same tensor for the same name every time.
 
     Parts name their scratch generically ("attn.qkv", "ffn.act", "delta"), so layers of the same
-    kind share it; a name asked for with a larger shape is grown (outside graph capture only).
+    kind share it; a name asked for with a larger shape or another dtype is allocated anew.  Once
+    a CUDA graph has been captured over the workspace (`frozen`), the graph holds the buffers'
+    addresses: new names may still be added, but replacing a buffer that exists raises instead of
+    leaving the graph with a pointer to freed memory.
     """
 
     def __init__(self, max_rows: int, device):
@@ -25,8 +28,9 @@ class Workspace:
         for s in shape:
             n *= s
         if t is None or t.dtype != dtype or t.numel() < n:
-            if self.frozen:
-                raise RuntimeError(f"workspace buffer {name!r} would be reallocated after the workspace was frozen")
+            if self.frozen and t is not None:
+                raise RuntimeError(f"workspace buffer {name!r} ({t.numel()} x {t.dtype}) would be replaced by "
+                                   f"{n} x {dtype} although a captured graph uses it")
             t = torch.empty(n, dtype=dtype, device=self.device)
             self._bufs[name] = t
         return t[:n].view(shape)
@@ -36,8 +40,8 @@ class Workspace:
         needs zeros (arrival counters); grown, and zeroed again, when a larger one is asked for."""
         t = self._bufs.get(name)
         if t is None or t.numel() < nbytes:
-            if self.frozen:
-                raise RuntimeError(f"workspace buffer {name!r} would be reallocated after the workspace was frozen")
+            if self.frozen and t is not None:
+                raise RuntimeError(f"workspace buffer {name!r} would be replaced although a captured graph uses it")
             t = torch.zeros(max(nbytes, 1), dtype=torch.uint8, device=self.device)
             self._bufs[name] = t
         return t
