@@ -131,9 +131,35 @@ def test_registry_detects_by_class_and_by_model_type_and_refuses_disagreement():
 def test_spec_is_data_with_one_entry_per_layer_and_all_sizes_as_parameters():
     spec = tiny_b().to_spec()
     assert len(spec.layers) == 3 and [e.layer for e in spec.run_order] == [0, 1, 2]
-    m = spec.layers[1].mixer
+    m = spec.layers[1].part("mixer")
     assert m.kind == "gqa_attention" and m["q_heads"] == 6 and m["kv_heads"] == 2 and m["head_dim"] == 32
     assert m["qk_norm_eps"] == 1e-5 and m["names"]["q"] == "model.layers.1.self_attn.q_proj.weight"
-    assert spec.layers[2].ffn["intermediate_size"] == 160 and spec.positions["rope"]["theta"] == 1e6
+    assert spec.layers[2].part("ffn")["intermediate_size"] == 160 and spec.positions["rope"]["theta"] == 1e6
     assert spec.head["tied"] is False and spec.head["names"]["weight"] == "lm_head.weight"
     assert tiny_a().to_spec().head["names"]["weight"] == "model.embed_tokens.weight"
+
+
+def test_a_layer_s_roles_are_checked_against_its_arrangement():
+    """A layer names its parts by role; which roles exist is the arrangement's business, and a
+    layer that leaves one out or brings an unknown one is refused before anything is built."""
+    import dataclasses
+    from x0ne_engine_b200.config import ConfigError, LayerSpec
+    from x0ne_engine_b200.engine import tensor_needs_of_spec
+    from x0ne_engine_b200.engine.model import cache_need_of_layer, step_bytes_of_spec
+    spec = tiny_b().to_spec()
+    l0 = spec.layers[0]
+    assert sorted(l0.parts) == ["ffn", "ffn_norm", "mixer", "mixer_norm"] and cache_need_of_layer(l0).kind == "kv"
+    with pytest.raises(ConfigError, match="no part in the role 'router'"):
+        l0.part("router")
+    without_ffn = LayerSpec(l0.block, {k: v for k, v in l0.parts.items() if k != "ffn"})
+    with pytest.raises(ConfigError, match=r"missing: \['ffn'\]"):
+        tensor_needs_of_spec(dataclasses.replace(spec, layers=(without_ffn,) + spec.layers[1:]))
+    extra = l0.with_part("post_norm", l0.part("ffn_norm"))
+    with pytest.raises(ConfigError, match=r"unknown: \['post_norm'\]"):
+        tensor_needs_of_spec(dataclasses.replace(spec, layers=(extra,) + spec.layers[1:]))
+    # bytes a decode step reads and a position holds, from the spec alone
+    c = tiny_b()
+    weights, cache = step_bytes_of_spec(spec, 2)
+    per_layer = (c.linear_params_per_layer) * 2 + (2 * c.hidden_size + 2 * c.head_dim) * 4
+    assert weights == c.num_hidden_layers * per_layer + c.vocab_size * c.hidden_size * 2 + c.hidden_size * 4
+    assert cache == c.kv_bytes_per_position

@@ -155,12 +155,12 @@ def test_a_toy_mixer_with_state_of_its_own_is_registered_built_and_stepped():
         norm = lambda name: PartSpec("rmsnorm", dict(size=h, eps=1e-6, names=dict(weight=name)))   # noqa: E731
         layers = []
         for l in range(2):
-            layers.append(LayerSpec(
-                block="prenorm", mixer_norm=norm(f"l{l}.n1"),
+            layers.append(LayerSpec(block="prenorm", parts=dict(
+                mixer_norm=norm(f"l{l}.n1"),
                 mixer=PartSpec("toy_decay", dict(hidden_size=h, decay=0.5 + 0.2 * l, names=dict(w=f"l{l}.mix"))),
                 ffn_norm=norm(f"l{l}.n2"),
                 ffn=PartSpec("swiglu", dict(hidden_size=h, intermediate_size=48,
-                                            names=dict(gate=f"l{l}.g", up=f"l{l}.u", down=f"l{l}.d")))))
+                                            names=dict(gate=f"l{l}.g", up=f"l{l}.u", down=f"l{l}.d"))))))
         spec = ModelSpec(architecture="ToyForCausalLM", vocab_size=vocab, hidden_size=h, max_position_embeddings=64,
                          embedding=PartSpec("token_embedding", dict(vocab_size=vocab, hidden_size=h, names=dict(weight="emb"))),
                          positions={}, layers=tuple(layers), run_order=(RunEntry(0), RunEntry(1), RunEntry(0)),
@@ -289,7 +289,7 @@ def test_a_model_with_a_windowed_layer_has_two_cache_groups_and_matches_the_plai
                       rms_norm_eps=1e-6, rope_theta=1e4, tie_word_embeddings=True, dtype=dtype)
     spec = cfg.to_spec()
     l1 = spec.layers[1]
-    l1 = dataclasses.replace(l1, mixer=PartSpec(l1.mixer.kind, {**l1.mixer.params, "window": window}))
+    l1 = l1.with_part("mixer", PartSpec(l1.part("mixer").kind, {**l1.part("mixer").params, "window": window}))
     spec = dataclasses.replace(spec, layers=(spec.layers[0], l1))
     tdt = torch.float32 if dtype == "float32" else torch.bfloat16
     init = RandomInit(seed=11, linear_std=0.1, norm_jitter=0.1)
@@ -424,8 +424,9 @@ def test_prenorm_block_alone_with_toy_parts():
         def forward(self, ctx, x, n_rows):
             return (3 * x).clone()
 
-    block = BLOCKS.get("prenorm")(Same(None, None), Twice(None, None), Same(None, None), Thrice(None, None))
-    assert len(block.parts()) == 4
+    block = BLOCKS.get("prenorm")(dict(mixer_norm=Same(None, None), mixer=Twice(None, None), ffn_norm=Same(None, None),
+                                       ffn=Thrice(None, None)))
+    assert len(block.parts()) == 4 and isinstance(block.parts()[1], Twice)
     n, h = 5, 24
     ctx = make_ctx(torch.float32, n, [0] * n, list(range(n)), None)
     x, d = rnd((64, h), 1).to(DEV), rnd((64, h), 2).to(DEV)
@@ -497,7 +498,8 @@ def test_a_toy_feed_forward_with_routing_and_a_toy_position_encoding():
                                                  names=dict(q=f"l{l}.q", k=f"l{l}.k", v=f"l{l}.v", o=f"l{l}.o")))
             ffn = PartSpec("toy_top_one", dict(hidden_size=h, intermediate_size=inter, experts=experts,
                                                names=dict(router=f"l{l}.router", experts=f"l{l}.experts")))
-            layers.append(LayerSpec(block="prenorm", mixer_norm=norm(f"l{l}.n1"), mixer=att, ffn_norm=norm(f"l{l}.n2"), ffn=ffn))
+            layers.append(LayerSpec(block="prenorm", parts=dict(mixer_norm=norm(f"l{l}.n1"), mixer=att,
+                                                                ffn_norm=norm(f"l{l}.n2"), ffn=ffn)))
         spec = ModelSpec(architecture="ToyRoutedForCausalLM", vocab_size=vocab, hidden_size=h, max_position_embeddings=64,
                          embedding=PartSpec("token_embedding", dict(vocab_size=vocab, hidden_size=h, names=dict(weight="emb"))),
                          positions={"learned": PartSpec("toy_learned", dict(positions=64, hidden_size=h, names=dict(table="pos")))},
@@ -547,3 +549,128 @@ def test_a_toy_feed_forward_with_routing_and_a_toy_position_encoding():
     finally:
         FEED_FORWARDS.unregister("toy_top_one")
         POSITIONS.unregister("toy_learned")
+
+
+def test_toy_arrangements_embedding_and_head_are_registered_from_here():
+    """What an architecture may need beyond other mixers and feed-forwards, each defined in this
+    test and registered without a change to the library: an arrangement whose mixer and
+    feed-forward both read one norm's output (three roles), an arrangement without a feed-forward
+    (two roles), an embedding that scales its rows, and a head that soft-caps its logits.  A model
+    of one layer of each arrangement is built from a spec, checked by name like any checkpoint,
+    and stepped whole, token by token and in a batch against float64."""
+    from x0ne_engine_b200 import Engine
+    from x0ne_engine_b200.config import ConfigError, LayerSpec, ModelSpec, PartSpec, RunEntry
+    from x0ne_engine_b200.engine import tensor_needs_of_spec
+    from x0ne_engine_b200.parts import BLOCKS, EMBEDDINGS, HEADS, Block, LMHead, TokenEmbedding
+    from x0ne_engine_b200.weights import RandomInit, make_tensor
+
+    class ParallelBlock(Block):
+        """x += mixer(norm(x)) + ffn(norm(x)): both branches read the same normed rows."""
+        ROLES = {"norm": "norm", "mixer": "mixer", "ffn": "feed_forward"}
+
+        def forward(self, ctx, entry, resid, delta, cache_entry=None, write_cache=True):
+            normed = ctx.ws.buffer("normed", (ctx.ws.max_rows, resid.shape[-1]), ctx.dtype)
+            self.norm.add_norm(ctx, resid, delta, normed, ctx.n_rows)
+            a = self.mixer.forward(ctx, entry, normed, ctx.n_rows, cache_entry=cache_entry, write_cache=write_cache)
+            both = ctx.ws.buffer("toy.both", (ctx.ws.max_rows, resid.shape[-1]), ctx.dtype)
+            both[:ctx.n_rows] = a[:ctx.n_rows]                 # (the mixer and the feed-forward share the "delta" buffer)
+            b = self.ffn.forward(ctx, normed, ctx.n_rows)
+            both[:ctx.n_rows] += b[:ctx.n_rows]
+            return both
+
+    class MixerOnlyBlock(Block):
+        """x += mixer(norm(x)), nothing else."""
+        ROLES = {"norm": "norm", "mixer": "mixer"}
+
+        def forward(self, ctx, entry, resid, delta, cache_entry=None, write_cache=True):
+            normed = ctx.ws.buffer("normed", (ctx.ws.max_rows, resid.shape[-1]), ctx.dtype)
+            self.norm.add_norm(ctx, resid, delta, normed, ctx.n_rows)
+            return self.mixer.forward(ctx, entry, normed, ctx.n_rows, cache_entry=cache_entry, write_cache=write_cache)
+
+    class ScaledEmbedding(TokenEmbedding):
+        def forward(self, ctx, resid, n_rows):
+            super().forward(ctx, resid, n_rows)
+            resid[:n_rows] *= float(self.spec["scale"])
+
+    class CappedHead(LMHead):
+        def forward(self, normed, logits, n_rows):
+            super().forward(normed, logits, n_rows)
+            cap = float(self.spec["cap"])
+            logits[:n_rows] = cap * torch.tanh(logits[:n_rows] / cap)
+            return logits
+
+    BLOCKS.register("toy_parallel", ParallelBlock)
+    BLOCKS.register("toy_mixer_only", MixerOnlyBlock)
+    EMBEDDINGS.register("toy_scaled_embedding", ScaledEmbedding)
+    HEADS.register("toy_capped_head", CappedHead)
+    try:
+        h, vocab, qh, kvh, hd, inter, eps, theta, scale, cap = 48, 70, 3, 1, 16, 80, 1e-5, 1e4, 3.0, 2.0
+        norm = lambda name: PartSpec("rmsnorm", dict(size=h, eps=eps, names=dict(weight=name)))   # noqa: E731
+        att = lambda l: PartSpec("gqa_attention", dict(                                           # noqa: E731
+            hidden_size=h, q_heads=qh, kv_heads=kvh, head_dim=hd, qk_norm_eps=eps, window=None, position="rope", scale=None,
+            names={k: f"l{l}.{k}" for k in ("q", "k", "v", "o", "q_norm", "k_norm")}))
+        ffn = PartSpec("swiglu", dict(hidden_size=h, intermediate_size=inter, names=dict(gate="l0.g", up="l0.u", down="l0.d")))
+        layers = (LayerSpec("toy_parallel", dict(norm=norm("l0.n"), mixer=att(0), ffn=ffn)),
+                  LayerSpec("toy_mixer_only", dict(norm=norm("l1.n"), mixer=att(1))))
+        spec = ModelSpec(architecture="ToyForCausalLM", vocab_size=vocab, hidden_size=h, max_position_embeddings=128,
+                         embedding=PartSpec("toy_scaled_embedding", dict(vocab_size=vocab, hidden_size=h, scale=scale,
+                                                                         names=dict(weight="emb"))),
+                         positions={"rope": PartSpec("rope", dict(head_dim=hd, rotary_dim=hd, theta=theta))},
+                         layers=layers, run_order=(RunEntry(0), RunEntry(1)), final_norm=norm("fn"),
+                         head=PartSpec("toy_capped_head", dict(vocab_size=vocab, hidden_size=h, tied=False, cap=cap,
+                                                               names=dict(weight="head"))))
+        with pytest.raises(ConfigError, match="missing"):
+            tensor_needs_of_spec(dataclasses_replace_layers(spec, (LayerSpec("toy_parallel", dict(norm=norm("l0.n"), mixer=att(0))),)))
+        needs = tensor_needs_of_spec(spec)
+        assert {"l0.g", "l1.q", "head", "emb"} <= {n.name for n in needs} and "l1.g" not in {n.name for n in needs}
+        init = RandomInit(seed=9, linear_std=0.2, norm_jitter=0.1)
+        cpu = {n.name: make_tensor(n, init, torch.float32, "cpu") for n in needs}
+        eng = Engine(spec, {k: v.to(DEV) for k, v in cpu.items()}, "float32", DEV, max_tokens=512)
+        assert not eng.replayable                          # the toy arrangements promise nothing about graphs
+
+        w = {k: v.double().numpy() for k, v in cpu.items()}
+        pc = dict(q_heads=qh, kv_heads=kvh, head_dim=hd, eps=eps, theta=theta)
+
+        def attention_of(x, l, pos):
+            names = {f"a.{k}_proj.weight": w[f"l{l}.{k}"] for k in "qkvo"}
+            names.update({"a.q_norm.weight": w[f"l{l}.q_norm"], "a.k_norm.weight": w[f"l{l}.k_norm"]})
+            return P.attention_block(x, names, "a.", pc, pos)
+
+        def plain(ids):
+            pos = np.arange(len(ids))
+            x = w["emb"][ids] * scale
+            n0 = P.rmsnorm(x, w["l0.n"], eps)
+            x = x + attention_of(n0, 0, pos) + P.swiglu_mlp(n0, {"m.gate_proj.weight": w["l0.g"], "m.up_proj.weight": w["l0.u"],
+                                                                 "m.down_proj.weight": w["l0.d"]}, "m.")
+            x = x + attention_of(P.rmsnorm(x, w["l1.n"], eps), 1, pos)
+            return cap * np.tanh(P.rmsnorm(x, w["fn"], eps) @ w["head"].T / cap)
+
+        a, b = prompts_of(vocab, [40, 9], seed=4)
+        wa, wb = plain(a), plain(b)
+        sa, sb = eng.new_sequence(), eng.new_sequence()
+        got = eng.step([sa, sb], [a[:30], b[:5]], [list(range(30)), [4]]).cpu().numpy()
+        rows_a, rows_b = [got[:30]], [got[30:]]
+        for t in range(4):
+            got = eng.step([sa, sb], [[a[30 + t]], [b[5 + t]]]).cpu().numpy()
+            rows_a.append(got[:1])
+            rows_b.append(got[1:])
+        eng.free_sequence(sb)
+        rows_a.append(eng.step([sa], [a[34:]], [list(range(6))]).cpu().numpy())
+        eng.free_sequence(sa)
+        for got, want, what in ((np.concatenate(rows_a), wa, "long"), (np.concatenate(rows_b), wb[4:], "short")):
+            assert np.abs(got - want).max() / np.abs(want).max() < 1e-4, what
+    finally:
+        BLOCKS.unregister("toy_parallel")
+        BLOCKS.unregister("toy_mixer_only")
+        EMBEDDINGS.unregister("toy_scaled_embedding")
+        HEADS.unregister("toy_capped_head")
+
+
+def dataclasses_replace_layers(spec, layers):
+    import dataclasses
+    return dataclasses.replace(spec, layers=tuple(layers), run_order=tuple(spec.run_order[:len(layers)]))
+
+
+def prompts_of(vocab, lengths, seed):
+    rng = np.random.default_rng(seed)
+    return [rng.integers(0, vocab, n).tolist() for n in lengths]

@@ -4,8 +4,11 @@ Commands and their options follow the reference's own programs where it has them
 
   core-bench <model dir> [--lengths short,1k,4k] [--decode N] [--reps N] [--batch B] [--dtype D]
       [--random-weights SEED]
-      time to first token, prefill and decode rates per prompt length, one line
-      `x0ne-bench-result: <JSON>` (x0ne-core/oracle/examples/core-bench.rs:6-16,420-436).
+      time to first token, prefill and decode rates and the gaps between tokens (p50 / p90 / p99, as
+      x0ne-core/runtime/src/engine.rs:1106-1116 stamps them) per prompt length, one line
+      `x0ne-bench-result: <JSON>` (x0ne-core/oracle/examples/core-bench.rs:6-16,420-436).  Exit code
+      3 when two repetitions of a length gave different tokens
+      (x0ne-core/oracle/examples/core-perf.rs:85-89).
   roofline --config config.json --gpu <GB/s> --prompt P --generated N [--tok-s X] [--batch B]
       places a decode rate against the bandwidth ceiling
       (x0ne-core/runtime/src/bin/x0ne-core-roofline.rs:4-5, x0ne-core/runtime/src/roofline.rs:55-102).
@@ -14,8 +17,11 @@ Commands and their options follow the reference's own programs where it has them
   replay ...            the trace replay program (same as bin/trace_run)
   init <config.json> <out dir> [--seed S] [--linear-std X] [--norm-jitter X]
       writes a model folder with random weights
-  kernel-bench --kernel NAME [sizes]   times one kernel alone with CUDA events
-      (the reference's per-kernel timing entry: x0ne-core/runtime/src/ops.rs:579-681)
+  kernel-bench --kernel NAME [sizes] [--impl ours|reference]   times one kernel alone with CUDA events
+      (the reference's per-kernel timing entry: x0ne-core/runtime/src/ops.rs:579-681).  With
+      `--impl reference` the reference project's own kernel of that name (attention_decode,
+      attention_prefill, add_rmsnorm, qk_norm_rope, swiglu), compiled unchanged from its sources, runs
+      on the same sizes at batch 1, the only batch its kernels take.
 """
 from __future__ import annotations
 
@@ -77,14 +83,15 @@ def cmd_core_bench(a) -> int:
     import torch
     from . import Model
     from .config import config_from_folder
-    from .engine.generate import GenerationStats
+    from .engine.generate import GenerationStats, percentiles
     cfg = config_from_folder(a.model)
+    limit, vocab = cfg.to_spec().max_position_embeddings, cfg.to_spec().vocab_size
     names = [n.strip() for n in a.lengths.split(",")]
     if any(not n for n in names) or a.decode < 2 or a.reps < 1:
         print("usage: core-bench <model directory> [--lengths a,b,...] [--decode N>=2] [--reps N>=1]", file=sys.stderr)
         return 2
-    lens = [_length_tokens(n, cfg.max_position_embeddings - a.decode) for n in names]
-    max_ctx = min(cfg.max_position_embeddings, max(lens) + a.decode)
+    lens = [_length_tokens(n, limit - a.decode) for n in names]
+    max_ctx = min(limit, max(lens) + a.decode)
     t0 = time.time()
     if a.random_weights is not None:      # the folder needs only its config.json
         m = Model.random(cfg, seed=a.random_weights, dtype=a.dtype, max_batch=a.batch, max_ctx=max_ctx)
@@ -94,8 +101,8 @@ def cmd_core_bench(a) -> int:
     load_s = time.time() - t0
     results = []
     for name, n in zip(names, lens):
-        prompts = [synthetic_ids(n, cfg.vocab_size, 0x0C0E5EED + i) for i in range(a.batch)]
-        ttft, prefill, decode, tokens = [], [], [], []
+        prompts = [synthetic_ids(n, vocab, 0x0C0E5EED + i) for i in range(a.batch)]
+        ttft, prefill, decode, tokens, gaps = [], [], [], [], []
         first = None
         # two runs before the timed ones: the first launches a short prompt pass itself, the second
         # captures its launches into a graph, later ones replay it
@@ -108,33 +115,44 @@ def cmd_core_bench(a) -> int:
                 first = rates
             elif rep >= 2:
                 ttft.append(rates[0]); prefill.append(rates[1]); decode.append(rates[2]); tokens.append(out.tokens)
+                gaps += st.token_gaps
         same = all(t == tokens[0] for t in tokens)
-        results.append({"name": name, "tokens": n, "source": "synthetic", "status": "ok", "same_tokens": same,
+        results.append({"name": name, "tokens": n, "source": "synthetic", "status": "ok" if same else "tokens differ",
+                        "same_tokens": same,
                         "first": {"ttft_s": first[0], "prefill_tok_s": first[1], "decode_tok_s": first[2]},
-                        "ttft_s": _stats(ttft), "prefill_tok_s": _stats(prefill), "decode_tok_s": _stats(decode)})
+                        "ttft_s": _stats(ttft), "prefill_tok_s": _stats(prefill), "decode_tok_s": _stats(decode),
+                        "token_gap_s": percentiles(gaps)})
     free, total = torch.cuda.mem_get_info()
+    spec = m.engine.spec
     print("x0ne-bench-result: " + json.dumps({
         "schema": 1, "kind": "core", "model": a.model, "max_ctx": max_ctx, "decode_tokens": a.decode, "reps": a.reps,
         "batch": a.batch, "engine": m.engine.describe(),
-        "config": {"model_type": "qwen3", "layers": cfg.num_hidden_layers, "hidden_size": cfg.hidden_size,
-                   "vocab_size": cfg.vocab_size, "max_position_embeddings": cfg.max_position_embeddings},
+        "config": {"architecture": spec.architecture, "layers": len(spec.run_order), "hidden_size": spec.hidden_size,
+                   "vocab_size": spec.vocab_size, "max_position_embeddings": spec.max_position_embeddings,
+                   "step_weight_bytes": m.engine.model.step_weight_bytes(),
+                   "cache_bytes_per_token": m.engine.cache.bytes_per_token()},
         "load": {"cold_s": load_s}, "memory": {"device_total_bytes": total, "free_after_bytes": free},
         "lengths": results}))
+    if not all(r["same_tokens"] for r in results):
+        # a rate measured while the tokens change from one repetition to the next is no measurement of generation
+        print("core-bench: two repetitions of the same greedy generation gave different tokens", file=sys.stderr)
+        return 3
     return 0
 
 
 def cmd_roofline(a) -> int:
+    """Bytes from the model as data: every run-order entry's tensors once and the head's, and what
+    one position of one sequence holds in the cache; nothing here names an architecture."""
     from .config import config_from_folder
+    from .engine.model import step_bytes_of_spec
     import os
-    cfg = config_from_folder(os.path.dirname(os.path.abspath(a.config)))
-    h = cfg.hidden_size
-    per_layer = cfg.linear_params_per_layer + 2 * h + 2 * cfg.head_dim
-    weights = (cfg.num_hidden_layers * per_layer + h + cfg.vocab_size * h + h) * 2
+    spec = config_from_folder(os.path.dirname(os.path.abspath(a.config))).to_spec()
+    weights, kv_per_position = step_bytes_of_spec(spec, 2)
     ctx = a.prompt + a.generated / 2.0
-    kv = cfg.kv_bytes_per_position * ctx * a.batch
+    kv = kv_per_position * ctx * a.batch
     ceiling = a.gpu * 1e9 / (weights + kv) * a.batch
-    row = {"prompt_tokens": a.prompt, "generated": a.generated, "batch": a.batch, "mean_ctx": ctx,
-           "weight_bytes": weights, "kv_bytes": kv, "bandwidth_gb_s": a.gpu, "ceiling_tok_s": ceiling}
+    row = {"architecture": spec.architecture, "prompt_tokens": a.prompt, "generated": a.generated, "batch": a.batch,
+           "mean_ctx": ctx, "weight_bytes": weights, "kv_bytes": kv, "bandwidth_gb_s": a.gpu, "ceiling_tok_s": ceiling}
     if a.tok_s is not None:
         row.update(tok_s=a.tok_s, share=a.tok_s / ceiling)
     print(json.dumps(row))
@@ -164,7 +182,7 @@ def cmd_kernel_bench(a) -> int:
     dev = "cuda:0"
     torch.manual_seed(0)
 
-    def timed(fn, bytes_per_launch, flops_per_launch=0.0):
+    def timed(fn, bytes_per_launch, flops_per_launch=0.0, n_copies=None):
         """The launches are captured into one CUDA graph, so the time is the device's, not the host's."""
         for _ in range(a.warmup):
             fn()
@@ -181,9 +199,13 @@ def cmd_kernel_bench(a) -> int:
         e.record()
         torch.cuda.synchronize()
         us = s.elapsed_time(e) * 1e3 / a.iters
-        print(json.dumps({"kernel": a.kernel, "m": a.m, "n": a.n, "k": a.k, "batch": a.batch, "context": a.context,
-                          "us": us, "gb_s": bytes_per_launch / us / 1e3, "tflops": flops_per_launch / us / 1e6,
-                          "copies": copies}))
+        print(json.dumps({"kernel": a.kernel, "impl": a.impl, "m": a.m, "n": a.n, "k": a.k, "batch": a.batch,
+                          "context": a.context, "us": us, "gb_s": bytes_per_launch / us / 1e3, "tflops": flops_per_launch / us / 1e6,
+                          "copies": copies if n_copies is None else n_copies}))
+
+    copies = 1
+    if a.impl == "reference":
+        return _kernel_bench_reference(a, timed)
 
     if a.kernel in ("gemm_smallm", "gemm_smallm_swiglu", "gemm_library", "gemm_tc", "gemm_tc_swiglu", "gemm_tc1",
                     "gemm_tc1_swiglu", "gemm_skinny", "gemm_skinny_swiglu"):
@@ -278,6 +300,13 @@ def cmd_kernel_bench(a) -> int:
         copies = 1
         timed(lambda: ops.add_rmsnorm(resid, delta, w, out, rows, 1e-6), rows * h * (4 + 4 + 2 + 2))
         return 0
+    if a.kernel == "swiglu":
+        rows, inter = a.m, a.n
+        gu = torch.randn(rows, 2 * inter, device=dev).bfloat16()
+        out = torch.empty(rows, inter, device=dev, dtype=torch.bfloat16)
+        copies = 1
+        timed(lambda: ops.swiglu(gu, out, rows), rows * inter * 6)
+        return 0
     if a.kernel == "qk_norm_rope":
         # a.m rows of one sequence at positions 0 .. m-1: q/k head norm, rotation from the table, K/V into the pages
         hd, kvh, qh, rows = a.head_dim, a.kv_heads, a.q_heads, a.m
@@ -301,6 +330,77 @@ def cmd_kernel_bench(a) -> int:
         return 0
     print(f"unknown kernel {a.kernel!r}", file=sys.stderr)
     return 2
+
+
+def _kernel_bench_reference(a, timed) -> int:
+    """The reference project's kernel of the asked name at the asked sizes (one sequence), from its
+    unmodified sources; inputs of the same shapes and distributions as this library's case, in the
+    reference's own layouts (contiguous cache [max_ctx][kv_heads][128], bfloat16 norm weights)."""
+    import math
+    import torch
+    from . import reference_kernels as R
+    dev = "cuda:0"
+    try:
+        k = R.load()
+    except R.ReferenceUnavailable as e:
+        print(json.dumps({"impl": "reference", "unavailable": str(e).splitlines()[0]}))
+        return 0
+    hd, kvh, qh = a.head_dim, a.kv_heads, a.q_heads
+    if hd != R.HEAD_DIM:
+        print(json.dumps({"impl": "reference", "unavailable": f"the reference's kernels are written for head size {R.HEAD_DIM}"}))
+        return 0
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    u32 = lambda v: torch.tensor([v], dtype=torch.int32, device=dev)   # noqa: E731
+    bf = lambda *shape: torch.randn(*shape, device=dev).bfloat16()     # noqa: E731
+    if a.kernel == "attention_decode":
+        ctx = a.context
+        kv_bytes = 2 * ctx * kvh * hd * 2
+        copies = max(2, int(math.ceil(256e6 / kv_bytes)) + 1)
+        caches = [(bf(ctx, kvh, hd), bf(ctx, kvh, hd)) for _ in range(copies)]
+        q, out, pos = bf(1, qh * hd), torch.empty(1, qh * hd, device=dev, dtype=torch.bfloat16), u32(ctx - 1)
+        plan = R.split_plan(k, qh, kvh, sms)
+        state = torch.zeros(qh * plan[2] * R.SPLIT_STATE, device=dev)
+        counter = torch.zeros(max(kvh, qh), dtype=torch.int32, device=dev)
+        print(f"reference split plan: kernel {plan[0]}, grid {plan[1]} x {plan[2]}", file=sys.stderr)
+        i = [0]
+
+        def fn():
+            kc, vc = caches[i[0] % copies]
+            i[0] += 1
+            R.attention_decode(k, q, kc, vc, state, counter, out, pos, qh, kvh, ctx, 1 / math.sqrt(hd), plan)
+        timed(fn, kv_bytes, 4.0 * qh * hd * ctx, copies)
+        return 0
+    if a.kernel == "attention_prefill":
+        T = a.context
+        kc, vc, q = bf(T, kvh, hd), bf(T, kvh, hd), bf(T, qh * hd)
+        out, pos0 = torch.empty_like(q), u32(0)
+        timed(lambda: R.attention_prefill(k, q, kc, vc, out, pos0, T, qh, kvh, T, 1 / math.sqrt(hd)),
+              2 * T * qh * hd * 2 + 2 * T * kvh * hd * 2, 4.0 * qh * hd * T * (T + 1) / 2, 1)
+        return 0
+    if a.kernel == "add_rmsnorm":
+        rows, h = a.m, a.n
+        resid, delta, w = torch.randn(rows, h, device=dev), bf(rows, h), torch.ones(h, device=dev).bfloat16()
+        out = torch.empty_like(delta)
+        timed(lambda: R.add_rmsnorm(k, resid, delta, w, out, rows, h, 1e-6), rows * h * (4 + 4 + 2 + 2), 0.0, 1)
+        return 0
+    if a.kernel == "qk_norm_rope":
+        rows = a.m
+        qkv, q_out = bf(rows, (qh + 2 * kvh) * hd), torch.empty(rows, qh * hd, device=dev, dtype=torch.bfloat16)
+        kc, vc = torch.zeros(rows, kvh, hd, device=dev, dtype=torch.bfloat16), torch.zeros(rows, kvh, hd, device=dev, dtype=torch.bfloat16)
+        ones = torch.ones(hd, device=dev).bfloat16()
+        inv_freq = (1e6 ** (-torch.arange(0, hd, 2, device=dev, dtype=torch.float32) / hd)).contiguous()
+        pos0 = u32(0)
+        moved = rows * ((qh + 2 * kvh) * hd * 2 + qh * hd * 2 + 2 * kvh * hd * 2)
+        timed(lambda: R.qk_norm_rope_kv_write(k, qkv, ones, ones, inv_freq, q_out, kc, vc, pos0, rows, qh, kvh, rows, 1e-6),
+              moved, 0.0, 1)
+        return 0
+    if a.kernel == "swiglu":
+        rows, inter = a.m, a.n
+        gu, out = bf(rows, 2 * inter), torch.empty(rows, inter, device=dev, dtype=torch.bfloat16)
+        timed(lambda: R.swiglu(k, gu, out, rows, inter), rows * inter * 6, 0.0, 1)
+        return 0
+    print(json.dumps({"impl": "reference", "unavailable": f"the reference has no kernel for {a.kernel!r}"}))
+    return 0
 
 
 def main(argv=None) -> int:
@@ -354,6 +454,7 @@ def main(argv=None) -> int:
 
     k = sub.add_parser("kernel-bench")
     k.add_argument("--kernel", required=True)
+    k.add_argument("--impl", default="ours", choices=["ours", "reference"])
     k.add_argument("--m", type=int, default=8)
     k.add_argument("--n", type=int, default=4096)
     k.add_argument("--k", type=int, default=4096)

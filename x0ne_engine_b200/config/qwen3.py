@@ -215,14 +215,13 @@ class Qwen3Config:
                 hidden_size=h, intermediate_size=self.intermediate_size,
                 names=dict(gate=f"{p}.mlp.gate_proj.weight", up=f"{p}.mlp.up_proj.weight",
                            down=f"{p}.mlp.down_proj.weight")))
-            layers.append(LayerSpec(
-                block="prenorm",
+            layers.append(LayerSpec(block="prenorm", parts=dict(
                 mixer_norm=PartSpec("rmsnorm", dict(size=h, eps=eps,
                                                     names=dict(weight=f"{p}.input_layernorm.weight"))),
                 mixer=attn,
                 ffn_norm=PartSpec("rmsnorm", dict(size=h, eps=eps,
                                                   names=dict(weight=f"{p}.post_attention_layernorm.weight"))),
-                ffn=mlp))
+                ffn=mlp)))
         spec = ModelSpec(
             architecture=ARCHITECTURE,
             vocab_size=self.vocab_size,

@@ -35,16 +35,27 @@ class PartSpec:
 
 @dataclass(frozen=True)
 class LayerSpec:
-    """A layer: how its parts are arranged (`block`) and the parts themselves.
+    """A layer: how its parts are arranged (`block`, a registered arrangement) and the parts
+    themselves by role.
 
-    A layer may mix tokens with any registered mixer and transform them with any registered
-    feed-forward; two layers of one model need not use the same kinds.
+    Which roles exist, which are required and what kind of part fills each (a norm, a mixer, a
+    feed-forward) is the arrangement's business: the pre-norm block takes `mixer_norm`, `mixer`,
+    `ffn_norm` and `ffn`; an arrangement with four norms, with both branches in parallel or
+    without a feed-forward names its own.  Two layers of one model need not use the same
+    arrangement, mixer or feed-forward.
     """
     block: str
-    mixer_norm: PartSpec
-    mixer: PartSpec
-    ffn_norm: PartSpec
-    ffn: PartSpec
+    parts: Mapping[str, PartSpec] = field(default_factory=dict)
+
+    def part(self, role: str) -> PartSpec:
+        try:
+            return self.parts[role]
+        except KeyError:
+            raise ConfigError(f"a {self.block!r} layer has no part in the role {role!r}; it has {sorted(self.parts)}") from None
+
+    def with_part(self, role: str, spec: PartSpec) -> "LayerSpec":
+        """A copy of this layer with one role filled anew."""
+        return LayerSpec(self.block, {**self.parts, role: spec})
 
 
 @dataclass(frozen=True)

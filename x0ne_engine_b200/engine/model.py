@@ -7,8 +7,8 @@ from typing import Dict, List, Mapping, Optional
 import torch
 
 from ..config.spec import ModelSpec
+from ..config.spec import ConfigError, LayerSpec
 from ..parts import base as P
-from ..parts.embedding import LMHead, TokenEmbedding
 from ..weights.loader import TensorNeed
 
 
@@ -23,27 +23,69 @@ def _unique(needs: List[TensorNeed]) -> List[TensorNeed]:
     return list(seen.values())
 
 
+def layer_part_classes(layer: LayerSpec):
+    """(role, part class, part spec) of a layer in the order its arrangement runs them; checks the
+    layer's roles against the arrangement's."""
+    block = P.BLOCKS.get(layer.block)
+    try:
+        block.check_roles(list(layer.parts))
+    except ValueError as e:
+        raise ConfigError(str(e)) from None
+    return [(role, P.PART_REGISTRIES[kind].get(layer.parts[role].kind), layer.parts[role])
+            for role, kind in block.ROLES.items() if role in layer.parts]
+
+
 def tensor_needs_of_spec(spec: ModelSpec) -> List[TensorNeed]:
     """Every checkpoint tensor the model reads, by name, in model order (no device needed)."""
-    needs: List[TensorNeed] = list(TokenEmbedding.tensor_needs(spec.embedding))
+    needs: List[TensorNeed] = list(P.EMBEDDINGS.get(spec.embedding.kind).tensor_needs(spec.embedding))
     for ps in spec.positions.values():
         needs += P.POSITIONS.get(ps.kind).tensor_needs(ps)
     for layer in spec.layers:
-        needs += P.NORMS.get(layer.mixer_norm.kind).tensor_needs(layer.mixer_norm)
-        needs += P.MIXERS.get(layer.mixer.kind).tensor_needs(layer.mixer)
-        needs += P.NORMS.get(layer.ffn_norm.kind).tensor_needs(layer.ffn_norm)
-        needs += P.FEED_FORWARDS.get(layer.ffn.kind).tensor_needs(layer.ffn)
+        for _, cls, ps in layer_part_classes(layer):
+            needs += cls.tensor_needs(ps)
     needs += P.NORMS.get(spec.final_norm.kind).tensor_needs(spec.final_norm)
-    needs += LMHead.tensor_needs(spec.head)
+    needs += P.HEADS.get(spec.head.kind).tensor_needs(spec.head)
     return _unique(needs)
 
 
 def optional_duplicates_of_spec(spec: ModelSpec) -> Dict[str, str]:
     """Tensors a checkpoint may carry although the model does not read them, each with the
-    tensor it must equal: the head of a tied model."""
-    if spec.head.get("tied"):
-        return {"lm_head.weight": spec.head["names"]["weight"]}
-    return {}
+    tensor it must equal (the head of a tied model): what the head's class says."""
+    return dict(P.HEADS.get(spec.head.kind).optional_duplicates(spec.head))
+
+
+def cache_need_of_layer(layer: LayerSpec) -> P.CacheNeed:
+    """What a run-order entry of this layer keeps per sequence: its mixer's need.  A layer without
+    a mixer keeps nothing; a layer may hold one mixer that keeps something."""
+    needs = [cls.cache_need(ps) for _, cls, ps in layer_part_classes(layer) if issubclass(cls, P.Mixer)]
+    needs = [n for n in needs if n.kind != "none"]
+    if len(needs) > 1:
+        raise ConfigError("a layer with two mixers that both keep something per sequence is not served: "
+                          "give each a layer of its own")
+    return needs[0] if needs else P.CacheNeed()
+
+
+def step_bytes_of_spec(spec: ModelSpec, dtype_bytes: int = 2):
+    """(bytes of weights a decode step reads, bytes of cache one position of one sequence holds),
+    from the spec alone: every run-order entry's tensors once and the head's, matrices in the
+    run's dtype and vectors in float32; the embedding table is read one row per token, so it only
+    counts where the head reads it whole (a tied model)."""
+    def nbytes(need: TensorNeed) -> int:
+        n = 1
+        for s in need.shape:
+            n *= s
+        return n * (4 if need.role in ("vector", "table") else dtype_bytes)
+
+    weights = sum(nbytes(n) for n in P.HEADS.get(spec.head.kind).tensor_needs(spec.head))
+    weights += sum(nbytes(n) for n in P.NORMS.get(spec.final_norm.kind).tensor_needs(spec.final_norm))
+    cache = 0
+    for e in spec.run_order:
+        layer = spec.layers[e.layer]
+        weights += sum(nbytes(n) for _, cls, ps in layer_part_classes(layer) for n in cls.tensor_needs(ps))
+        need = cache_need_of_layer(layer)
+        if need.kind == "kv" and e.reads_cache_of is None:
+            cache += 2 * need.kv_heads * need.head_dim * dtype_bytes
+    return weights, cache
 
 
 class CausalLM:
@@ -56,16 +98,12 @@ class CausalLM:
         for name, ps in spec.positions.items():
             env.positions[name] = P.POSITIONS.get(ps.kind)(ps, env)
         self.env = env
-        self.embedding = TokenEmbedding(spec.embedding, env)
+        self.embedding = P.EMBEDDINGS.get(spec.embedding.kind)(spec.embedding, env)
         self.blocks: List[P.Block] = []
         for layer in spec.layers:
-            self.blocks.append(P.BLOCKS.get(layer.block)(
-                P.NORMS.get(layer.mixer_norm.kind)(layer.mixer_norm, env),
-                P.MIXERS.get(layer.mixer.kind)(layer.mixer, env),
-                P.NORMS.get(layer.ffn_norm.kind)(layer.ffn_norm, env),
-                P.FEED_FORWARDS.get(layer.ffn.kind)(layer.ffn, env)))
+            self.blocks.append(P.BLOCKS.get(layer.block)({role: cls(ps, env) for role, cls, ps in layer_part_classes(layer)}))
         self.final_norm = P.NORMS.get(spec.final_norm.kind)(spec.final_norm, env)
-        self.head = LMHead(spec.head, env)
+        self.head = P.HEADS.get(spec.head.kind)(spec.head, env)
 
     def parts(self) -> List[P.Part]:
         out: List[P.Part] = [self.embedding] + list(self.env.positions.values())
@@ -80,8 +118,7 @@ class CausalLM:
 
     def cache_needs(self) -> List[P.CacheNeed]:
         """One CacheNeed per run-order entry."""
-        return [P.MIXERS.get(self.spec.layers[e.layer].mixer.kind).cache_need(self.spec.layers[e.layer].mixer)
-                for e in self.spec.run_order]
+        return [cache_need_of_layer(self.spec.layers[e.layer]) for e in self.spec.run_order]
 
     def bind(self, tensors: Mapping[str, torch.Tensor]) -> None:
         for part in self.parts():

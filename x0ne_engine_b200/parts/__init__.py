@@ -1,6 +1,6 @@
 """The parts layers are made of, and their registries."""
-from .base import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITIONS, Block, BuildEnv, CacheNeed, FeedForward,
-                   Mixer, Norm, Part, PositionEncoding, Registry)
+from .base import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, PART_REGISTRIES, POSITIONS, Block, BuildEnv,
+                   CacheNeed, Embedding, FeedForward, Head, Mixer, Norm, Part, PositionEncoding, Registry)
 from .linear import Linear
 from . import attention, block, embedding, mlp, norm, rope  # noqa: F401  (registers the built-in parts)
 from .attention import GQAttention
@@ -10,6 +10,7 @@ from .mlp import SwiGLU
 from .norm import RMSNorm
 from .rope import NoPosition, Rope, inv_freq_f32
 
-__all__ = ["BLOCKS", "FEED_FORWARDS", "MIXERS", "NORMS", "POSITIONS", "Block", "BuildEnv", "CacheNeed",
-           "FeedForward", "Mixer", "Norm", "Part", "PositionEncoding", "Registry", "Linear", "GQAttention",
+__all__ = ["BLOCKS", "EMBEDDINGS", "FEED_FORWARDS", "HEADS", "MIXERS", "NORMS", "PART_REGISTRIES", "POSITIONS", "Block",
+           "BuildEnv", "CacheNeed", "Embedding", "FeedForward", "Head", "Mixer", "Norm", "Part", "PositionEncoding",
+           "Registry", "Linear", "GQAttention",
            "PreNormBlock", "LMHead", "TokenEmbedding", "SwiGLU", "RMSNorm", "NoPosition", "Rope", "inv_freq_f32"]

@@ -14,8 +14,12 @@ sees the model's name or its config.json.  The kinds:
   * `PositionEncoding` — `rotary()` gives (inv_freq float32 [rotary_dim/2], rotary_dim) for
                      mixers that rotate q and k, or None; `on_embedding(ctx, resid, n_rows)` lets
                      an additive encoding change the residual after the token embedding.
-  * `Block`        — how a layer's norms, mixer and feed-forward are arranged around the
-                     residual: `forward(ctx, entry, resid, delta)` returns the pending delta.
+  * `Block`        — how a layer's parts are arranged around the residual.  The class names its
+                     roles and the kind of part each takes (`ROLES`, `OPTIONAL`); the engine builds
+                     the layer's parts by role and hands them over; `forward(ctx, entry, resid,
+                     delta)` returns the pending delta.
+  * `Embedding`    — `forward(ctx, resid, n_rows)` fills the float32 residual from the token ids.
+  * `Head`         — `forward(normed, logits, n_rows)` writes float32 logits of the normed rows.
 
 To add a part: subclass the kind, implement `tensor_needs(spec)` (static: the checkpoint
 tensors, by name, with shapes) and `bind(tensors)`, and call the kind's `register`.  A part that
@@ -109,15 +113,50 @@ class PositionEncoding(Part):
         return None
 
 
-class Block:
-    """Arrangement of one layer's parts; built by the engine from a LayerSpec."""
-    replayable = False      # as for Part
+class Embedding(Part):
+    def forward(self, ctx, resid: torch.Tensor, n_rows: int) -> None:
+        raise NotImplementedError
 
-    def __init__(self, mixer_norm: Norm, mixer: Mixer, ffn_norm: Norm, ffn: FeedForward):
-        self.mixer_norm, self.mixer, self.ffn_norm, self.ffn = mixer_norm, mixer, ffn_norm, ffn
+
+class Head(Part):
+    @staticmethod
+    def optional_duplicates(spec: PartSpec) -> Dict[str, str]:
+        """Tensors a checkpoint may carry although the head does not read them, each with the name
+        of the needed tensor it must equal (a tied model that also stores its head)."""
+        return {}
+
+    def forward(self, normed: torch.Tensor, logits: torch.Tensor, n_rows: int) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class Block:
+    """Arrangement of one layer's parts.  A subclass names the roles it takes and the kind of part
+    in each (`ROLES`: role -> "norm" | "mixer" | "feed_forward", in the order the parts run) and
+    which of them a layer may leave out (`OPTIONAL`); the engine builds the parts of a LayerSpec by
+    these and passes them by role."""
+    replayable = False      # as for Part
+    ROLES: Dict[str, str] = {}
+    OPTIONAL: Tuple[str, ...] = ()
+
+    def __init__(self, parts: Mapping[str, Part]):
+        self.by_role: Dict[str, Part] = dict(parts)
+        for role, part in self.by_role.items():
+            setattr(self, role, part)
+        for role in self.OPTIONAL:
+            if role not in self.by_role:
+                setattr(self, role, None)
+
+    @classmethod
+    def check_roles(cls, given) -> None:
+        """Raises ValueError unless `given` (role names) fits this arrangement."""
+        unknown = [r for r in given if r not in cls.ROLES]
+        missing = [r for r in cls.ROLES if r not in given and r not in cls.OPTIONAL]
+        if unknown or missing:
+            raise ValueError(f"a {cls.__name__} layer takes the roles {list(cls.ROLES)}"
+                             + (f"; unknown: {unknown}" if unknown else "") + (f"; missing: {missing}" if missing else ""))
 
     def parts(self) -> List[Part]:
-        return [self.mixer_norm, self.mixer, self.ffn_norm, self.ffn]
+        return [self.by_role[r] for r in self.ROLES if r in self.by_role]
 
     def forward(self, ctx, entry: int, resid, delta, cache_entry=None, write_cache=True):
         raise NotImplementedError
@@ -151,3 +190,7 @@ MIXERS = Registry("mixer")
 FEED_FORWARDS = Registry("feed-forward")
 POSITIONS = Registry("position encoding")
 BLOCKS = Registry("block")
+EMBEDDINGS = Registry("embedding")
+HEADS = Registry("head")
+# the registry behind each kind of part a block's role may name
+PART_REGISTRIES = {"norm": NORMS, "mixer": MIXERS, "feed_forward": FEED_FORWARDS}

@@ -9,6 +9,7 @@ class PreNormBlock(Block):
     into the norm that follows it, so a block takes the previous block's pending delta and
     returns its own (x0ne-core/runtime/src/engine.rs:749,781,823)."""
     replayable = True
+    ROLES = {"mixer_norm": "norm", "mixer": "mixer", "ffn_norm": "norm", "ffn": "feed_forward"}
 
     def forward(self, ctx, entry, resid, delta, cache_entry=None, write_cache=True):
         normed = ctx.ws.buffer("normed", (ctx.ws.max_rows, resid.shape[-1]), ctx.dtype)

@@ -8,11 +8,11 @@ import torch
 from ..config.spec import PartSpec
 from ..csrc import ops
 from ..weights.loader import TensorNeed
-from .base import Part
+from .base import EMBEDDINGS, HEADS, Embedding, Head
 from .linear import Linear
 
 
-class TokenEmbedding(Part):
+class TokenEmbedding(Embedding):
     """resid[r] = float32(table[token[r]]); an id outside the table gives a zero row
     (x0ne-core/kernels/cuda/embedding.cu:5-17).  Parameters: vocab_size, hidden_size,
     names.weight."""
@@ -34,7 +34,7 @@ class TokenEmbedding(Part):
         ops.embedding(self.table, ctx.tokens, resid, n_rows)
 
 
-class LMHead(Part):
+class LMHead(Head):
     """logits = normed W^T in float32 for the wanted rows only; W is the embedding table when the
     model is tied (x0ne-core/runtime/src/engine.rs:823-835).  Parameters: vocab_size,
     hidden_size, tied, names.weight."""
@@ -52,8 +52,17 @@ class LMHead(Part):
     def bind(self, tensors: Mapping[str, torch.Tensor]) -> None:
         self.linear = Linear(tensors[self.spec["names"]["weight"]])
 
+    @staticmethod
+    def optional_duplicates(spec: PartSpec):
+        # a tied checkpoint may also store lm_head.weight, equal to the table (x0ne-core/runtime/src/weights.rs:154-159)
+        return {"lm_head.weight": spec["names"]["weight"]} if spec.get("tied") else {}
+
     def weight_bytes(self) -> int:
         return self.linear.weight_bytes()
 
     def forward(self, normed, logits, n_rows):
         return self.linear(normed, logits, n_rows)
+
+
+EMBEDDINGS.register("token_embedding", TokenEmbedding)
+HEADS.register("lm_head", LMHead)
