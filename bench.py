@@ -10,7 +10,7 @@ up to 2,048 generated tokens: mean 3,072), so the prompt fed before them has 3,0
 with K = 2,047 that is the benchmark's own run.  `value` is decoded tokens a second (batch * K /
 time); `e2e` is the same rate through `Model.generate` with host token lists in and out;
 `prefill` is one 2,048-token prompt through the step function; `points` has decode at batch 1
-and 64 and the milliseconds a 128-token prompt takes through the step function; `roofline` places the decode step against the bytes it must read.  One JSON line is
+and 64 and the milliseconds a 128-token and a 512-token prompt take through the step function; `roofline` places the decode step against the bytes it must read.  One JSON line is
 printed.  This library runs on one GPU: for --gpus above 1 a line says so and the exit code is 2.
 """
 from __future__ import annotations
@@ -257,6 +257,7 @@ def main() -> int:
             print(f"[bench] decode b{b}: {r['tok_s']:.0f} tok/s, {r['ms'] / k:.3f} ms/step", file=sys.stderr, flush=True)
         # a short prompt through the step function (its launches come from a graph after the second pass)
         points["prompt_t128_ms"] = time_prompt(128)
+        points["prompt_t512_ms"] = time_prompt(512)
 
     # ---- end to end through the Python entry point: host token lists in, host token lists out
     e2e = None

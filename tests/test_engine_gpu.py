@@ -464,6 +464,46 @@ def test_layers_of_the_large_shape_against_the_plain_implementation(dtype):
         eng.free_sequence(sl)
 
 
+def test_all_36_layers_of_the_large_shape_in_32_bit_against_the_plain_implementation():
+    """The whole depth of the 8B shape (36 layers of width 4096, 32 q heads over 8 kv heads of 128,
+    feed-forward 12288; only the vocabulary is cut, to 5,000, so that the logits stay small) on the
+    true 32-bit path: a 16-token prompt with logits at its first and last place, then two tokens one
+    by one, against the plain float64 implementation on the same values: within 1e-4 of each row's
+    largest logit, and the same greedy token.  An error that grows with depth (a residual that is
+    rounded, a norm that drifts) shows here and not in two layers.  The plain run takes its weights
+    one tensor at a time from the same generator, so the host never holds the model."""
+    import plain_impl as P
+    from x0ne_engine_b200 import Engine, Qwen3Config
+    from x0ne_engine_b200.engine import tensor_needs_of_spec
+    from x0ne_engine_b200.weights import RandomInit, make_tensor
+    layers, vocab = 36, 5000
+    cfg = Qwen3Config(hidden_size=4096, intermediate_size=12288, num_hidden_layers=layers, num_attention_heads=32,
+                      num_key_value_heads=8, head_dim=128, vocab_size=vocab, max_position_embeddings=4096,
+                      rms_norm_eps=1e-6, rope_theta=1000000.0, tie_word_embeddings=False, dtype="float32")
+    init = RandomInit(7, 0.02, 0.1)
+    eng = Engine.random(cfg, seed=7, dtype="float32", device="cuda:0", linear_std=0.02, norm_jitter=0.1, max_tokens=64)
+    ids = prompts_for(vocab, [18], seed=24)[0]
+    s = eng.new_sequence()
+    got = [eng.step([s], [ids[:16]], [[0, 15]]).cpu().numpy()]
+    got += [eng.step([s], [[t]]).cpu().numpy() for t in ids[16:]]
+    eng.free_sequence(s)
+    got = np.concatenate(got)
+    del eng
+    torch.cuda.empty_cache()
+
+    needs = {n.name: n for n in tensor_needs_of_spec(cfg.to_spec())}
+
+    class OneAtATime(dict):
+        def __getitem__(self, name):
+            return make_tensor(needs[name], init, torch.float32, "cuda:0").cpu().numpy()
+
+    pc = dict(hidden=4096, inter=12288, layers=layers, q_heads=32, kv_heads=8, head_dim=128, vocab=vocab, eps=1e-6, theta=1e6,
+              tied=False, max_pos=4096)
+    want = P.forward(pc, OneAtATime(), ids)[[0, 15, 16, 17]]
+    assert_close_f32(got, want, "36 layers in 32-bit")
+    assert [int(np.argmax(r)) for r in got] == [int(np.argmax(r)) for r in want]
+
+
 ODD_CONFIGS = [
     # hidden, inter, layers, q heads, kv heads, head_dim, vocab, eps, theta, tied
     (100, 172, 2, 6, 3, 80, 257, 1e-6, 1e4, True),        # width no multiple of 8: the products go to the library

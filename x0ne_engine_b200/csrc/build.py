@@ -32,7 +32,7 @@ NVCC_FLAGS += shlex.split(os.environ.get("X0NE_NVCC_FLAGS", ""))
 
 # module name -> sources.  `core` is all a 32-bit run needs; `fast` holds the bfloat16 kernels.
 MODULES: Dict[str, List[str]] = {
-    "core": ["elementwise.cu", "attention_generic.cu", "gemm_f32.cu", "sampling.cu"],
+    "core": ["elementwise.cu", "attention_generic.cu", "gemm_f32.cu", "sampling.cu", "step_plan.cu"],
     "fast": ["attention_bf16.cu", "gemm_bf16.cu", "fast_common.cu"],
     "noalloc": ["attention_decode_noalloc.cu"],
     "tc": ["gemm_tcgen05.cu", "gemm_skinny_tcgen05.cu", "attention_tcgen05.cu", "fast_common.cu"],
@@ -129,9 +129,10 @@ def build(name: str, verbose: bool = True) -> str:
     if r.returncode != 0:
         raise BuildError(f"link of module '{name}' failed:\n{r.stdout}\n{r.stderr}")
     os.replace(tmp, out)
-    # libraries of older versions of this module's sources are of no use any more
+    # libraries of older versions of this module's sources are of no use any more (X0NE_KEEP_BUILDS=1
+    # keeps them: several sets of experiment flags built side by side)
     prefix = f"libx0ne_{name}-"
-    for f in os.listdir(bdir):
+    for f in ([] if os.environ.get("X0NE_KEEP_BUILDS") == "1" else os.listdir(bdir)):
         if f.startswith(prefix) and f.endswith(".so") and os.path.join(bdir, f) != out:
             try:
                 os.remove(os.path.join(bdir, f))

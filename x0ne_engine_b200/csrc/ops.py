@@ -66,6 +66,7 @@ _SIGNATURES = {
     "x0ne_gemm_bf16_tcgen05": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _P],
     "x0ne_gemm_bf16_skinny_tcgen05": [_P, _P, _I, _P, _I, _I, _I, _I, _I, _P, _P],
     "x0ne_sample": ["io", _I, _P],
+    "x0ne_plan_pass": [_I, _P, _P, _P, _P, _L, _L, _P, _I, _I, _I, _P, _L, _P],
 }
 
 
@@ -120,6 +121,24 @@ def _need(t: torch.Tensor, dtype, what: str) -> None:
         raise KernelError(f"{what} is {t.dtype}, the kernel needs {dtype}")
     if not t.is_contiguous():
         raise KernelError(f"{what} is not contiguous")
+
+
+def plan_pass(slots, starts, first_row, tokens, r0: int, r1: int, want_sorted, tile_rows: int, launch_rows: int,
+              stage: torch.Tensor):
+    """Fills the pinned staging table `stage` (int32 [9][stride]) for rows [r0, r1) of a step (native
+    host code, step_plan.cu).  `slots`, `starts` (int32 per sequence), `first_row` (int64, one more
+    than sequences), `tokens` (int32, all rows of the step) and `want_sorted` (int64) are contiguous
+    NumPy arrays.  Returns (sequences in the pass, tiles, most rows of one sequence, one more than the
+    largest position, lo, hi) with want_sorted[lo:hi] the wanted rows of the pass."""
+    lib = _lib("core")
+    out = (c_int32 * 6)()
+    code = lib.x0ne_plan_pass(len(slots), slots.ctypes.data, starts.ctypes.data, first_row.ctypes.data,
+                              tokens.ctypes.data, r0, r1, want_sorted.ctypes.data, len(want_sorted), tile_rows,
+                              launch_rows, stage.data_ptr(), stage.stride(0), ctypes.addressof(out))
+    if code != 0:
+        msg = lib.x0ne_last_error()
+        raise KernelError(f"plan_pass: {msg.decode() if msg else 'error'} (code {code})")
+    return tuple(out)
 
 
 def embedding(table: torch.Tensor, tokens: torch.Tensor, resid: torch.Tensor, n_rows: int) -> None:
@@ -362,8 +381,7 @@ def attention_decode_bf16(q: torch.Tensor, out: torch.Tensor, cache: PagedCacheA
 # ---------------------------------------------------------------------------------------------
 # bfloat16 small-M weight-streaming product (module `fast`)
 # ---------------------------------------------------------------------------------------------
-SMALL_M_LIMIT = 8           # rows up to which the weight-streaming kernel beats the library product
-SMALL_M_LIMIT_FUSED = 16    # with the SwiGLU epilogue it also saves a kernel and a round trip of gate and up
+SMALL_M_MAX_ROWS = 32       # rows the weight-streaming kernel takes (which products use it: routes.py)
 _sm_count = {}
 
 
@@ -376,8 +394,8 @@ def _sms(device) -> int:
 
 
 def gemm_smallm_takes(w: torch.Tensor, m: int, swiglu: bool = False) -> bool:
-    limit = SMALL_M_LIMIT_FUSED if swiglu else SMALL_M_LIMIT
-    return w.dtype == torch.bfloat16 and 0 < m <= limit and w.shape[1] % 8 == 0
+    """Whether the weight-streaming kernel takes this shape."""
+    return w.dtype == torch.bfloat16 and 0 < m <= SMALL_M_MAX_ROWS and w.shape[1] % 8 == 0 and not (swiglu and w.shape[0] % 2)
 
 
 def gemm_bf16_smallm(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, m: int, swiglu: bool = False) -> None:
@@ -405,12 +423,12 @@ def gemm_bf16_smallm(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, m: int, 
 # bfloat16 product on tcgen05 tensor cores with TMA operands (module `tc`), for passes with many rows
 # ---------------------------------------------------------------------------------------------
 _tc_status = {}
-TC_MIN_ROWS = 768        # from about this many rows the fused tcgen05 gate/up product beats the library product + SwiGLU
 tc_used = False          # set when a tcgen05 product was launched since the last check_tc_status()
 
 
 def gemm_tc_takes(w: torch.Tensor, m: int) -> bool:
-    return w.dtype == torch.bfloat16 and m >= TC_MIN_ROWS and w.shape[1] % 8 == 0
+    """Whether the tcgen05 product for many rows takes this shape (from which row count it is used: routes.py)."""
+    return w.dtype == torch.bfloat16 and m >= 1 and w.shape[1] % 8 == 0
 
 
 def check_tc_status(device) -> None:
@@ -478,13 +496,14 @@ def gemm_skinny_tc_takes(w: torch.Tensor, m: int) -> bool:
     return w.dtype == torch.bfloat16 and SKINNY_MIN_ROWS <= m <= SKINNY_MAX_ROWS and w.shape[1] % 8 == 0
 
 
-def gemm_skinny_tc_wins(w: torch.Tensor, m: int, swiglu: bool = False) -> bool:
-    """Where the engine uses it: always with the SwiGLU epilogue (it saves a kernel and the round
-    trip of gate and up), for long rows (K at least twice N, the down projection: every block then
-    streams long enough to pay for the cluster's merge), and up to 16 rows for every matrix;
-    measured at 16 and 64 rows: at 64 the library product is faster on the squarer matrices."""
-    big = w.numel() >= (1 << 20)      # below about 2 MB a product is launch latency whatever runs it
-    return gemm_skinny_tc_takes(w, m) and big and (swiglu or m <= 16 or w.shape[1] >= 2 * w.shape[0])
+def product_kernel(w: torch.Tensor, m: int, fused: bool = False) -> str:
+    """The kernel the routing table names for m rows against w, or "library" where that kernel does not
+    take the shape (a width that is no multiple of 8)."""
+    from . import routes
+    kernel = routes.kernel_for(m, w.shape[0], w.shape[1], fused=fused, sms=_sms(w.device))
+    can = {"smallm": gemm_smallm_takes(w, m, fused), "skinny": gemm_skinny_tc_takes(w, m), "tc_pair": gemm_tc_takes(w, m),
+           "library": True}[kernel]
+    return kernel if can else "library"
 
 
 def gemm_bf16_skinny_tcgen05(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, m: int, swiglu: bool = False) -> None:

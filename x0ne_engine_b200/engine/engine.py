@@ -103,12 +103,14 @@ class Engine:
         self.max_step_tokens = int(max_step_tokens or min(8192, max(PAGE_SIZE, max_tokens)))
         self.ws = Workspace(self.max_step_tokens, self.device)
         self.ws.max_want = self.max_step_tokens
-        # pass metadata: tokens, slots, positions, wanted rows; a small ring of pinned staging buffers
-        self._meta_dev = torch.zeros((6, self.max_step_tokens), dtype=torch.int32, device=self.device)
-        self._stage = [torch.zeros((6, self.max_step_tokens), dtype=torch.int32).pin_memory() for _ in range(4)]
+        # pass tables (per row: token, slot, position; wanted rows; tiles; per sequence: first row, slot,
+        # position), filled by native host code into a small ring of pinned staging buffers and brought
+        # to the device with one copy per pass
+        width = self.max_step_tokens + 1
+        self._meta_dev = torch.zeros((9, width), dtype=torch.int32, device=self.device)
+        self._stage = [torch.zeros((9, width), dtype=torch.int32).pin_memory() for _ in range(4)]
         self._stage_events: List[Optional[torch.cuda.Event]] = [None] * len(self._stage)
         self._stage_at = 0
-        self._seq_dev = torch.zeros((3, self.max_step_tokens + 1), dtype=torch.int32, device=self.device)
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
         # short bfloat16 prompt passes: padded to a few row counts, their launches kept as graphs
         self.replayable = self.model.replayable()
@@ -215,8 +217,6 @@ class Engine:
             raise StepError(f"the cache has no room for this step: {e}") from None
 
         total = int(flat.shape[0])
-        row_slot = np.repeat(np.asarray(slots, dtype=np.int32), lens)
-        row_pos = np.concatenate([np.arange(st, st + n, dtype=np.int32) for st, n in zip(starts, lens)])
         first_row = np.concatenate([[0], np.cumsum(lens)]).astype(np.int64)
         asked = np.asarray([first_row[i] + j for i, w in enumerate(want) for j in w], dtype=np.int64)
         # A place asked for twice is computed once (two rows of the final norm adding into the same
@@ -230,12 +230,10 @@ class Engine:
 
         decode = max(lens) == 1
         chunk = min(self.max_step_tokens, self.cache.max_chunk)
-        sorted_want = want_flat[order]
+        step = dict(slots=np.asarray(slots, dtype=np.int32), starts=np.asarray(starts, dtype=np.int32), first_row=first_row,
+                    tokens=np.ascontiguousarray(flat, dtype=np.int32), want_sorted=np.ascontiguousarray(want_flat[order]))
         for r0 in range(0, total, chunk):
-            r1 = min(total, r0 + chunk)
-            lo, hi = np.searchsorted(sorted_want, [r0, r1])
-            self._run_pass(flat[r0:r1], row_slot[r0:r1], row_pos[r0:r1], sorted_want[lo:hi] - r0, order[lo:hi],
-                           logits, decode, slots, starts, lens, first_row, r0, r1)
+            self._run_pass(step, r0, min(total, r0 + chunk), order, logits, decode)
         for s, n in zip(slots, lens):
             self.cache.lengths[s] += n
         if self.dtype == torch.bfloat16:
@@ -245,69 +243,46 @@ class Engine:
             logits = logits[torch.from_numpy(repeat).to(self.device)]
         return logits
 
-    def _run_pass(self, toks, rslot, rpos, want_rows, want_dest, logits, decode, slots, starts, lens, first_row,
-                  r0, r1) -> None:
-        n = len(toks)
+    def _run_pass(self, step: dict, r0: int, r1: int, order, logits, decode: bool) -> None:
+        """Rows [r0, r1) of a step's flattened rows as one launch of the model."""
+        from ..csrc import ops
+        n = r1 - r0
         # A short bfloat16 prompt pass is launched with a padded row count; the rows past n carry
         # slot -1, belong to no sequence and no tile, write no cache and are wanted by nobody.
         short = self.replayable and self.dtype == torch.bfloat16 and not decode and n <= PASS_GRAPH_MAX_ROWS
         rows = padded_rows(n) if short and padded_rows(n) <= self.ws.max_rows else n
         stage, si = self._stage_buffer()
-        stage[0, :n] = torch.from_numpy(toks.astype(np.int32))
-        stage[1, :n] = torch.from_numpy(rslot)
-        stage[2, :n] = torch.from_numpy(rpos)
-        if rows > n:
-            stage[0, n:rows] = 0
-            stage[1, n:rows] = -1
-            stage[2, n:rows] = 0
-        nw = len(want_rows)
-        if nw:
-            stage[3, :nw] = torch.from_numpy(want_rows.astype(np.int32))
-        # sequence-level view of the pass (for kernels that work per sequence) and its row tiles
-        seq_ids = [i for i in range(len(slots)) if first_row[i] < r1 and first_row[i + 1] > r0]
-        sfirst = np.asarray([max(first_row[i], r0) - r0 for i in seq_ids] + [r1 - r0], dtype=np.int32)
-        counts = np.diff(sfirst)
-        tr = self._tile_rows
-        tiles_per = (counts + tr - 1) // tr
-        n_tiles = int(tiles_per.sum())
-        tile_seq = np.repeat(np.arange(len(seq_ids), dtype=np.int32), tiles_per)
-        tile_k = np.arange(n_tiles, dtype=np.int32) - np.repeat(np.cumsum(tiles_per) - tiles_per, tiles_per).astype(np.int32)
-        stage[4, :n_tiles] = torch.from_numpy(tile_seq)
-        stage[5, :n_tiles] = torch.from_numpy(sfirst[tile_seq] + tr * tile_k)
-        self._meta_dev.copy_(stage, non_blocking=True)
+        ns, n_tiles, max_seq_rows, max_context, lo, hi = ops.plan_pass(
+            step["slots"], step["starts"], step["first_row"], step["tokens"], r0, r1, step["want_sorted"], self._tile_rows,
+            rows, stage)
+        nw = hi - lo
+        want_dest = order[lo:hi]
+        meta = self._meta_dev
+        meta.copy_(stage, non_blocking=True)
         ev = torch.cuda.Event()
         ev.record()
         self._stage_events[si] = ev
-        sslot = np.asarray([slots[i] for i in seq_ids], dtype=np.int32)
-        spos0 = np.asarray([starts[i] + (max(first_row[i], r0) - first_row[i]) for i in seq_ids], dtype=np.int32)
-        ns = len(seq_ids)
-        seq_host = np.zeros((3, ns + 1), dtype=np.int32)
-        seq_host[0, :ns + 1] = sfirst
-        seq_host[1, :ns] = sslot
-        seq_host[2, :ns] = spos0
-        self._seq_dev[:, :ns + 1].copy_(torch.from_numpy(seq_host))
-        max_seq_rows, max_context = int(counts.max()), int(rpos.max()) + 1
         if short:
             # the host-side numbers a part may size its launches by are rounded up, so that passes
             # with the same key below make the same launches
             max_seq_rows = padded_rows(max_seq_rows)
             max_context = -(-max_context // PAGE_SIZE) * PAGE_SIZE
         ctx = StepContext(
-            n_rows=rows, tokens=self._meta_dev[0], row_slot=self._meta_dev[1], row_pos=self._meta_dev[2],
+            n_rows=rows, tokens=meta[0], row_slot=meta[1], row_pos=meta[2],
             dtype=self.dtype, ws=self.ws, cache=self.cache, decode=decode, n_seqs=ns,
             max_seq_rows=max_seq_rows, max_context=max_context,
-            seq_first_row=self._seq_dev[0], seq_slot=self._seq_dev[1], seq_pos0=self._seq_dev[2],
-            n_tiles=n_tiles, tile_seq=self._meta_dev[4], tile_row0=self._meta_dev[5], sm_count=self.sm_count)
+            seq_first_row=meta[6], seq_slot=meta[7], seq_pos0=meta[8],
+            n_tiles=n_tiles, tile_seq=meta[4], tile_row0=meta[5], sm_count=self.sm_count)
         in_order = nw == logits.shape[0] and np.array_equal(want_dest, np.arange(nw))
         if short and self.pass_graphs and nw <= PASS_GRAPH_MAX_WANT and (nw == 0 or in_order):
             self._run_short_pass(ctx, (rows, n_tiles, ns, nw, max_seq_rows, max_context), nw, logits)
         elif nw == 0:
             self.model.forward(ctx, None, 0, None)
         elif in_order:
-            self.model.forward(ctx, self._meta_dev[3], nw, logits)
+            self.model.forward(ctx, meta[3], nw, logits)
         else:
             out = torch.empty((nw, self.vocab_size), dtype=torch.float32, device=self.device)
-            self.model.forward(ctx, self._meta_dev[3], nw, out)
+            self.model.forward(ctx, meta[3], nw, out)
             logits[torch.from_numpy(want_dest).to(self.device)] = out
 
     def _run_short_pass(self, ctx: StepContext, key: tuple, nw: int, logits: torch.Tensor) -> None:

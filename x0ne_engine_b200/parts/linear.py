@@ -27,18 +27,23 @@ class Linear:
         w = self.weight
         if w.dtype == torch.float32:
             ops.gemm_f32_nt(x, w, out, m)
-        elif ops.gemm_smallm_takes(w, m):
-            ops.gemm_bf16_smallm(x, w, out, m)
-        elif out.dtype == torch.bfloat16 and ops.gemm_skinny_tc_wins(w, m):
-            # (not for the float32 logits: the vocabulary's 1,187 tiles of 128 rows are 4.01 waves of
-            # blocks, and the library product is faster there: 203 us against 247 us at 12 rows)
-            ops.gemm_bf16_skinny_tcgen05(x, w, out, m)
-        elif w.dtype == torch.bfloat16:
-            if m > 0:
-                if out.dtype == torch.bfloat16:
-                    torch.mm(x[:m], w.t(), out=out[:m])
-                else:
-                    torch.mm(x[:m], w.t(), out_dtype=torch.float32, out=out[:m])
-        else:
+            return out
+        if w.dtype != torch.bfloat16:
             raise ops.KernelError(f"no matrix product for weights of {w.dtype}")
+        if out.dtype == torch.float32:
+            # logits: the weight-streaming kernel for a handful of rows, else the library (the vocabulary's
+            # 1,187 tiles of 128 rows are 4.01 waves of the few-row tcgen05 kernel's blocks: 247 us against
+            # 203 us at 12 rows)
+            kernel = "smallm" if m <= 8 and ops.gemm_smallm_takes(w, m) else "library"
+        else:
+            kernel = ops.product_kernel(w, m)          # the routing table (csrc/routes.py)
+        if kernel == "smallm":
+            ops.gemm_bf16_smallm(x, w, out, m)
+        elif kernel == "skinny":
+            ops.gemm_bf16_skinny_tcgen05(x, w, out, m)
+        elif m > 0:
+            if out.dtype == torch.bfloat16:
+                torch.mm(x[:m], w.t(), out=out[:m])
+            else:
+                torch.mm(x[:m], w.t(), out_dtype=torch.float32, out=out[:m])
         return out

@@ -43,11 +43,12 @@ class SwiGLU(FeedForward):
         gu = ctx.ws.buffer("ffn.gate_up", (ctx.ws.max_rows, 2 * self.inter), self.env.dtype)
         act = ctx.ws.buffer("ffn.act", (ctx.ws.max_rows, self.inter), self.env.dtype)
         out = ctx.ws.buffer("delta", (ctx.ws.max_rows, self.hidden), self.env.dtype)
-        if ops.gemm_skinny_tc_wins(self.gate_up.weight, n_rows, swiglu=True):
+        kernel = ops.product_kernel(self.gate_up.weight, n_rows, fused=True)       # the routing table (csrc/routes.py)
+        if kernel == "skinny":
             ops.gemm_bf16_skinny_tcgen05(x, self.gate_up.weight, act, n_rows, swiglu=True)   # 9 to 64 rows, tcgen05
-        elif ops.gemm_smallm_takes(self.gate_up.weight, n_rows, swiglu=True):
+        elif kernel == "smallm":
             ops.gemm_bf16_smallm(x, self.gate_up.weight, act, n_rows, swiglu=True)     # activation in the epilogue
-        elif ops.gemm_tc_takes(self.gate_up.weight, n_rows):
+        elif kernel == "tc_pair":
             ops.gemm_bf16_tcgen05(x, self.gate_up.weight, act, n_rows, swiglu=True)    # tcgen05, activation in the epilogue
         else:
             self.gate_up(x, gu, n_rows)
