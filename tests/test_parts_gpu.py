@@ -21,7 +21,8 @@ def make_ctx(engine_dtype, n_rows, slots, positions, cache, decode=False):
                        dtype=engine_dtype, ws=ws, cache=cache, decode=decode, n_seqs=1, max_seq_rows=n_rows,
                        max_context=max(positions) + 1, seq_first_row=mk([0, n_rows]), seq_slot=mk(slots[:1]),
                        seq_pos0=mk(positions[:1]), n_tiles=(n_rows + tr - 1) // tr,
-                       tile_seq=mk([0] * ((n_rows + tr - 1) // tr)), tile_row0=mk(list(range(0, n_rows, tr))))
+                       tile_seq=mk([0] * ((n_rows + tr - 1) // tr)), tile_row0=mk(list(range(0, n_rows, tr))),
+                       sm_count=torch.cuda.get_device_properties(0).multi_processor_count)
 
 
 def rnd(shape, seed, scale=1.0):

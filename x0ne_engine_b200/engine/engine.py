@@ -73,7 +73,7 @@ class StepContext:
     n_tiles: int = 0                               # tiles of consecutive rows of one sequence (prefill attention)
     tile_seq: Optional[torch.Tensor] = None        # int32 [n_tiles]
     tile_row0: Optional[torch.Tensor] = None       # int32 [n_tiles]
-    sm_count: int = 148
+    sm_count: int = 0                              # multiprocessors of the device the pass runs on (set by the engine)
 
 
 def require_gpu(device) -> torch.device:
