@@ -121,13 +121,13 @@ struct SampleIO {
     int32_t n_stop;
 };
 
-__global__ void __launch_bounds__(SB) sample_kernel(SampleIO io) {
+__global__ void __launch_bounds__(SB, 1) sample_kernel(SampleIO io) {
     __shared__ float shf[33];
     __shared__ int shi[33];
     __shared__ unsigned long long s_key[32];
     __shared__ int s_bi[32];
     __shared__ int s_pick;
-    const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int row = blockIdx.x, tid = threadIdx.x;
     pdl_prologue();
     // the word in which this library's tensor-core kernels report a wait that ran out travels to
     // the host with the picks: one more int after the last row's token
@@ -143,12 +143,28 @@ __global__ void __launch_bounds__(SB) sample_kernel(SampleIO io) {
     // (x0ne-core/kernels/cuda/argmax.cu:4-10: a NaN anywhere means no token)
     unsigned long long best = 0ull;
     bool nan = false;
-    for (int i = tid; i < V; i += SB) {
-        const float v = x[i];
+    auto look = [&](float v, int i) {
         nan |= v != v;
         const unsigned long long key = pick_key(v, i);
         best = key > best ? key : best;
+    };
+    // four logits per load where the row starts on a 16-byte boundary (one block scans the whole row,
+    // so what it has in flight decides the time: 24 us for 151,936 logits one by one); the maximum of
+    // the keys does not depend on the order they are looked at
+    int done = 0;
+    if ((reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+        const float4* x4 = reinterpret_cast<const float4*>(x);
+        const int n4 = V / 4;
+        for (int j = tid; j < n4; j += SB) {
+            const float4 v = x4[j];
+            look(v.x, 4 * j);
+            look(v.y, 4 * j + 1);
+            look(v.z, 4 * j + 2);
+            look(v.w, 4 * j + 3);
+        }
+        done = 4 * n4;
     }
+    for (int i = done + tid; i < V; i += SB) look(x[i], i);
     const bool any_nan = __syncthreads_or(nan);
     if (any_nan) {
         if (tid == 0) {
