@@ -17,6 +17,10 @@ Commands and their options follow the reference's own programs where it has them
   replay ...            the trace replay program (same as bin/trace_run)
   init <config.json> <out dir> [--seed S] [--linear-std X] [--norm-jitter X]
       writes a model folder with random weights
+  step-timeline <model dir> [--batch B] [--context N] [--random-weights SEED]
+      one decode step of B sequences at context N as the GPU ran it: every kernel of the replayed graph
+      with the time from the end of the kernel before it to its own end (what it adds to the step)
+      and its own duration, summed per kernel and listed for one layer in the middle of the model
   kernel-bench --kernel NAME [sizes] [--impl ours|reference]   times one kernel alone with CUDA events
       (the reference's per-kernel timing entry: x0ne-core/runtime/src/ops.rs:579-681).  With
       `--impl reference` the reference project's own kernel of that name (attention_decode,
@@ -137,6 +141,83 @@ def cmd_core_bench(a) -> int:
         # a rate measured while the tokens change from one repetition to the next is no measurement of generation
         print("core-bench: two repetitions of the same greedy generation gave different tokens", file=sys.stderr)
         return 3
+    return 0
+
+
+def cmd_step_timeline(a) -> int:
+    """Kernels overlap inside a step (each is launched while the one before it still runs and waits
+    for it on the device), so a kernel's own duration says little; what it adds to the step is the
+    time from its predecessor's end to its own end.  Taken with torch's profiler around one replay of
+    the decode graph, after the step has been timed without the profiler."""
+    import collections
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+    from . import Model
+    from .config import config_from_folder
+    from .engine.decode import DeviceBatch
+    from .engine.generate import Row
+    from .sampling import SamplingParams
+    cfg = config_from_folder(a.model)
+    spec = cfg.to_spec()
+    max_ctx = min(spec.max_position_embeddings, a.context + 64)
+    if a.random_weights is not None:
+        m = Model.random(cfg, seed=a.random_weights, dtype="bfloat16", max_batch=a.batch, max_ctx=max_ctx)
+    else:
+        m = Model.from_folder(a.model, dtype="bfloat16", max_batch=a.batch, max_ctx=max_ctx)
+    eng = m.engine
+    plen = a.context - 8
+    rows = [Row(i, synthetic_ids(plen, spec.vocab_size, 1 + i), SamplingParams(max_tokens=max_ctx), max_ctx - plen, i)
+            for i in range(a.batch)]
+    runner = DeviceBatch(eng, a.batch, cuda_graph=True)
+    runner.run_ahead = False
+    try:
+        runner.start(rows)
+        live = list(range(a.batch))
+        for _ in range(5):
+            runner.step(live)
+        g = runner.graphs[a.batch]
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        s.record()
+        for _ in range(20):
+            g.replay()
+        e.record()
+        torch.cuda.synchronize()
+        ms = s.elapsed_time(e) / 20
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            for _ in range(3):
+                g.replay()
+            torch.cuda.synchronize()
+        for slot in runner.slots:
+            eng.cache.lengths[slot] += 23
+    finally:
+        runner.close()
+    ev = sorted((k for k in prof.events() if k.device_type == torch.autograd.DeviceType.CUDA), key=lambda k: k.time_range.start)
+    last = ev[-(len(ev) // 3):]
+    weights, kv = eng.model.step_weight_bytes(), eng.cache.bytes_per_token() * a.batch * a.context
+    print(f"{eng.describe()}\nbatch {a.batch}, context {a.context}: {ms:.3f} ms per step without the profiler; a step reads "
+          f"{(weights + kv) / 1e9:.2f} GB = {(weights + kv) / ms / 1e6:.0f} GB/s")
+    share = collections.OrderedDict()
+    prev = last[0].time_range.start
+    for k in last:
+        name = k.name.split("(")[0][:56]
+        t = share.setdefault(name, [0, 0.0, 0.0])
+        t[0] += 1
+        t[1] += k.time_range.end - prev
+        t[2] += k.time_range.end - k.time_range.start
+        prev = k.time_range.end
+    print(f"one replay under the profiler: {last[-1].time_range.end - last[0].time_range.start:.0f} us, {len(last)} kernels")
+    print("   adds us   launches   each   own duration each   kernel")
+    for name, (n, add, own) in share.items():
+        print(f"{add:10.1f} {n:10d} {add / n:6.2f} {own / n:19.2f}   {name}")
+    n_entries = len(spec.run_order)
+    per_layer = (len(last) - 4) // max(1, n_entries)
+    start = 2 + per_layer * (n_entries // 2)
+    print(f"layer {n_entries // 2} of {n_entries}:")
+    prev = last[start - 1].time_range.end
+    for k in last[start:start + per_layer]:
+        print(f"   adds {k.time_range.end - prev:6.2f} us   own {k.time_range.end - k.time_range.start:6.2f}   {k.name[:80]}")
+        prev = k.time_range.end
     return 0
 
 
@@ -434,6 +515,13 @@ def main(argv=None) -> int:
     b.add_argument("--random-weights", type=int, default=None, metavar="SEED",
                    help="random weights made on the device from config.json alone (no safetensors needed)")
     b.set_defaults(fn=cmd_core_bench)
+
+    t = sub.add_parser("step-timeline")
+    t.add_argument("model")
+    t.add_argument("--batch", type=int, default=8)
+    t.add_argument("--context", type=int, default=3072)
+    t.add_argument("--random-weights", type=int, default=None, metavar="SEED")
+    t.set_defaults(fn=cmd_step_timeline)
 
     r = sub.add_parser("roofline")
     r.add_argument("--config", required=True)
