@@ -433,6 +433,34 @@ def _kernel_bench_reference(a, timed) -> int:
     sms = torch.cuda.get_device_properties(0).multi_processor_count
     u32 = lambda v: torch.tensor([v], dtype=torch.int32, device=dev)   # noqa: E731
     bf = lambda *shape: torch.randn(*shape, device=dev).bfloat16()     # noqa: E731
+    if a.kernel == "decode_step":
+        # the reference's kernels and cuBLAS in the reference engine's order, one sequence, as a CUDA graph
+        step = R.DecodeStepInReferenceOrder(k, a.layers, a.n, a.k, qh, kvh, a.vocab, a.context)
+        for _ in range(3):
+            step.launch()
+        step.reset()
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            step.launch()
+        steps = min(a.iters, 60)
+        step.reset()
+        g.replay()
+        step.reset()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        s.record()
+        for _ in range(steps):
+            g.replay()
+        e.record()
+        torch.cuda.synchronize()
+        ms = s.elapsed_time(e) / steps
+        bytes_step = step.weight_bytes() + a.layers * 2 * (a.context + steps / 2) * kvh * hd * 2
+        print(json.dumps({"kernel": "decode_step", "impl": "reference kernels + cuBLAS in the reference engine's order, launched by this "
+                          "library's host code (not the reference engine)", "layers": a.layers, "hidden": a.n, "intermediate": a.k,
+                          "context": a.context, "batch": 1, "ms_per_step": ms, "tokens_per_s": 1e3 / ms,
+                          "gb_s": bytes_step / ms / 1e6, "token_after": int(step.token[0])}))
+        return 0
     if a.kernel == "attention_decode":
         ctx = a.context
         kv_bytes = 2 * ctx * kvh * hd * 2
@@ -554,6 +582,8 @@ def main(argv=None) -> int:
     k.add_argument("--kv-heads", type=int, default=8)
     k.add_argument("--head-dim", type=int, default=128)
     k.add_argument("--splits", type=int, default=0)
+    k.add_argument("--layers", type=int, default=36, help="decode_step (--impl reference): layers of the model")
+    k.add_argument("--vocab", type=int, default=151936, help="decode_step (--impl reference): vocabulary")
     k.add_argument("--iters", type=int, default=50)
     k.add_argument("--warmup", type=int, default=5)
     k.set_defaults(fn=cmd_kernel_bench)

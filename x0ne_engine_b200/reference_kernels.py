@@ -180,3 +180,88 @@ def qk_norm_rope_kv_write(k, qkv, q_norm, k_norm, inv_freq, q_out, k_cache, v_ca
 def swiglu(k, gate_up, out, rows, inter):
     """grid (ceil(inter / 256), rows), block 256 (x0ne-core/kernels/cuda/swiglu.cu)."""
     k.launch("x0ne_swiglu_bf16", ((inter + 255) // 256, rows), 256, [_p(gate_up), _p(out), _u(inter)])
+
+
+def embedding(k, table, tokens, out, rows, hidden, vocab):
+    """grid (rows), block 128 (x0ne-core/kernels/cuda/embedding.cu)."""
+    k.launch("x0ne_embedding_bf16", (rows, 1), 128, [_p(table), _p(tokens), _p(out), _u(hidden), _u(vocab)])
+
+
+def argmax(k, logits, n, out, rows=1):
+    """grid (rows), block 1024 (x0ne-core/kernels/cuda/argmax.cu)."""
+    k.launch("x0ne_argmax_f32", (rows, 1), 1024, [_p(logits), _u(n), _p(out)])
+
+
+def advance(k, pos):
+    """grid (1), block 32 (x0ne-core/kernels/cuda/advance.cu)."""
+    k.launch("x0ne_advance_u32", (1, 1), 32, [_p(pos)])
+
+
+class DecodeStepInReferenceOrder:
+    """One greedy decode step of one sequence made of the reference's kernels and cuBLAS products, in
+    the order the reference engine launches them (x0ne-core/runtime/src/engine.rs:744-835: embedding,
+    zeroed float32 residual, per layer add+RMSNorm / q|k|v product / q,k norm + RoPE + cache write /
+    split-K attention with the last block merging / o product / add+RMSNorm / gate|up product / SwiGLU
+    / down product, then the final norm, the float32 logits product, argmax and the position advance).
+
+    It is this library's host code that launches them, so it is NOT the reference engine and no
+    reference arm of a benchmark: it says what the reference's own device code costs per step on
+    this GPU.  Random bfloat16 weights (every layer its own, so a step streams them from memory),
+    a cache filled up to `context` positions."""
+
+    def __init__(self, k: ReferenceKernels, layers: int, hidden: int, inter: int, q_heads: int, kv_heads: int, vocab: int,
+                 context: int, device="cuda:0"):
+        if hidden % 8 or context < 1:
+            raise ValueError("hidden must be a multiple of 8 and the context at least 1")
+        self.k, self.layers, self.h, self.inter, self.qh, self.kvh, self.vocab = k, layers, hidden, inter, q_heads, kv_heads, vocab
+        self.max_ctx = context + 64
+        hd = HEAD_DIM
+        w = lambda r, c: torch.randn(r, c, device=device).mul_(0.02).bfloat16()      # noqa: E731
+        ones = lambda n: torch.ones(n, device=device).bfloat16()                        # noqa: E731
+        self.embed, self.lm_head, self.final_norm = w(vocab, hidden), w(vocab, hidden), ones(hidden)
+        self.w = [dict(qkv=w((q_heads + 2 * kv_heads) * hd, hidden), o=w(hidden, q_heads * hd), gate_up=w(2 * inter, hidden),
+                       down=w(hidden, inter), n1=ones(hidden), n2=ones(hidden), qn=ones(hd), kn=ones(hd)) for _ in range(layers)]
+        self.kv = torch.randn(layers, 2, self.max_ctx, kv_heads * hd, device=device).bfloat16()
+        self.inv_freq = (1e6 ** (-torch.arange(0, hd, 2, device=device, dtype=torch.float32) / hd)).contiguous()
+        bf = lambda n: torch.zeros(1, n, device=device, dtype=torch.bfloat16)           # noqa: E731
+        self.delta, self.normed, self.qkv, self.q, self.att = bf(hidden), bf(hidden), bf((q_heads + 2 * kv_heads) * hd), bf(q_heads * hd), bf(q_heads * hd)
+        self.gate_up, self.act = bf(2 * inter), bf(inter)
+        self.residual = torch.zeros(1, hidden, device=device)
+        self.logits = torch.zeros(1, vocab, device=device)
+        self.token = torch.tensor([17], dtype=torch.int32, device=device)
+        self.pos = torch.tensor([context - 1], dtype=torch.int32, device=device)
+        self.pos0 = context - 1
+        sms = torch.cuda.get_device_properties(device).multi_processor_count
+        self.plan = split_plan(k, q_heads, kv_heads, sms)
+        self.state = torch.zeros(q_heads * self.plan[2] * SPLIT_STATE, device=device)
+        self.counter = torch.zeros(max(q_heads, kv_heads), dtype=torch.int32, device=device)
+        self.scale = 1.0 / (hd ** 0.5)
+
+    def weight_bytes(self) -> int:
+        per_layer = sum(v.numel() for name, v in self.w[0].items() if name in ("qkv", "o", "gate_up", "down")) * 2
+        return self.layers * per_layer + self.lm_head.numel() * 2
+
+    def launch(self) -> None:
+        k, h = self.k, self.h
+        embedding(k, self.embed, self.token, self.delta, 1, h, self.vocab)
+        self.residual.zero_()
+        for l, w in enumerate(self.w):
+            add_rmsnorm(k, self.residual, self.delta, w["n1"], self.normed, 1, h, 1e-6)
+            torch.mm(self.normed, w["qkv"].t(), out=self.qkv)
+            qk_norm_rope_kv_write(k, self.qkv, w["qn"], w["kn"], self.inv_freq, self.q, self.kv[l, 0], self.kv[l, 1], self.pos, 1,
+                                  self.qh, self.kvh, self.max_ctx, 1e-6)
+            attention_decode(k, self.q, self.kv[l, 0], self.kv[l, 1], self.state, self.counter, self.att, self.pos, self.qh, self.kvh,
+                             self.max_ctx, self.scale, self.plan)
+            torch.mm(self.att, w["o"].t(), out=self.delta)
+            add_rmsnorm(k, self.residual, self.delta, w["n2"], self.normed, 1, h, 1e-6)
+            torch.mm(self.normed, w["gate_up"].t(), out=self.gate_up)
+            swiglu(k, self.gate_up, self.act, 1, self.inter)
+            torch.mm(self.act, w["down"].t(), out=self.delta)
+        add_rmsnorm(k, self.residual, self.delta, self.final_norm, self.normed, 1, h, 1e-6)
+        torch.mm(self.normed, self.lm_head.t(), out_dtype=torch.float32, out=self.logits)
+        argmax(k, self.logits, self.vocab, self.token)
+        advance(k, self.pos)
+
+    def reset(self) -> None:
+        self.pos.fill_(self.pos0)
+        self.token.fill_(17)
