@@ -3,12 +3,14 @@
 Commands and their options follow the reference's own programs where it has them:
 
   core-bench <model dir> [--lengths short,1k,4k] [--decode N] [--reps N] [--batch B] [--dtype D]
-      [--random-weights SEED]
+      [--random-weights SEED] [--clock-trace]
       time to first token, prefill and decode rates and the gaps between tokens (p50 / p90 / p99, as
       x0ne-core/runtime/src/engine.rs:1106-1116 stamps them) per prompt length, one line
       `x0ne-bench-result: <JSON>` (x0ne-core/oracle/examples/core-bench.rs:6-16,420-436).  Exit code
       3 when two repetitions of a length gave different tokens
-      (x0ne-core/oracle/examples/core-perf.rs:85-89).
+      (x0ne-core/oracle/examples/core-perf.rs:85-89).  --clock-trace adds the SM clock during the
+      last repetition (read through NVML, nothing is set): what the prompts' pass does to the clock
+      and how long the first decode steps run at the lowered clock.
   roofline --config config.json --gpu <GB/s> --prompt P --generated N [--tok-s X] [--batch B]
       places a decode rate against the bandwidth ceiling
       (x0ne-core/runtime/src/bin/x0ne-core-roofline.rs:4-5, x0ne-core/runtime/src/roofline.rs:55-102).
@@ -83,6 +85,55 @@ def cmd_generate(a) -> int:
     return 0
 
 
+class _ClockPoll:
+    """Reads the SM clock and the power draw through NVML every millisecond on a host thread
+    (reading only; it sets nothing)."""
+
+    def __init__(self, device: int = 0):
+        import threading
+        import pynvml
+        pynvml.nvmlInit()
+        self._nvml, self._h = pynvml, pynvml.nvmlDeviceGetHandleByIndex(device)
+        self.samples, self._stop = [], False
+        self._thread = threading.Thread(target=self._run, daemon=True)
+
+    def _run(self):
+        n = self._nvml
+        while not self._stop:
+            self.samples.append((time.perf_counter(), n.nvmlDeviceGetClockInfo(self._h, n.NVML_CLOCK_SM),
+                                 n.nvmlDeviceGetPowerUsage(self._h) / 1000.0))
+            time.sleep(0.001)
+
+    def __enter__(self):
+        self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop = True
+        self._thread.join()
+
+    def runs(self, first_token_at: float, gaps) -> list:
+        """Stretches of one clock value, in milliseconds after the first token (negative: during the
+        prompts' pass), each with the median gap of the tokens that arrived in it."""
+        arrivals, t = [], first_token_at
+        for g in gaps:
+            t += g
+            arrivals.append((t, g))
+        out = []
+        for ts, mhz, watts in self.samples:
+            if out and out[-1]["sm_mhz"] == mhz:
+                out[-1]["_to"], out[-1]["_w"] = ts, out[-1]["_w"] + [watts]
+            else:
+                out.append({"sm_mhz": mhz, "_from": ts, "_to": ts, "_w": [watts]})
+        for r in out:
+            inside = sorted(g for t, g in arrivals if r["_from"] <= t <= r["_to"])
+            r["from_ms"] = round((r.pop("_from") - first_token_at) * 1e3, 1)
+            r["to_ms"] = round((r.pop("_to") - first_token_at) * 1e3, 1)
+            r["watts"] = round(sorted(r["_w"])[len(r.pop("_w")) // 2])
+            r["tokens"], r["gap_ms_median"] = len(inside), round(inside[len(inside) // 2] * 1e3, 3) if inside else None
+        return out
+
+
 def cmd_core_bench(a) -> int:
     import torch
     from . import Model
@@ -110,9 +161,17 @@ def cmd_core_bench(a) -> int:
         first = None
         # two runs before the timed ones: the first launches a short prompt pass itself, the second
         # captures its launches into a graph, later ones replay it
+        clock_runs = None
         for rep in range(a.reps + 2):
             m._generator.stats = st = GenerationStats()
-            out = m.generate(prompts, max_tokens=a.decode, stop_token_ids=())
+            if a.clock_trace and rep == a.reps + 1:
+                time.sleep(0.5)                     # the GPU idles first, as before a user's call
+                with _ClockPoll(torch.cuda.current_device()) as poll:
+                    began = time.perf_counter()
+                    out = m.generate(prompts, max_tokens=a.decode, stop_token_ids=())
+                clock_runs = poll.runs(began + st.prefill_seconds, st.token_gaps)
+            else:
+                out = m.generate(prompts, max_tokens=a.decode, stop_token_ids=())
             rates = (st.prefill_seconds, st.prefill_tokens / st.prefill_seconds,
                      st.decode_tokens / st.decode_seconds if st.decode_seconds else 0.0)
             if rep == 0:
@@ -126,6 +185,8 @@ def cmd_core_bench(a) -> int:
                         "first": {"ttft_s": first[0], "prefill_tok_s": first[1], "decode_tok_s": first[2]},
                         "ttft_s": _stats(ttft), "prefill_tok_s": _stats(prefill), "decode_tok_s": _stats(decode),
                         "token_gap_s": percentiles(gaps)})
+        if clock_runs is not None:
+            results[-1]["clock_runs"] = clock_runs
     free, total = torch.cuda.mem_get_info()
     spec = m.engine.spec
     print("x0ne-bench-result: " + json.dumps({
@@ -542,6 +603,9 @@ def main(argv=None) -> int:
     b.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     b.add_argument("--random-weights", type=int, default=None, metavar="SEED",
                    help="random weights made on the device from config.json alone (no safetensors needed)")
+    b.add_argument("--clock-trace", action="store_true",
+                   help="read the SM clock (NVML) every millisecond during the last repetition and report the "
+                        "stretches of one clock value with the token gaps that fell into each")
     b.set_defaults(fn=cmd_core_bench)
 
     t = sub.add_parser("step-timeline")
