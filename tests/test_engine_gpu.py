@@ -283,6 +283,68 @@ def test_a_far_key_among_hundreds_decides_the_logits(dtype):
     check(dtype, got, want, "far key")
 
 
+def test_one_and_two_long_sequences_decode_through_several_clusters_per_kv_head():
+    """With one or two sequences and thousands of keys the decode attention gives every kv head
+    several thread-block clusters whose results meet in scratch.  The keys of one early page are made
+    to weigh on the last query (that page holds one token whose embedding row is scaled up, and the
+    last prompt token is the same one), so a lost or misplaced partial result would show.
+    The plain implementation takes a minute per sequence at this length, so the 32-bit path, which
+    the other tests tie to it and whose attention is the plain kernel, stands in for it on the same
+    bfloat16-rounded matrices.  Through the step function at batch 2 and batch 1, and through
+    generation (graph replay), whose first token must be the step function's."""
+    from x0ne_engine_b200 import Engine, Model, Qwen3Config
+    from x0ne_engine_b200.engine import tensor_needs_of_spec
+    from x0ne_engine_b200.parts.attention import decode_plan
+    from x0ne_engine_b200.weights import RandomInit, make_tensor
+    cfg = Qwen3Config(hidden_size=64, intermediate_size=96, num_hidden_layers=2, num_attention_heads=4,
+                      num_key_value_heads=2, head_dim=32, vocab_size=300, max_position_embeddings=16384,
+                      rms_norm_eps=1e-6, rope_theta=1000000.0, tie_word_embeddings=False, dtype="float32")
+    init = RandomInit(11, 0.05, 0.1)
+    tensors = {}
+    for need in tensor_needs_of_spec(cfg.to_spec()):
+        t = make_tensor(need, init, torch.float32, "cuda:0")
+        tensors[need.name] = t.bfloat16().float() if t.dim() == 2 else t
+    special = 7
+    tensors["model.embed_tokens.weight"][special] *= 6.0
+    n, ctx = 8600, 8704
+    rng = np.random.default_rng(12)
+    a = [int(t) for t in rng.integers(8, cfg.vocab_size, n)]
+    b = [int(t) for t in rng.integers(8, cfg.vocab_size, n - 777)]
+    a[192:256] = [special] * 64           # page 3: the first cluster's range
+    a[-1] = special
+    other = list(a)
+    other[192:256] = [9] * 64
+    last3 = lambda ids: [len(ids) - 3, len(ids) - 2, len(ids) - 1]   # noqa: E731
+    ref = Engine(cfg.to_spec(), tensors, "float32", "cuda:0", max_tokens=ctx + 64, max_seq_len=ctx)
+    want = {}
+    for name, ids in (("a", a), ("b", b), ("other", other)):
+        s = ref.new_sequence()
+        want[name] = ref.step([s], [ids], [last3(ids)]).cpu().numpy()
+        ref.free_sequence(s)
+    del ref
+    assert np.abs(want["other"][-1] - want["a"][-1]).max() > 2e-2 * np.abs(want["a"][-1]).max(), \
+        "the far page does not matter enough for this test to see it"
+    held = {k: (v.bfloat16() if v.dim() == 2 else v) for k, v in tensors.items()}
+    eng = Engine(cfg.to_spec(), held, "bfloat16", "cuda:0", max_tokens=2 * ctx + 128, max_seq_len=ctx)
+    for batch in (1, 2):
+        splits, groups = decode_plan(type("C", (), {"max_context": eng.max_seq_len, "sm_count": eng.sm_count}), batch,
+                                     cfg.num_key_value_heads, cfg.num_attention_heads, cfg.head_dim)
+        assert groups > 1 and splits // groups >= 2, "this engine would not take the path the test is for"
+    sa, sb = eng.new_sequence(), eng.new_sequence()
+    eng.step([sa, sb], [a[:-3], b[:-3]], [[], []])
+    got = [eng.step([sa, sb], [[x], [y]]).cpu().numpy() for x, y in zip(a[-3:-1], b[-3:-1])]
+    eng.free_sequence(sb)
+    last_a = eng.step([sa], [[a[-1]]]).cpu().numpy()[0]               # batch 1
+    eng.free_sequence(sa)
+    check("bfloat16", np.stack([g[0] for g in got] + [last_a]), want["a"], "long context, first sequence")
+    check("bfloat16", np.stack([g[1] for g in got]), want["b"][:2], "long context, second sequence")
+    m = Model(eng, max_batch=2)
+    out = m.generate([a, b], max_tokens=3, stop_token_ids=())
+    assert out.tokens[0][0] == int(np.argmax(last_a))
+    again = m.generate([a, b], max_tokens=3, stop_token_ids=())
+    assert again.tokens == out.tokens
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name,lengths,n_new", [("A", [5, 11, 17], 8), ("B", [1, 7, 30, 64], 12)])
 @pytest.mark.parametrize("decode", ["graph", "eager"])

@@ -463,6 +463,42 @@ def test_decode_attention_bf16(q_heads, kv_heads, hd, window, splits):
     assert int(counters.abs().sum()) == 0
 
 
+@pytest.mark.parametrize("q_heads,kv_heads,hd", [(4, 2, 16), (5, 1, 48), (32, 8, 128), (3, 3, 96)])
+@pytest.mark.parametrize("window", [0, 200])
+@pytest.mark.parametrize("cluster,groups", [(2, 2), (8, 4), (3, 5), (5, 7), (8, 8)])
+def test_decode_attention_bf16_in_several_clusters(q_heads, kv_heads, hd, window, cluster, groups):
+    """The splits of a (sequence, kv head) as several thread-block clusters: each cluster merges in
+    shared memory, the clusters' results meet in scratch.  Contexts around every tile edge, also
+    fewer pages than splits (clusters with nothing to read); the arrival counters must be back at
+    zero afterwards, and the second call must give the same bits."""
+    o = ops()
+    ctxs = [1, 2, 17, 64, 65, 129, 300, 513, 1100]
+    n = len(ctxs)
+    storage, table, view = make_cache(kv_heads, hd, n * 18, n, torch.bfloat16, 18)
+    fill_cache(storage, torch.bfloat16, 54)
+    slots = torch.arange(n, dtype=torch.int32, device=DEV)
+    pos = torch.tensor([c - 1 for c in ctxs], dtype=torch.int32, device=DEV)
+    q = rnd((n, q_heads * hd), torch.bfloat16, 55)
+    scratch = torch.zeros(o.attention_decode_scratch_bytes(n, q_heads, kv_heads, hd, groups), dtype=torch.uint8, device=DEV)
+    outs = []
+    for _ in range(2):
+        out = torch.full_like(q, 55.0)
+        o.attention_decode_bf16(q, out, view, slots, pos, n, q_heads, 1 / math.sqrt(hd), window, cluster * groups, scratch,
+                                groups=groups)
+        outs.append(out)
+    want = plain_attention_over_cache(q.reshape(n, q_heads, hd), storage, table, slots, pos, q_heads, kv_heads, hd, window)
+    vmax = float(storage.float().abs().max())
+    assert (outs[0].double().cpu() - want).abs().max() / vmax < BF16_EPS
+    assert torch.equal(outs[0], outs[1])
+    group_chunks = (q_heads // kv_heads + 15) // 16
+    assert int(scratch[: n * kv_heads * group_chunks * 4].view(torch.int32).abs().sum()) == 0
+    with pytest.raises(o.KernelError):      # clusters of 2 to 8 blocks; a scratch is needed
+        o.attention_decode_bf16(q, out, view, slots, pos, n, q_heads, 1 / math.sqrt(hd), window, 9 * 2, scratch, groups=2)
+    with pytest.raises(o.KernelError):
+        o.attention_decode_bf16(q, out, view, slots, pos, n, q_heads, 1 / math.sqrt(hd), window, cluster * groups, None,
+                                groups=groups)
+
+
 @pytest.mark.parametrize("splits", [1, 3])
 def test_decode_attention_bf16_long_contexts(splits):
     """Contexts past 128 pages per block (the page numbers a block keeps in shared memory) and a

@@ -375,7 +375,7 @@ def cmd_kernel_bench(a) -> int:
         return 0
 
     if a.kernel == "attention_decode":
-        from .parts.attention import decode_splits
+        from .parts.attention import decode_plan
         hd, kvh, qh, B, ctx = a.head_dim, a.kv_heads, a.q_heads, a.batch, a.context
         pages_per = (ctx + 63) // 64
         kv_bytes = B * pages_per * 2 * kvh * 64 * hd * 2
@@ -393,7 +393,7 @@ def cmd_kernel_bench(a) -> int:
         class Ctx:
             max_context = ctx
             sm_count = torch.cuda.get_device_properties(0).multi_processor_count
-        splits = a.splits or decode_splits(Ctx, B, kvh, qh, hd)
+        splits, groups = (a.splits, max(1, a.groups)) if a.splits else decode_plan(Ctx, B, kvh, qh, hd)
         scratch = torch.zeros(max(1, ops.attention_decode_scratch_bytes(B, qh, kvh, hd, splits)), dtype=torch.uint8,
                               device=dev)
         i = [0]
@@ -402,8 +402,9 @@ def cmd_kernel_bench(a) -> int:
             v = views[i[0] % copies]
             i[0] += 1
             ops.attention_decode_bf16(q, out, v, slots, pos, B, qh, 1 / math.sqrt(hd), 0, splits,
-                                      scratch if (a.scratch_merge or splits > ops.ATTENTION_DECODE_CLUSTER_SPLITS) else None)
-        print(f"splits {splits}", file=sys.stderr)
+                                      scratch if (groups > 1 or a.scratch_merge or splits > ops.ATTENTION_DECODE_CLUSTER_SPLITS)
+                                      else None, groups=groups)
+        print(f"splits {splits} in {groups} cluster(s)", file=sys.stderr)
         timed(fn, B * ctx * 2 * kvh * hd * 2, 4.0 * B * qh * hd * ctx)
         return 0
 
@@ -646,6 +647,8 @@ def main(argv=None) -> int:
     k.add_argument("--kv-heads", type=int, default=8)
     k.add_argument("--head-dim", type=int, default=128)
     k.add_argument("--splits", type=int, default=0)
+    k.add_argument("--groups", type=int, default=1,
+                   help="attention_decode: with --splits, how many thread-block clusters the splits of a (sequence, kv head) form")
     k.add_argument("--layers", type=int, default=36, help="decode_step (--impl reference): layers of the model")
     k.add_argument("--vocab", type=int, default=151936, help="decode_step (--impl reference): vocabulary")
     k.add_argument("--iters", type=int, default=50)

@@ -333,14 +333,15 @@ struct DecodeArgs {
     bf16* out;
     const int32_t* row_slot;
     const int32_t* row_pos;
-    float* part_o;         // [rows * q_heads][splits][HD]
-    float* part_ml;        // [rows * q_heads][splits][2]
+    float* part_o;         // [rows * q_heads][parts][HD]
+    float* part_ml;        // [rows * q_heads][parts][2]
     int32_t* counters;     // [rows * kv_heads * group_chunks], zero before the launch, zero after
     int32_t q_heads;
     int32_t window;
-    int32_t splits;
+    int32_t splits;        // blocks per (sequence, kv head): the pages are cut into this many ranges
     float scale_log2;
-    int32_t cluster_merge;  // merge the splits inside a thread-block cluster (needs no scratch; splits <= 8)
+    int32_t cluster_merge;  // the splits form thread-block clusters of splits / groups blocks that merge in shared memory
+    int32_t groups;         // clusters per (sequence, kv head); more than one: their results meet in scratch
 };
 
 #define DEC_MAX_PAGES 128
@@ -365,9 +366,11 @@ __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
-// CLUSTER: the blocks of one (sequence, kv head) are one thread-block cluster and merge their
-// partial results through each other's shared memory (at most 8 splits); otherwise they go through
-// global scratch and the last block to arrive merges.
+// CLUSTER: the blocks of one (sequence, kv head) form `groups` thread-block clusters of at most 8
+// blocks, each of which merges its partial results through its blocks' shared memory; one cluster
+// writes the output itself, several leave one partial result each in global scratch and the last
+// block to arrive merges those (a long context at a small batch: 4 clusters of 8 put 256 blocks on
+// 8 kv heads).  Not CLUSTER: every block's partial result goes through scratch.
 template <int HD, int STAGES, bool CLUSTER>
 __global__ void __launch_bounds__(128) attention_decode_kernel(DecodeArgs a, PagedCache cache) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -381,6 +384,10 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(DecodeArgs a, Pag
     pdl_launch_dependents();
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int split = blockIdx.x, b = blockIdx.z;
+    const int csize = CLUSTER ? a.splits / a.groups : 1;        // blocks of one cluster
+    const int crank = CLUSTER ? split % csize : 0;
+    const int parts = CLUSTER ? a.groups : a.splits;            // partial results that meet in scratch
+    const int part = CLUSTER ? split / csize : split;
     const int G = a.q_heads / cache.kv_heads;
     const int gchunks = (G + 15) / 16;
     const int kh = blockIdx.y / gchunks, gc = blockIdx.y % gchunks;
@@ -553,80 +560,91 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(DecodeArgs a, Pag
                 xml[r * 2 + 1] = L;
             }
         } else {
-            a.part_o[((qrow0 + r) * a.splits + split) * HD + d] = acc;
+            a.part_o[((qrow0 + r) * parts + part) * HD + d] = acc;
             if (d == 0) {
-                a.part_ml[((qrow0 + r) * a.splits + split) * 2] = M;
-                a.part_ml[((qrow0 + r) * a.splits + split) * 2 + 1] = L;
+                a.part_ml[((qrow0 + r) * parts + part) * 2] = M;
+                a.part_ml[((qrow0 + r) * parts + part) * 2 + 1] = L;
             }
         }
     }
     if (a.splits == 1) return;
     if constexpr (CLUSTER) {
-        // Every block of the cluster takes a share of the output and sums the splits in their order.
+        // Every block of the cluster takes a share of the output and sums the cluster's splits in their order.
         cluster_sync_all();
-        for (int e = split * 128 + tid; e < nheads * (HD / 4); e += 128 * a.splits) {
+        for (int e = crank * 128 + tid; e < nheads * (HD / 4); e += 128 * csize) {
             const int r = e / (HD / 4), d = (e % (HD / 4)) * 4;
             float M = -INFINITY;
-            for (int sp = 0; sp < a.splits; ++sp) M = fmaxf(M, ld_dsmem(dsmem_addr(xml + r * 2, sp)));
+            for (int sp = 0; sp < csize; ++sp) M = fmaxf(M, ld_dsmem(dsmem_addr(xml + r * 2, sp)));
             float L = 0.f;
             float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-            for (int sp = 0; sp < a.splits; ++sp) {
+            for (int sp = 0; sp < csize; ++sp) {
                 const float ms = ld_dsmem(dsmem_addr(xml + r * 2, sp));
                 const float f = ms == -INFINITY ? 0.f : exp2f(ms - M);
                 L += ld_dsmem(dsmem_addr(xml + r * 2 + 1, sp)) * f;
                 const float4 v = ld_dsmem4(dsmem_addr(mo + r * HD + d, sp));
                 acc.x += v.x * f; acc.y += v.y * f; acc.z += v.z * f; acc.w += v.w * f;
             }
-            const float il = 1.0f / L;
-            bf16* dst = a.out + (qrow0 + r) * HD + d;
-            *reinterpret_cast<uint2*>(dst) = make_uint2(pack_bf16(acc.x * il, acc.y * il), pack_bf16(acc.z * il, acc.w * il));
+            if (parts == 1) {
+                const float il = 1.0f / L;
+                bf16* dst = a.out + (qrow0 + r) * HD + d;
+                *reinterpret_cast<uint2*>(dst) = make_uint2(pack_bf16(acc.x * il, acc.y * il), pack_bf16(acc.z * il, acc.w * il));
+            } else {
+                // this cluster's result, not yet divided by its sum, for the merge of the clusters
+                *reinterpret_cast<float4*>(a.part_o + ((qrow0 + r) * parts + part) * HD + d) = acc;
+                if (d == 0) {
+                    a.part_ml[((qrow0 + r) * parts + part) * 2] = M;
+                    a.part_ml[((qrow0 + r) * parts + part) * 2 + 1] = L;
+                }
+            }
         }
+        if (parts > 1) __threadfence();     // this block's share is visible before any block of the cluster counts itself in
         cluster_sync_all();      // nobody leaves while its shared memory may still be read
-        return;
+        if (parts == 1) return;
     }
 
-    // last arriver merges the splits in their fixed order
+    // The last block to arrive (every block of every cluster counts itself in) merges the partial
+    // results in their fixed order.
     __threadfence();
     __syncthreads();
     if (tid == 0) {
         int32_t* cnt = a.counters + ((int64_t)b * cache.kv_heads * gchunks + blockIdx.y);
         const int prev = atomicAdd(cnt, 1);
-        s_last = prev == a.splits - 1;
+        s_last = prev == (int)gridDim.x - 1;
         if (s_last) *cnt = 0;
     }
     __syncthreads();
     if (!s_last) return;
     __threadfence();
-    // Per (head, split) weights first, all loads in parallel, then every thread sums four
-    // consecutive output values over the splits in their order.
-    float* wgt = reinterpret_cast<float*>(ks);           // [16][splits]: exp2(m_s - M); then [16]: 1 / L
-    float* inv_l = wgt + 16 * a.splits;
-    for (int e = tid; e < nheads * a.splits; e += 128) {
-        const int r = e / a.splits, sp = e % a.splits;
-        wgt[r * a.splits + sp] = __ldcg(a.part_ml + ((qrow0 + r) * a.splits + sp) * 2);
+    // Per (head, part) weights first, all loads in parallel, then every thread sums four
+    // consecutive output values over the parts in their order.
+    float* wgt = reinterpret_cast<float*>(ks);           // [16][parts]: exp2(m_s - M); then [16]: 1 / L
+    float* inv_l = wgt + 16 * parts;
+    for (int e = tid; e < nheads * parts; e += 128) {
+        const int r = e / parts, sp = e % parts;
+        wgt[r * parts + sp] = __ldcg(a.part_ml + ((qrow0 + r) * parts + sp) * 2);
     }
     __syncthreads();
     if (tid < nheads) {
         float M = -INFINITY;
-        for (int sp = 0; sp < a.splits; ++sp) M = fmaxf(M, wgt[tid * a.splits + sp]);
+        for (int sp = 0; sp < parts; ++sp) M = fmaxf(M, wgt[tid * parts + sp]);
         float L = 0.f;
-        for (int sp = 0; sp < a.splits; ++sp) {
-            const float ms = wgt[tid * a.splits + sp];
+        for (int sp = 0; sp < parts; ++sp) {
+            const float ms = wgt[tid * parts + sp];
             const float f = ms == -INFINITY ? 0.f : exp2f(ms - M);
-            wgt[tid * a.splits + sp] = f;
-            L += __ldcg(a.part_ml + ((qrow0 + tid) * a.splits + sp) * 2 + 1) * f;
+            wgt[tid * parts + sp] = f;
+            L += __ldcg(a.part_ml + ((qrow0 + tid) * parts + sp) * 2 + 1) * f;
         }
         inv_l[tid] = 1.0f / L;
     }
     __syncthreads();
     for (int e = tid; e < nheads * (HD / 4); e += 128) {
         const int r = e / (HD / 4), d = (e % (HD / 4)) * 4;
-        const float* po = a.part_o + (qrow0 + r) * a.splits * HD + d;
+        const float* po = a.part_o + (qrow0 + r) * parts * HD + d;
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll 8
-        for (int sp = 0; sp < a.splits; ++sp) {
+        for (int sp = 0; sp < parts; ++sp) {
             const float4 v = __ldcg(reinterpret_cast<const float4*>(po + sp * HD));
-            const float f = wgt[r * a.splits + sp];
+            const float f = wgt[r * parts + sp];
             acc.x += v.x * f; acc.y += v.y * f; acc.z += v.z * f; acc.w += v.w * f;
         }
         const float il = inv_l[r];
@@ -678,7 +696,7 @@ static int launch_decode_variant(const DecodeArgs& a, const PagedCache& cache, i
     const int G = a.q_heads / cache.kv_heads;
     dim3 grid(a.splits, cache.kv_heads * ((G + 15) / 16), n_rows);
     if (CLUSTER)
-        x0ne_launch_clusters(attention_decode_kernel<HD, DECODE_STAGES, CLUSTER>, dim3(grid), dim3(128), a.splits, smem, stream, a, cache);
+        x0ne_launch_clusters(attention_decode_kernel<HD, DECODE_STAGES, CLUSTER>, dim3(grid), dim3(128), a.splits / a.groups, smem, stream, a, cache);
     else
         x0ne_launch(attention_decode_kernel<HD, DECODE_STAGES, CLUSTER>, dim3(grid), dim3(128), smem, stream, a, cache);
     X0NE_LAUNCH_CHECK();
@@ -686,7 +704,7 @@ static int launch_decode_variant(const DecodeArgs& a, const PagedCache& cache, i
 
 template <int HD>
 static int launch_decode(const DecodeArgs& a, const PagedCache& cache, int n_rows, cudaStream_t stream) {
-    if (a.cluster_merge && a.splits > 1 && a.splits <= DECODE_CLUSTER_MAX)
+    if (a.cluster_merge && a.splits > 1 && a.splits / a.groups <= DECODE_CLUSTER_MAX)
         return launch_decode_variant<HD, true>(a, cache, n_rows, stream);
     return launch_decode_variant<HD, false>(a, cache, n_rows, stream);
 }
@@ -780,12 +798,19 @@ X0NE_API int64_t x0ne_attention_decode_scratch_bytes(int n_rows, int q_heads, in
     return po + ml + ((cn + 255) / 256) * 256;
 }
 
-X0NE_API int x0ne_attention_decode_bf16(const void* q, void* out, PagedCache cache, const int32_t* row_slot,
-                                        const int32_t* row_pos, int n_rows, int q_heads, float scale, int window,
-                                        int splits, void* scratch, int64_t scratch_bytes, cudaStream_t stream) {
+// `groups` = 1: `splits` blocks per (sequence, kv head); without scratch (and with at most 8 splits)
+// they are one thread-block cluster and merge in shared memory, with scratch every block leaves its
+// partial result there and the last one merges.  `groups` > 1: `groups` clusters of splits / groups
+// blocks (2 to 8) each; a cluster merges in shared memory, the clusters' results meet in scratch
+// (sized by x0ne_attention_decode_scratch_bytes for `groups` parts).
+static int decode_entry(const void* q, void* out, PagedCache cache, const int32_t* row_slot, const int32_t* row_pos,
+                        int n_rows, int q_heads, float scale, int window, int splits, int groups, void* scratch,
+                        int64_t scratch_bytes, cudaStream_t stream) {
     if (int e = check_common(cache, q_heads, "attention_decode")) return e;
     X0NE_REQUIRE(n_rows >= 0 && n_rows <= 65535, "attention_decode: %d rows in one launch (limit 65535)", n_rows);
     X0NE_REQUIRE(splits >= 1 && splits <= 64, "attention_decode: %d splits (1 to 64)", splits);
+    X0NE_REQUIRE(groups >= 1 && splits % groups == 0 && (groups == 1 || (splits / groups >= 2 && splits / groups <= DECODE_CLUSTER_MAX)),
+                 "attention_decode: %d splits in %d clusters (clusters of 2 to %d blocks)", splits, groups, DECODE_CLUSTER_MAX);
     X0NE_REQUIRE(window >= 0, "attention_decode: negative window");
     if (n_rows == 0) return 0;
     DecodeArgs a{};
@@ -796,20 +821,37 @@ X0NE_API int x0ne_attention_decode_bf16(const void* q, void* out, PagedCache cac
     a.q_heads = q_heads;
     a.window = window;
     a.splits = splits;
+    a.groups = groups;
     a.scale_log2 = scale * LOG2E;
-    if (splits > 1 && scratch == nullptr && splits <= DECODE_CLUSTER_MAX) {
+    if (groups == 1 && splits > 1 && scratch == nullptr && splits <= DECODE_CLUSTER_MAX) {
         a.cluster_merge = 1;      // no scratch given: the splits of a (sequence, kv head) merge inside their cluster
     } else if (splits > 1) {
-        const int64_t need = x0ne_attention_decode_scratch_bytes(n_rows, q_heads, cache.kv_heads, cache.head_dim, splits);
+        const int parts = groups > 1 ? groups : splits;
+        const int64_t need = x0ne_attention_decode_scratch_bytes(n_rows, q_heads, cache.kv_heads, cache.head_dim, parts);
         X0NE_REQUIRE(scratch != nullptr && scratch_bytes >= need, "attention_decode: scratch of %lld bytes, %lld needed",
                      (long long)scratch_bytes, (long long)need);
         const int G = q_heads / cache.kv_heads, gchunks = (G + 15) / 16;
         const int64_t cn = (((int64_t)n_rows * cache.kv_heads * gchunks * 4 + 255) / 256) * 256;
         a.counters = (int32_t*)scratch;
         a.part_o = (float*)((char*)scratch + cn);            // 256-byte aligned: read back as float4
-        a.part_ml = a.part_o + (int64_t)n_rows * q_heads * splits * cache.head_dim;
+        a.part_ml = a.part_o + (int64_t)n_rows * q_heads * parts * cache.head_dim;
+        a.cluster_merge = groups > 1;
         X0NE_REQUIRE(((uintptr_t)scratch & 15) == 0, "attention_decode: scratch is not 16-byte aligned");
     }
     DISPATCH_HD(cache.head_dim, return launch_decode<HD_>(a, cache, n_rows, stream));
     X0NE_REQUIRE(false, "attention_decode: head_dim %d not built", cache.head_dim);
+}
+
+X0NE_API int x0ne_attention_decode_bf16(const void* q, void* out, PagedCache cache, const int32_t* row_slot,
+                                        const int32_t* row_pos, int n_rows, int q_heads, float scale, int window,
+                                        int splits, void* scratch, int64_t scratch_bytes, cudaStream_t stream) {
+    return decode_entry(q, out, cache, row_slot, row_pos, n_rows, q_heads, scale, window, splits, 1, scratch, scratch_bytes, stream);
+}
+
+X0NE_API int x0ne_attention_decode_grouped_bf16(const void* q, void* out, PagedCache cache, const int32_t* row_slot,
+                                                const int32_t* row_pos, int n_rows, int q_heads, float scale, int window,
+                                                int splits, int groups, void* scratch, int64_t scratch_bytes,
+                                                cudaStream_t stream) {
+    return decode_entry(q, out, cache, row_slot, row_pos, n_rows, q_heads, scale, window, splits, groups, scratch, scratch_bytes,
+                        stream);
 }

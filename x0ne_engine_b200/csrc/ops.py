@@ -61,6 +61,7 @@ _SIGNATURES = {
     "x0ne_gemm_f32_nt": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     "x0ne_attention_prefill_bf16": [_P, _P, None, _P, _P, _I, _P, _P, _P, _I, _F, _I, _P],
     "x0ne_attention_decode_bf16": [_P, _P, None, _P, _P, _I, _I, _F, _I, _I, _P, _L, _P],
+    "x0ne_attention_decode_grouped_bf16": [_P, _P, None, _P, _P, _I, _I, _F, _I, _I, _I, _P, _L, _P],
     "x0ne_gemm_bf16_smallm": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     "x0ne_attention_prefill_tcgen05": [_P, _P, _I, None, _P, _P, _I, _P, _P, _P, _I, _F, _I, _P, _P],
     "x0ne_gemm_bf16_tcgen05": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _P],
@@ -351,14 +352,17 @@ def attention_decode_scratch_bytes(n_rows: int, q_heads: int, kv_heads: int, hea
 
 
 ATTENTION_DECODE_CLUSTER_SPLITS = 8     # splits that can merge inside one thread-block cluster
+ATTENTION_DECODE_MAX_SPLITS = 64        # blocks per (sequence, kv head) the kernel takes
 
 
 def attention_decode_bf16(q: torch.Tensor, out: torch.Tensor, cache: PagedCacheArg, row_slot: torch.Tensor,
                           row_pos: torch.Tensor, n_rows: int, q_heads: int, scale: float, window: int, splits: int,
-                          scratch: Optional[torch.Tensor]) -> None:
+                          scratch: Optional[torch.Tensor], groups: int = 1) -> None:
     """Split-KV flash decoding: one query row per sequence.  `scratch` (uint8, zero when first
     used; the kernel leaves its counters at zero) holds the partial results when splits > 1; without
-    it (and with at most 8 splits) the splits merge inside a thread-block cluster instead."""
+    it (and with at most 8 splits) the splits merge inside a thread-block cluster instead.  With
+    `groups` > 1 the splits are `groups` clusters of splits / groups blocks (2 to 8): each cluster
+    merges in shared memory and the clusters' results meet in `scratch` (sized for `groups` parts)."""
     lib = _lib("fast")
     _need(q, torch.bfloat16, "q")
     _need(out, torch.bfloat16, "attention output")
@@ -373,6 +377,11 @@ def attention_decode_bf16(q: torch.Tensor, out: torch.Tensor, cache: PagedCacheA
     if scratch is not None:
         _need(scratch, torch.uint8, "decode scratch")
         nbytes = scratch.numel()
+    if groups > 1:
+        _check(lib, lib.x0ne_attention_decode_grouped_bf16(
+            _ptr(q), _ptr(out), cache, _ptr(row_slot), _ptr(row_pos), n_rows, q_heads, scale,
+            window, splits, groups, _ptr(scratch), nbytes, _stream()), "attention_decode_grouped_bf16")
+        return
     _check(lib, lib.x0ne_attention_decode_bf16(
         _ptr(q), _ptr(out), cache, _ptr(row_slot), _ptr(row_pos), n_rows, q_heads, scale,
         window, splits, _ptr(scratch), nbytes, _stream()), "attention_decode_bf16")

@@ -19,9 +19,15 @@ def run_attention(ctx, q, out, view, n_rows, q_heads, scale, window):
     if not ops.fast_attention_takes(view, q.dtype):
         ops.attention_rows(q, out, view, ctx.row_slot, ctx.row_pos, n_rows, q_heads, scale, window)
     elif ctx.decode:
-        # up to 8 splits merge inside a thread-block cluster and need no scratch
-        splits = decode_splits(ctx, n_rows, view.kv_heads, q_heads, view.head_dim)
-        ops.attention_decode_bf16(q, out, view, ctx.row_slot, ctx.row_pos, n_rows, q_heads, scale, window, splits, None)
+        # up to 8 splits merge inside a thread-block cluster and need no scratch; several clusters
+        # per (sequence, kv head) leave one partial result each in a scratch of the workspace
+        splits, groups = decode_plan(ctx, n_rows, view.kv_heads, q_heads, view.head_dim)
+        scratch = None
+        if groups > 1:
+            # one size for every launch that can come this way, so that a captured graph's pointer stays good
+            scratch = ctx.ws.zeroed("attn.decode_parts", decode_scratch_bytes(ctx, view.kv_heads, q_heads, view.head_dim))
+        ops.attention_decode_bf16(q, out, view, ctx.row_slot, ctx.row_pos, n_rows, q_heads, scale, window, splits, scratch,
+                                  groups=groups)
     else:
         kernel = ops.attention_prefill_tcgen05 if ops.attention_tc_takes(view, q.dtype) else ops.attention_prefill_bf16
         kernel(q, out, view, ctx.tile_seq, ctx.tile_row0, ctx.n_tiles, ctx.seq_first_row, ctx.seq_slot, ctx.seq_pos0,
@@ -33,30 +39,77 @@ def run_attention(ctx, q, out, view, n_rows, q_heads, scale, window):
 # the split only has to be near the best one, and the same rule chose well at 1 to 256 sequences and
 # contexts of 1,024 to 17,408
 DECODE_BLOCK_FIXED_PAGES = 10
+# Several clusters per (sequence, kv head), measured at 1 and 2 sequences with 8 kv heads x 128 and
+# 4,096 to 32,768 keys (microseconds): a block that shares the GPU with few others takes 0.85 per
+# page (it waits for its own copies), with 256 blocks about 1.3 (they share the memory's
+# bandwidth); the meeting of the clusters' results in scratch costs 3.5 on top with clusters of 4
+# and 5.5 with clusters of 8, and half a microsecond more for every cluster past two.  One sequence
+# at 32,768 keys: one cluster of 8 54.8, four clusters of 8 31.4; at 4,096 keys 11.2 and 13.2.
+DECODE_PAGE_US_ALONE = 0.85
+DECODE_PAGE_US_PER_BLOCK = 0.0023       # per block past 64, at head_dim 128
+DECODE_GROUP_US = {4: 3.5, 8: 5.5}      # by cluster size
+DECODE_GROUP_MARGIN_US = 1.0
+DECODE_MAX_GROUPS = 4
 
 
-def decode_splits(ctx, n_rows: int, kv_heads: int, q_heads: int, head_dim: int) -> int:
-    """Into how many blocks each (sequence, kv head) of a decode pass is split.  The splits of one
-    are a thread-block cluster (at most 8) and merge through shared memory.  With `fit(s)` clusters
-    of s blocks running at once (asked of the runtime: clusters do not pack the GPU completely,
-    296 blocks but only 71 clusters of 4), a launch takes ceil(units / fit(s)) waves of blocks that
-    each walk pages / s pages and cost a fixed start and merge besides; the split with the shortest
-    total wins.  So a small batch is split until it fills the GPU once, and a batch of 48
-    sequences, whose 384 blocks would be 1.3 waves, is split in two (three shorter waves)."""
+def _fit(ctx, head_dim: int, cluster: int) -> int:
+    fit = ops.attention_decode_max_clusters(head_dim, cluster)
+    if fit <= 0:      # unknown: assume seven eighths of the resident blocks
+        resident = ops.attention_decode_blocks_per_sm() * ctx.sm_count
+        fit = max(1, (resident - resident // 8) // cluster)
+    return fit
+
+
+def decode_plan(ctx, n_rows: int, kv_heads: int, q_heads: int, head_dim: int) -> tuple:
+    """(splits, groups): into how many blocks each (sequence, kv head) of a decode pass is split, and
+    how many thread-block clusters those blocks form.  The blocks of a cluster (at most 8) merge
+    through shared memory.  With `fit(s)` clusters of s blocks running at once (asked of the runtime:
+    clusters do not pack the GPU completely, 296 blocks but only 71 clusters of 4), a launch takes
+    ceil(units / fit(s)) waves of blocks that each walk pages / s pages and cost a fixed start and
+    merge besides; the split with the shortest total wins.  So a small batch is split until it fills
+    the GPU once, and a batch of 48 sequences, whose 384 blocks would be 1.3 waves, is split in two
+    (three shorter waves).  Where even 8 splits leave most of the GPU idle (one or two sequences) and
+    the context is long, several clusters per (sequence, kv head) follow: their results meet in
+    scratch, which costs a few microseconds, so they are taken only where the shorter walk pays
+    for that by the measured times above, and only as many as run at once."""
     group_chunks = (q_heads // kv_heads + 15) // 16
     units = max(1, n_rows * kv_heads * group_chunks)
     pages = max(1, (ctx.max_context + 63) // 64)
     best, best_cost = 1, None
     for splits in range(1, min(pages, ops.ATTENTION_DECODE_CLUSTER_SPLITS) + 1):
-        fit = ops.attention_decode_max_clusters(head_dim, splits)
-        if fit <= 0:      # unknown: assume seven eighths of the resident blocks
-            resident = ops.attention_decode_blocks_per_sm() * ctx.sm_count
-            fit = max(1, (resident - resident // 8) // splits)
-        waves = -(-units // fit)
+        waves = -(-units // _fit(ctx, head_dim, splits))
         cost = waves * (pages / splits + DECODE_BLOCK_FIXED_PAGES)
         if best_cost is None or cost < best_cost - 1e-9:
             best, best_cost = splits, cost
-    return best
+    if best < ops.ATTENTION_DECODE_CLUSTER_SPLITS:
+        return best, 1
+
+    def page_us(blocks):
+        return DECODE_PAGE_US_ALONE + max(0, blocks - 64) * DECODE_PAGE_US_PER_BLOCK * head_dim / 128
+
+    plan, plan_us = (best, 1), -(-pages // best) * page_us(units * best) - DECODE_GROUP_MARGIN_US
+    for cluster, merge_us in DECODE_GROUP_US.items():
+        for groups in range(2, DECODE_MAX_GROUPS + 1):
+            splits = cluster * groups
+            if splits <= best or splits > pages or splits > ops.ATTENTION_DECODE_MAX_SPLITS or units * groups > _fit(ctx, head_dim, cluster):
+                continue
+            us = -(-pages // splits) * page_us(units * splits) + merge_us + 0.5 * (groups - 2)
+            if us < plan_us - 1e-9:
+                plan, plan_us = (splits, groups), us
+    return plan
+
+
+def decode_scratch_bytes(ctx, kv_heads: int, q_heads: int, head_dim: int) -> int:
+    """Scratch for the largest decode launch that decode_plan gives several clusters per (sequence,
+    kv head): those are the launches whose clusters all run at once."""
+    group_chunks = (q_heads // kv_heads + 15) // 16
+    rows = max(1, max(_fit(ctx, head_dim, c) for c in DECODE_GROUP_US) // (2 * kv_heads * group_chunks))
+    return ops.attention_decode_scratch_bytes(rows, q_heads, kv_heads, head_dim, DECODE_MAX_GROUPS)
+
+
+def decode_splits(ctx, n_rows: int, kv_heads: int, q_heads: int, head_dim: int) -> int:
+    """Blocks per (sequence, kv head) of a decode pass (see decode_plan)."""
+    return decode_plan(ctx, n_rows, kv_heads, q_heads, head_dim)[0]
 
 
 class GQAttention(Mixer):
