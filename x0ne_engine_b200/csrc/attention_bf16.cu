@@ -597,7 +597,6 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(DecodeArgs a, Pag
                 }
             }
         }
-        if (parts > 1) __threadfence();     // this block's share is visible before any block of the cluster counts itself in
         cluster_sync_all();      // nobody leaves while its shared memory may still be read
         if (parts == 1) return;
     }
@@ -615,6 +614,41 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(DecodeArgs a, Pag
     __syncthreads();
     if (!s_last) return;
     __threadfence();
+    if (parts <= 8) {
+        // Few parts: every thread asks for all it needs at once (the parts' maxima and sums of its
+        // row, and its four output values of every part), so the merge is one trip to L2; the sums
+        // are taken in the order of the parts, as below.
+        for (int e = tid; e < nheads * (HD / 4); e += 128) {
+            const int r = e / (HD / 4), d = (e % (HD / 4)) * 4;
+            const float2* pml = reinterpret_cast<const float2*>(a.part_ml + (qrow0 + r) * parts * 2);
+            const float* po = a.part_o + (qrow0 + r) * parts * HD + d;
+            float2 ml[8];
+            float4 v[8];
+#pragma unroll
+            for (int sp = 0; sp < 8; ++sp)
+                if (sp < parts) {
+                    ml[sp] = __ldcg(pml + sp);
+                    v[sp] = __ldcg(reinterpret_cast<const float4*>(po + sp * HD));
+                }
+            float M = -INFINITY;
+#pragma unroll
+            for (int sp = 0; sp < 8; ++sp)
+                if (sp < parts) M = fmaxf(M, ml[sp].x);
+            float L = 0.f;
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int sp = 0; sp < 8; ++sp)
+                if (sp < parts) {
+                    const float f = ml[sp].x == -INFINITY ? 0.f : exp2f(ml[sp].x - M);
+                    L += ml[sp].y * f;
+                    acc.x += v[sp].x * f; acc.y += v[sp].y * f; acc.z += v[sp].z * f; acc.w += v[sp].w * f;
+                }
+            const float il = 1.0f / L;
+            bf16* dst = a.out + (qrow0 + r) * HD + d;
+            *reinterpret_cast<uint2*>(dst) = make_uint2(pack_bf16(acc.x * il, acc.y * il), pack_bf16(acc.z * il, acc.w * il));
+        }
+        return;
+    }
     // Per (head, part) weights first, all loads in parallel, then every thread sums four
     // consecutive output values over the parts in their order.
     float* wgt = reinterpret_cast<float*>(ks);           // [16][parts]: exp2(m_s - M); then [16]: 1 / L

@@ -41,14 +41,15 @@ def run_attention(ctx, q, out, view, n_rows, q_heads, scale, window):
 DECODE_BLOCK_FIXED_PAGES = 10
 # Several clusters per (sequence, kv head), measured at 1 and 2 sequences with 8 kv heads x 128 and
 # 4,096 to 32,768 keys (microseconds): a block that shares the GPU with few others takes 0.85 per
-# page (it waits for its own copies), with 256 blocks about 1.3 (they share the memory's
-# bandwidth); the meeting of the clusters' results in scratch costs 3.5 on top with clusters of 4
-# and 5.5 with clusters of 8, and half a microsecond more for every cluster past two.  One sequence
-# at 32,768 keys: one cluster of 8 54.8, four clusters of 8 31.4; at 4,096 keys 11.2 and 13.2.
+# page (one SM takes in about 38 GB/s), with 256 blocks about 1.3 (they share the memory's
+# bandwidth); the meeting of the clusters' results in scratch costs 2.5 on top with clusters of 4
+# and 4.5 with clusters of 8, and a quarter more for every cluster past two.  One sequence at 32,768
+# keys: one cluster of 8 57.4, four clusters of 8 30.5; at 6,144 keys 15.0 and 13.3; at 4,096 11.7
+# and 12.4.
 DECODE_PAGE_US_ALONE = 0.85
 DECODE_PAGE_US_PER_BLOCK = 0.0023       # per block past 64, at head_dim 128
-DECODE_GROUP_US = {4: 3.5, 8: 5.5}      # by cluster size
-DECODE_GROUP_MARGIN_US = 1.0
+DECODE_GROUP_US = {4: 2.5, 8: 4.5}      # by cluster size
+DECODE_GROUP_MARGIN_US = 0.5
 DECODE_MAX_GROUPS = 4
 
 
@@ -93,7 +94,7 @@ def decode_plan(ctx, n_rows: int, kv_heads: int, q_heads: int, head_dim: int) ->
             splits = cluster * groups
             if splits <= best or splits > pages or splits > ops.ATTENTION_DECODE_MAX_SPLITS or units * groups > _fit(ctx, head_dim, cluster):
                 continue
-            us = -(-pages // splits) * page_us(units * splits) + merge_us + 0.5 * (groups - 2)
+            us = -(-pages // splits) * page_us(units * splits) + merge_us + 0.25 * (groups - 2)
             if us < plan_us - 1e-9:
                 plan, plan_us = (splits, groups), us
     return plan
