@@ -2,13 +2,14 @@
 
 Commands and their options follow the reference's own programs where it has them:
 
-  core-bench <model dir> [--lengths short,1k,4k] [--decode N] [--reps N] [--batch B] [--dtype D]
+  core-bench <model dir> [--lengths short,1k,4k,16-1024] [--decode N] [--reps N] [--batch B] [--dtype D]
       [--random-weights SEED] [--clock-trace]
       time to first token, prefill and decode rates and the gaps between tokens (p50 / p90 / p99, as
       x0ne-core/runtime/src/engine.rs:1106-1116 stamps them) per prompt length, one line
       `x0ne-bench-result: <JSON>` (x0ne-core/oracle/examples/core-bench.rs:6-16,420-436).  Exit code
       3 when two repetitions of a length gave different tokens
-      (x0ne-core/oracle/examples/core-perf.rs:85-89).  --clock-trace adds the SM clock during the
+      (x0ne-core/oracle/examples/core-perf.rs:85-89).  A length "16-1024" is an unequal batch: prompt
+      lengths uniform between the two ends, from a seed.  --clock-trace adds the SM clock during the
       last repetition (read through NVML, nothing is set): what the prompts' pass does to the clock
       and how long the first decode steps run at the lowered clock.
   roofline --config config.json --gpu <GB/s> --prompt P --generated N [--tok-s X] [--batch B]
@@ -64,6 +65,8 @@ def _stats(v):
 
 
 def _length_tokens(name: str, limit: int) -> int:
+    if "-" in name:                      # "16-1024": an unequal batch; the longest prompt sizes the run
+        return _length_tokens(name.split("-", 1)[1], limit)
     if name == "short":
         return 20
     if name == "max":
@@ -156,7 +159,12 @@ def cmd_core_bench(a) -> int:
     load_s = time.time() - t0
     results = []
     for name, n in zip(names, lens):
-        prompts = [synthetic_ids(n, vocab, 0x0C0E5EED + i) for i in range(a.batch)]
+        if "-" in name:                  # lengths uniform between the two ends, from the same generator as the ids
+            lo = _length_tokens(name.split("-", 1)[0], limit - a.decode)
+            each = [lo + v % (n - lo + 1) for v in synthetic_ids(a.batch, 1 << 30, 0x1E26)]
+        else:
+            each = [n] * a.batch
+        prompts = [synthetic_ids(k, vocab, 0x0C0E5EED + i) for i, k in enumerate(each)]
         ttft, prefill, decode, tokens, gaps = [], [], [], [], []
         first = None
         # two runs before the timed ones: the first launches a short prompt pass itself, the second
@@ -180,7 +188,7 @@ def cmd_core_bench(a) -> int:
                 ttft.append(rates[0]); prefill.append(rates[1]); decode.append(rates[2]); tokens.append(out.tokens)
                 gaps += st.token_gaps
         same = all(t == tokens[0] for t in tokens)
-        results.append({"name": name, "tokens": n, "source": "synthetic", "status": "ok" if same else "tokens differ",
+        results.append({"name": name, "tokens": n, "prompt_tokens": each, "source": "synthetic", "status": "ok" if same else "tokens differ",
                         "same_tokens": same,
                         "first": {"ttft_s": first[0], "prefill_tok_s": first[1], "decode_tok_s": first[2]},
                         "ttft_s": _stats(ttft), "prefill_tok_s": _stats(prefill), "decode_tok_s": _stats(decode),

@@ -151,20 +151,35 @@ __device__ __forceinline__ void copy16(bf16* d, const bf16* s) { *reinterpret_ca
 __device__ __forceinline__ void copy2(float* d, const float* s) { *reinterpret_cast<float2*>(d) = *reinterpret_cast<const float2*>(s); }
 __device__ __forceinline__ void copy2(bf16* d, const bf16* s) { *reinterpret_cast<uint32_t*>(d) = *reinterpret_cast<const uint32_t*>(s); }
 
-template <typename T>
+// ITS: how many sweeps of the block cover a row (1, 2 or VEC_IT).
+template <typename T, int ITS>
 __global__ void add_rmsnorm_vec_kernel(float* __restrict__ resid, const T* __restrict__ delta,
                                        const float* __restrict__ w, T* __restrict__ out,
                                        const int32_t* __restrict__ rows, int hidden, float eps) {
     __shared__ float sh[32];
-    pdl_prologue();
+    // The weight and the list of rows are older than any kernel still running: they are asked for
+    // before the wait for the kernel before this one, so that its end is followed by one trip to
+    // memory (the row) and not by two.  (With four sweeps the weight would not fit in the registers
+    // that 1,024 threads can have; it is read after the sum then.)
+    constexpr bool EARLY = ITS <= 2;
+    pdl_launch_dependents();
     const int64_t src = rows ? rows[blockIdx.x] : blockIdx.x;
+    float wv[EARLY ? ITS : 1][8];
+    if (EARLY) {
+#pragma unroll
+        for (int it = 0; it < ITS; ++it) {
+            const int i = (it * blockDim.x + threadIdx.x) * 8;
+            if (i < hidden) load8(w + i, wv[it]);
+        }
+    }
+    pdl_wait();
     float* r = resid + src * hidden;
     const T* d = delta ? delta + src * hidden : nullptr;
     T* o = out + (int64_t)blockIdx.x * hidden;
-    float v[VEC_IT][8];
+    float v[ITS][8];
     float ss = 0.f;
 #pragma unroll
-    for (int it = 0; it < VEC_IT; ++it) {
+    for (int it = 0; it < ITS; ++it) {
         const int i = (it * blockDim.x + threadIdx.x) * 8;
         if (i < hidden) {
             load8(r + i, v[it]);
@@ -182,16 +197,28 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ resid, const T* __res
     const float total = block_sum(ss, sh);
     const float scale = 1.0f / sqrtf(total / (float)hidden + eps);
 #pragma unroll
-    for (int it = 0; it < VEC_IT; ++it) {
+    for (int it = 0; it < ITS; ++it) {
         const int i = (it * blockDim.x + threadIdx.x) * 8;
         if (i < hidden) {
-            float wv[8], ov[8];
-            load8(w + i, wv);
+            float late[8], ov[8];
+            if (!EARLY) load8(w + i, late);
 #pragma unroll
-            for (int k = 0; k < 8; ++k) ov[k] = v[it][k] * scale * wv[k];
+            for (int k = 0; k < 8; ++k) ov[k] = v[it][k] * scale * (EARLY ? wv[EARLY ? it : 0][k] : late[k]);
             store8(o + i, ov);
         }
     }
+}
+
+template <typename T>
+static void launch_add_rmsnorm_vec(float* resid, const T* delta, const float* w, T* out, const int32_t* rows, int n_rows,
+                                   int hidden, float eps, int threads, cudaStream_t stream) {
+    const int sweeps = (hidden / 8 + threads - 1) / threads;
+    if (sweeps <= 1)
+        x0ne_launch(add_rmsnorm_vec_kernel<T, 1>, dim3(n_rows), dim3(threads), 0, stream, resid, delta, w, out, rows, hidden, eps);
+    else if (sweeps == 2)
+        x0ne_launch(add_rmsnorm_vec_kernel<T, 2>, dim3(n_rows), dim3(threads), 0, stream, resid, delta, w, out, rows, hidden, eps);
+    else
+        x0ne_launch(add_rmsnorm_vec_kernel<T, VEC_IT>, dim3(n_rows), dim3(threads), 0, stream, resid, delta, w, out, rows, hidden, eps);
 }
 
 X0NE_API int x0ne_add_rmsnorm(float* resid, const void* delta, const float* w, void* out, int dt,
@@ -204,9 +231,9 @@ X0NE_API int x0ne_add_rmsnorm(float* resid, const void* delta, const float* w, v
         if (threads > 1024) threads = 1024;
         if (hidden / 8 > 512 && hidden / 8 <= 1024) threads = 512;   // two sweeps of 512 rather than one of 1024
         if (dt == X0NE_F32)
-            x0ne_launch(add_rmsnorm_vec_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, resid, (const float*)delta, w, (float*)out, rows, hidden, eps);
+            launch_add_rmsnorm_vec<float>(resid, (const float*)delta, w, (float*)out, rows, n_rows, hidden, eps, threads, stream);
         else if (dt == X0NE_BF16)
-            x0ne_launch(add_rmsnorm_vec_kernel<bf16>, dim3(n_rows), dim3(threads), 0, stream, resid, (const bf16*)delta, w, (bf16*)out, rows, hidden, eps);
+            launch_add_rmsnorm_vec<bf16>(resid, (const bf16*)delta, w, (bf16*)out, rows, n_rows, hidden, eps, threads, stream);
         else
             X0NE_REQUIRE(false, "add_rmsnorm: unknown dtype tag %d", dt);
         X0NE_LAUNCH_CHECK();
@@ -387,7 +414,10 @@ __global__ void qk_norm_rope_kv_write_vec_kernel(const T* __restrict__ qkv, cons
     constexpr int LPH = HD / 16;        // lanes per head
     constexpr int HPW = 32 / LPH;       // heads per warp
     constexpr int HALF = HD / 2;
-    pdl_prologue();
+    // Positions, slots, the page table, the norm weights and the rotation table are older than any
+    // kernel still running; only q|k|v comes from the kernel before this one.  So everything but
+    // q|k|v is asked for before the wait: the end of the product is followed by one trip to memory.
+    pdl_launch_dependents();
     const int lane = threadIdx.x & 31;
     const int heads = q_heads + cache.kv_heads;
     const int64_t item = ((int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * HPW + lane / LPH;
@@ -400,6 +430,29 @@ __global__ void qk_norm_rope_kv_write_vec_kernel(const T* __restrict__ qkv, cons
     const T* src = qkv + (int64_t)row * (q_dim + 2 * kv_dim) + (is_q ? head * HD : q_dim + kh * HD);
     const float* nw = is_q ? norm_q : norm_k;
     const int pos = row_pos[row];
+    const bool writes = live && (is_q || write_kv);
+    T* dst = nullptr;
+    if (writes) {
+        if (is_q) {
+            dst = q_out + (int64_t)row * q_dim + head * HD;
+        } else {
+            const int64_t off = cache_row_offset(cache, row_slot[row], pos, kh, 0);
+            if (off >= 0) dst = (T*)cache.base + off;
+        }
+    }
+    float wa[8], wb[8], cs[8], sn[8];
+    if (nw) {
+        load8(nw + c, wa);
+        load8(nw + HALF + c, wb);
+    }
+    if (pos >= 0 && pos < table_positions) {
+        load8(rope_table + (int64_t)pos * HD + c, cs);
+        load8(rope_table + (int64_t)pos * HD + HALF + c, sn);
+    } else {        // a position the table does not cover
+#pragma unroll
+        for (int k = 0; k < 8; ++k) sincosf((float)pos * inv_freq[c + k], &sn[k], &cs[k]);
+    }
+    pdl_wait();
     float a[8], b[8];
     load8(src + c, a);
     load8(src + HALF + c, b);
@@ -408,34 +461,16 @@ __global__ void qk_norm_rope_kv_write_vec_kernel(const T* __restrict__ qkv, cons
     for (int k = 0; k < 8; ++k) ss += a[k] * a[k] + b[k] * b[k];
 #pragma unroll
     for (int o = 1; o < LPH; o <<= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-    if (!live || (!is_q && !write_kv)) return;
-    T* dst;
-    if (is_q) {
-        dst = q_out + (int64_t)row * q_dim + head * HD;
-    } else {
-        const int64_t off = cache_row_offset(cache, row_slot[row], pos, kh, 0);
-        if (off < 0) return;
-        dst = (T*)cache.base + off;
-    }
+    if (dst == nullptr) return;
     if (nw) {
         const float scale = 1.0f / sqrtf(ss / (float)HD + eps);
-        float wa[8], wb[8];
-        load8(nw + c, wa);
-        load8(nw + HALF + c, wb);
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
             a[k] = a[k] * scale * wa[k];
             b[k] = b[k] * scale * wb[k];
         }
     }
-    float cs[8], sn[8], ra[8], rb[8];
-    if (pos >= 0 && pos < table_positions) {
-        load8(rope_table + (int64_t)pos * HD + c, cs);
-        load8(rope_table + (int64_t)pos * HD + HALF + c, sn);
-    } else {        // a position the table does not cover
-#pragma unroll
-        for (int k = 0; k < 8; ++k) sincosf((float)pos * inv_freq[c + k], &sn[k], &cs[k]);
-    }
+    float ra[8], rb[8];
 #pragma unroll
     for (int k = 0; k < 8; ++k) {
         ra[k] = a[k] * cs[k] - b[k] * sn[k];

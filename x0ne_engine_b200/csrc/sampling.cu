@@ -128,7 +128,10 @@ __global__ void __launch_bounds__(SB, 1) sample_kernel(SampleIO io) {
     __shared__ int s_bi[32];
     __shared__ int s_pick;
     const int row = blockIdx.x, tid = threadIdx.x;
-    pdl_prologue();
+    // This kernel writes the next step's token and position at its very end, and kernels of the
+    // next step read positions and slots before they wait for their own predecessor.  So it does
+    // not let its successor start early: whatever follows starts when this kernel is complete.
+    pdl_wait();
     // the word in which this library's tensor-core kernels report a wait that ran out travels to
     // the host with the picks: one more int after the last row's token
     if (row == 0 && tid == 0 && io.status) io.out_token[gridDim.x] = *io.status;
