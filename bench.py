@@ -199,7 +199,7 @@ def main() -> int:
             live = list(range(batch))
             for _ in range(warmup):
                 runner.step(live)
-            g = runner.graphs[batch]
+            g = runner.last_graph
             start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             sampler = ClockSampler() if with_clocks else None
             if sampler:

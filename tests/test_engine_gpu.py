@@ -345,6 +345,36 @@ def test_one_and_two_long_sequences_decode_through_several_clusters_per_kv_head(
     assert again.tokens == out.tokens
 
 
+def test_decode_graphs_follow_the_context_across_a_bucket_boundary():
+    """Decode graphs are kept per (rows, context bucket), because a graph fixes how the attention
+    divides its work.  An engine sized for 16,384 positions generates after a prompt of 2,040 tokens
+    and a short one: the long sequence crosses 2,048 on the way, so two graphs serve the batch, and
+    every token must be the step function's (up to a top-2 margin within the bfloat16 tolerance)."""
+    from x0ne_engine_b200 import Engine, Model, Qwen3Config
+    cfg = Qwen3Config(hidden_size=64, intermediate_size=96, num_hidden_layers=2, num_attention_heads=4,
+                      num_key_value_heads=2, head_dim=32, vocab_size=300, max_position_embeddings=16384,
+                      rms_norm_eps=1e-6, rope_theta=1000000.0, tie_word_embeddings=False, dtype="bfloat16")
+    eng = Engine.random(cfg, seed=21, dtype="bfloat16", linear_std=0.05, norm_jitter=0.1, max_tokens=3 * 2176, max_slots=3)
+    assert eng.max_seq_len == 16384
+    a, b = prompts_for(cfg.vocab_size, [2040, 100], seed=31)
+    m = Model(eng, max_batch=2)
+    n_new = 24
+    out = m.generate([a, b], max_tokens=n_new, stop_token_ids=())
+    assert {k for k in m._generator._runner.graphs} >= {(2, 2048), (2, 4096)}
+    for prompt, got in zip((a, b), out.tokens):
+        assert len(got) == n_new
+        s = eng.new_sequence()
+        row = eng.step([s], [prompt]).cpu().numpy()[0]
+        for t in got:
+            top = np.sort(row)[-2:]
+            if t != int(np.argmax(row)):
+                assert top[1] - top[0] <= 2 * 0.05 * np.abs(row).max(), "a token of the replayed graphs left a clear argmax"
+                break
+            row = eng.step([s], [[t]]).cpu().numpy()[0]
+        eng.free_sequence(s)
+    assert m.generate([a, b], max_tokens=n_new, stop_token_ids=()).tokens == out.tokens
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name,lengths,n_new", [("A", [5, 11, 17], 8), ("B", [1, 7, 30, 64], 12)])
 @pytest.mark.parametrize("decode", ["graph", "eager"])

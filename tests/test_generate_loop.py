@@ -181,3 +181,15 @@ def test_a_status_word_behind_the_picks_fails_the_step_it_came_with():
     b._out_host[0][3] = 1 << 5
     with pytest.raises(KernelError, match=r"the prompts' step of this batch.*codes \[5\]"):
         b._read(6, 3)
+
+
+def test_context_buckets_of_the_decode_graphs():
+    """Decode graphs are kept per (rows, context bucket): powers of two from 2,048 up to the engine's limit."""
+    from x0ne_engine_b200.engine.decode import DECODE_CONTEXT_BUCKET_MIN, context_bucket
+    assert DECODE_CONTEXT_BUCKET_MIN == 2048
+    assert context_bucket(1, 40960) == 2048 and context_bucket(2048, 40960) == 2048
+    assert context_bucket(2049, 40960) == 4096 and context_bucket(8193, 40960) == 16384
+    assert context_bucket(33000, 40960) == 40960           # the last bucket is the limit itself
+    assert context_bucket(10, 512) == 512                  # an engine smaller than the smallest bucket
+    seen = {context_bucket(n, 40960) for n in range(1, 40961, 7)}
+    assert seen == {2048, 4096, 8192, 16384, 32768, 40960}

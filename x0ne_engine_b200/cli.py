@@ -244,7 +244,7 @@ def cmd_step_timeline(a) -> int:
         live = list(range(a.batch))
         for _ in range(5):
             runner.step(live)
-        g = runner.graphs[a.batch]
+        g = runner.last_graph
         s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         torch.cuda.synchronize()
         s.record()

@@ -14,7 +14,10 @@ once more than needed; the device has marked it finished where it could know (st
 and either way its extra pick is dropped.  So the GPU never waits for the host's decisions.
 
 When sequences finish, the live rows are compacted on the device and the graph of the smaller
-batch size is used.
+batch size is used.  A graph also fixes how the decode attention divides its work, which depends
+on how long the sequences are: graphs are kept per (batch size, context bucket), the bucket being
+the longest live sequence rounded up to a power of two, so an engine sized for 40,000 positions
+does not split a 500-token sequence as if it had 40,000 keys.
 
 What a captured step reads lives at fixed device addresses for the life of the `DeviceBatch`: the
 per-row arrays, and a stop-id list of fixed length (`STOP_IDS_ON_DEVICE` entries, unused ones -1)
@@ -25,7 +28,7 @@ not zero raises, naming the step.
 """
 from __future__ import annotations
 
-from typing import Dict, List, Optional, Sequence
+from typing import Dict, List, Optional, Sequence, Tuple
 
 import numpy as np
 import torch
@@ -39,6 +42,18 @@ from .generate import GenerationError, Row
 # Stop tokens the device itself ends a row on (all rows of a batch must share them).  A batch with
 # more, or with different ones per row, leaves them to the host, which decides every pick anyway.
 STOP_IDS_ON_DEVICE = 16
+
+
+# The smallest context bucket: below it the decode attention's division of work does not change.
+DECODE_CONTEXT_BUCKET_MIN = 2048
+
+
+def context_bucket(longest: int, limit: int) -> int:
+    """The power of two (at least DECODE_CONTEXT_BUCKET_MIN, at most `limit`) that holds `longest` positions."""
+    b = DECODE_CONTEXT_BUCKET_MIN
+    while b < longest:
+        b *= 2
+    return min(b, limit)
 
 
 def device_stop_ids(rows: Sequence[Row]) -> List[int]:
@@ -82,7 +97,8 @@ class DeviceBatch:
         self._per_row = [self.tokens, self.row_slot, self.row_pos, self.counter, self.finished, self.budget,
                          self.temperature, self.top_p, self.seed]
         self.stop_ids = torch.full((STOP_IDS_ON_DEVICE,), -1, **i32)
-        self.graphs: Dict[int, torch.cuda.CUDAGraph] = {}
+        self.graphs: Dict[Tuple[int, int], torch.cuda.CUDAGraph] = {}     # by (rows, context bucket)
+        self.last_graph: Optional[torch.cuda.CUDAGraph] = None            # the one the latest step replayed
         self.slots: List[int] = []
         self.rows: Sequence[Row] = ()
         self.live: List[int] = []
@@ -166,14 +182,17 @@ class DeviceBatch:
         if live != self.live:
             self._compact(live)
         n = len(live)
+        lengths = self.engine.cache.lengths
+        bucket = context_bucket(max(int(lengths[self.slots[i]]) for i in live) + 1, self.engine.max_seq_len)
         if self.cuda_graph:
-            g = self.graphs.get(n)
+            g = self.graphs.get((n, bucket))
             if g is None:
-                g = self._capture(n)
+                g = self._capture(n, bucket)
             g.replay()
+            self.last_graph = g
             self.graph_replays += 1
         else:
-            self._launch(n)
+            self._launch(n, bucket)
             self.eager_steps += 1
         for i in live:
             self.engine.cache.lengths[self.slots[i]] += 1
@@ -208,32 +227,34 @@ class DeviceBatch:
             t[:n] = t[idx]
         self.live = live
 
-    def _launch(self, n: int) -> None:
+    def _launch(self, n: int, max_context: int) -> None:
         eng = self.engine
         ctx = StepContext(n_rows=n, tokens=self.tokens, row_slot=self.row_slot, row_pos=self.row_pos,
                           dtype=eng.dtype, ws=eng.ws, cache=eng.cache, decode=True, n_seqs=n, max_seq_rows=1,
-                          max_context=eng.max_seq_len, seq_first_row=self.seq_first_row, seq_slot=self.row_slot,
+                          max_context=max_context, seq_first_row=self.seq_first_row, seq_slot=self.row_slot,
                           seq_pos0=self.row_pos, sm_count=eng.sm_count)
         eng.model.forward(ctx, self.want_rows, n, self.logits)
         self._sample(self.logits, n)
 
-    def _capture(self, n: int) -> torch.cuda.CUDAGraph:
-        """Captures the launches of one decode step of `n` rows.  The warm-up run before the capture
-        would advance the sequences, so their state is saved and restored around it."""
+    def _capture(self, n: int, max_context: int) -> torch.cuda.CUDAGraph:
+        """Captures the launches of one decode step of `n` rows whose sequences hold at most
+        `max_context` positions (more would still be computed rightly, only divided less well).  The
+        warm-up run before the capture would advance the sequences, so their state is saved and
+        restored around it."""
         saved = [t[:n].clone() for t in self._per_row]
         saved_out = self.out_token[:n].clone()      # (the status word behind them is not touched)
         torch.cuda.synchronize()
         before = ops.LAUNCHES
-        self._launch(n)            # lets libraries and the workspace finish their lazy set-up
+        self._launch(n, max_context)            # lets libraries and the workspace finish their lazy set-up
         self.launches_per_step = ops.LAUNCHES - before
         torch.cuda.synchronize()
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g):
-            self._launch(n)
+            self._launch(n, max_context)
         for t, s in zip(self._per_row, saved):
             t[:n] = s
         self.out_token[:n] = saved_out
         torch.cuda.synchronize()
         self.engine.ws.frozen = True      # the graph holds the buffers' addresses
-        self.graphs[n] = g
+        self.graphs[(n, max_context)] = g
         return g
