@@ -29,41 +29,6 @@ bool x0ne_pdl_enabled() {
 
 
 // ----------------------------------------------------------------------------------------
-// Embedding: resid[r] = f32(table[tokens[r]]); an id outside the table gives a zero row
-// (x0ne-core/kernels/cuda/embedding.cu:5-17).  The engine there copies the row and lets the
-// first add-norm add it to a zeroed residual (x0ne-core/runtime/src/engine.rs:744-745); here
-// the row is written straight into the float32 residual, which is the same value.
-// ----------------------------------------------------------------------------------------
-template <typename T>
-__global__ void embedding_kernel(const T* __restrict__ table, const int32_t* __restrict__ tokens,
-                                 float* __restrict__ resid, int hidden, int vocab) {
-    pdl_prologue();
-    const int row = blockIdx.x;
-    const int t = tokens[row];
-    float* dst = resid + (int64_t)row * hidden;
-    if (t < 0 || t >= vocab) {
-        for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = 0.f;
-        return;
-    }
-    const T* src = table + (int64_t)t * hidden;
-    for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = to_f32(src[i]);
-}
-
-X0NE_API int x0ne_embedding(const void* table, int dt, const int32_t* tokens, float* resid, int n_rows,
-                            int hidden, int vocab, cudaStream_t stream) {
-    X0NE_REQUIRE(n_rows >= 0 && hidden > 0 && vocab > 0, "embedding: rows %d hidden %d vocab %d", n_rows, hidden, vocab);
-    if (n_rows == 0) return 0;
-    const int block = hidden >= 1024 ? 256 : 128;
-    if (dt == X0NE_F32)
-        x0ne_launch(embedding_kernel<float>, dim3(n_rows), dim3(block), 0, stream, (const float*)table, tokens, resid, hidden, vocab);
-    else if (dt == X0NE_BF16)
-        x0ne_launch(embedding_kernel<bf16>, dim3(n_rows), dim3(block), 0, stream, (const bf16*)table, tokens, resid, hidden, vocab);
-    else
-        X0NE_REQUIRE(false, "embedding: unknown dtype tag %d", dt);
-    X0NE_LAUNCH_CHECK();
-}
-
-// ----------------------------------------------------------------------------------------
 // Residual add, then RMSNorm: r = resid + f32(delta) (one IEEE add, stored back);
 // out = T(r * rsqrt(mean(r^2) + eps) * w)  (x0ne-core/kernels/cuda/rmsnorm.cu:11-20; eps is
 // inside the root; the weight multiplies directly).  `delta` may be null (norm only).
@@ -610,3 +575,79 @@ X0NE_API int x0ne_swiglu(const void* gate_up, void* out, int dt, int n_rows, int
     }
     X0NE_LAUNCH_CHECK();
 }
+
+// ----------------------------------------------------------------------------------------
+// Embedding: resid[r] = f32(table[tokens[r]]); an id outside the table gives a zero row
+// (x0ne-core/kernels/cuda/embedding.cu:5-17).  The engine there copies the row and lets the
+// first add-norm add it to a zeroed residual (x0ne-core/runtime/src/engine.rs:744-745); here
+// the row is written straight into the float32 residual, which is the same value.
+// ----------------------------------------------------------------------------------------
+template <typename T>
+__global__ void embedding_kernel(const T* __restrict__ table, const int32_t* __restrict__ tokens,
+                                 float* __restrict__ resid, int hidden, int vocab) {
+    pdl_prologue();
+    const int row = blockIdx.x;
+    const int t = tokens[row];
+    float* dst = resid + (int64_t)row * hidden;
+    if (t < 0 || t >= vocab) {
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = 0.f;
+        return;
+    }
+    const T* src = table + (int64_t)t * hidden;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = to_f32(src[i]);
+}
+
+// The same with 16-byte accesses (hidden % 8 == 0, aligned rows): all of a row's loads are in flight
+// at once, where the loop above waits for memory once per 256 values (9.5 us for 8 rows of 4,096).
+template <typename T>
+__global__ void embedding_vec_kernel(const T* __restrict__ table, const int32_t* __restrict__ tokens,
+                                     float* __restrict__ resid, int hidden, int vocab) {
+    pdl_prologue();
+    const int row = blockIdx.x;
+    const int t = tokens[row];
+    float* dst = resid + (int64_t)row * hidden;
+    const bool none = t < 0 || t >= vocab;
+    const T* src = table + (int64_t)(none ? 0 : t) * hidden;
+    for (int i0 = threadIdx.x * 8; i0 < hidden; i0 += 4 * blockDim.x * 8) {
+        float v[4][8];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int i = i0 + u * blockDim.x * 8;
+            if (i < hidden && !none) load8(src + i, v[u]);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int i = i0 + u * blockDim.x * 8;
+            if (i < hidden) {
+                if (none) {
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) v[u][k] = 0.f;
+                }
+                store8(dst + i, v[u]);
+            }
+        }
+    }
+}
+
+X0NE_API int x0ne_embedding(const void* table, int dt, const int32_t* tokens, float* resid, int n_rows,
+                            int hidden, int vocab, cudaStream_t stream) {
+    X0NE_REQUIRE(n_rows >= 0 && hidden > 0 && vocab > 0, "embedding: rows %d hidden %d vocab %d", n_rows, hidden, vocab);
+    if (n_rows == 0) return 0;
+    const int block = hidden >= 1024 ? 256 : 128;
+    if (hidden % 8 == 0 && (((uintptr_t)table | (uintptr_t)resid) & 15) == 0 && (dt == X0NE_F32 || dt == X0NE_BF16)) {
+        const int threads = hidden / 8 >= 256 ? 256 : (hidden / 8 + 31) / 32 * 32;
+        if (dt == X0NE_F32)
+            x0ne_launch(embedding_vec_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, (const float*)table, tokens, resid, hidden, vocab);
+        else
+            x0ne_launch(embedding_vec_kernel<bf16>, dim3(n_rows), dim3(threads), 0, stream, (const bf16*)table, tokens, resid, hidden, vocab);
+        X0NE_LAUNCH_CHECK();
+    }
+    if (dt == X0NE_F32)
+        x0ne_launch(embedding_kernel<float>, dim3(n_rows), dim3(block), 0, stream, (const float*)table, tokens, resid, hidden, vocab);
+    else if (dt == X0NE_BF16)
+        x0ne_launch(embedding_kernel<bf16>, dim3(n_rows), dim3(block), 0, stream, (const bf16*)table, tokens, resid, hidden, vocab);
+    else
+        X0NE_REQUIRE(false, "embedding: unknown dtype tag %d", dt);
+    X0NE_LAUNCH_CHECK();
+}
+
