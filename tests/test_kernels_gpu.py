@@ -530,6 +530,46 @@ def test_decode_attention_bf16_long_contexts(splits):
 
 
 # ------------------------------------------------------------------------------------------ sampler
+@pytest.mark.parametrize("v", [5, 1000, 4099, 151936])
+@pytest.mark.parametrize("rows", [1, 8, 200])
+def test_sampler_with_the_many_block_search_for_the_largest_logit(v, rows):
+    """With a word of scratch per row the rows' largest logits are found by many blocks per row
+    first.  Same picks, greedy and sampled, with ties, a NaN row, a finished row and a row whose
+    start is not 16-byte aligned; the scratch is zero again afterwards."""
+    o = ops()
+    logits = rnd((rows, v), torch.float32, 61)                    # (5 and 4,099 logits: rows that start off 16-byte boundaries)
+    logits[0, v // 2] = logits[0, v - 1] = 40.0                   # tie: lowest index
+    if rows > 1:
+        logits[1, v // 3] = float("nan")
+    temp = torch.zeros(rows, dtype=torch.float32, device=DEV)
+    temp[2::3] = 0.8                                              # every third row is sampled
+    top_p = torch.full((rows,), 0.9, dtype=torch.float32, device=DEV)
+    seed = torch.arange(rows, dtype=torch.int64, device=DEV) + 5
+    results = []
+    for scratch in (None, torch.zeros(rows, dtype=torch.int64, device=DEV)):
+        out = torch.full((rows,), -9, dtype=torch.int32, device=DEV)
+        fin = torch.zeros(rows, dtype=torch.int32, device=DEV)
+        fin[rows - 1] = 1 if rows > 2 else 0
+        cnt = torch.zeros(rows, dtype=torch.int32, device=DEV)
+        nxt = torch.full((rows,), 7, dtype=torch.int32, device=DEV)
+        o.sample(logits, rows, out, temperature=temp, top_p=top_p, seed=seed, draw_counter=cnt, finished=fin,
+                 next_token=nxt, row_best=scratch)
+        results.append((out.clone(), fin.clone(), cnt.clone(), nxt.clone()))
+        if scratch is not None:
+            assert int(scratch.abs().sum()) == 0
+            o.sample(logits, rows, out, temperature=temp, top_p=top_p, seed=seed, draw_counter=cnt * 0, finished=fin * 0 + fin,
+                     next_token=nxt, row_best=scratch)          # a second step on the same scratch
+            assert int(scratch.abs().sum()) == 0
+    for a, b in zip(*results):
+        assert torch.equal(a, b)
+    out = results[0][0]
+    assert out[0] == v // 2
+    if rows > 1:
+        assert out[1] == -1
+    if rows > 2:
+        assert out[rows - 1] == -2
+
+
 def test_sampler_argmax_ties_nan_and_feedback():
     o = ops()
     v = 1000

@@ -42,7 +42,7 @@ class SampleIOArg(Structure):
     _fields_ = [("logits", c_void_p), ("temperature", c_void_p), ("top_p", c_void_p), ("seed", c_void_p),
                 ("draw_counter", c_void_p), ("stop_ids", c_void_p), ("finished", c_void_p), ("budget", c_void_p),
                 ("out_token", c_void_p), ("next_token", c_void_p), ("next_pos", c_void_p),
-                ("status", c_void_p), ("ld", c_int64), ("vocab", c_int32), ("n_stop", c_int32)]
+                ("status", c_void_p), ("row_best", c_void_p), ("ld", c_int64), ("vocab", c_int32), ("n_stop", c_int32)]
 
 
 _libs = {}
@@ -260,10 +260,12 @@ def gemm_f32_nt(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, m: int) -> No
 
 def sample(logits: torch.Tensor, n_rows: int, out_token: torch.Tensor, *, temperature=None, top_p=None, seed=None,
            draw_counter=None, stop_ids=None, finished=None, budget=None, next_token=None, next_pos=None,
-           status=None) -> None:
+           status=None, row_best=None) -> None:
     """Picks a token per logits row on the device (see sampling.cu for the rules).  `stop_ids` may
     be padded with -1 (no token has that id).  With `status` (one int32 on the device) the kernel
-    also copies that int to out_token[n_rows], so it reaches the host with the picks."""
+    also copies that int to out_token[n_rows], so it reaches the host with the picks.  With
+    `row_best` (one int64 per row, zero; left zero) a launch of many blocks per row finds the rows'
+    largest logits first, which one block per row takes 17 us for at a vocabulary of 151,936."""
     lib = _lib("core")
     _need(logits, torch.float32, "logits")
     _need(out_token, torch.int32, "token output")
@@ -281,14 +283,21 @@ def sample(logits: torch.Tensor, n_rows: int, out_token: torch.Tensor, *, temper
         _need(status, torch.int32, "status word")
         if out_token.numel() < n_rows + 1:
             raise KernelError("sample: no room for the status word after the picks")
+    if row_best is not None:
+        _need(row_best, torch.int64, "largest-logit scratch")
+        if row_best.numel() < n_rows:
+            raise KernelError("sample: largest-logit scratch shorter than the rows asked for")
     n_stop = 0
     if stop_ids is not None and stop_ids.numel() > 0:
         _need(stop_ids, torch.int32, "stop ids")
         n_stop = stop_ids.numel()
     io = SampleIOArg(_ptr(logits), _ptr(temperature), _ptr(top_p), _ptr(seed), _ptr(draw_counter),
                      _ptr(stop_ids if n_stop else None), _ptr(finished), _ptr(budget), _ptr(out_token),
-                     _ptr(next_token), _ptr(next_pos), _ptr(status), logits.stride(0), logits.shape[1], n_stop)
+                     _ptr(next_token), _ptr(next_pos), _ptr(status), _ptr(row_best), logits.stride(0), logits.shape[1], n_stop)
     _check(lib, lib.x0ne_sample(io, n_rows, _stream()), "sample")
+    if row_best is not None and n_rows > 0:
+        global LAUNCHES
+        LAUNCHES += 1        # that entry point launched two kernels
 
 
 # ---------------------------------------------------------------------------------------------

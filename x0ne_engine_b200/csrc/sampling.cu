@@ -1,6 +1,8 @@
 // Picking the next token of every sequence on the device: greedy, temperature, nucleus.
 //
-// One block of 1024 threads per logits row.  The pick also feeds the next decode step: it
+// One block of 1024 threads per logits row; where the caller gives a word per row of scratch, a
+// launch of many blocks per row finds each row's largest logit first (one block draws some 30 GB/s
+// from memory, which made 17 us of scanning for a vocabulary of 151,936).  The pick also feeds the next decode step: it
 // writes the token where that step reads it, advances the sequence's position and draw
 // counter, and marks the sequence finished on a stop token or a spent budget, so token and
 // position never leave the device between two steps (the library engine's decode graph ends
@@ -116,10 +118,51 @@ struct SampleIO {
     int32_t* next_token;         // [rows] or null: where the next step reads its token
     int32_t* next_pos;           // [rows] or null: advanced by one when the token will be fed
     const int32_t* status;       // null, or one int copied to out_token[rows] (the kernels' status word)
+    unsigned long long* row_best; // null, or [rows]: zero before and after; the rows' largest keys, found by row_best_kernel
     int64_t ld;
     int32_t vocab;
     int32_t n_stop;
 };
+
+#define ROW_BEST_NAN (~0ull)      // above every key: the row holds a NaN
+
+// Block (s, row) looks at its share of the row and leaves the largest key (or ROW_BEST_NAN) in
+// row_best[row] with an atomic maximum, which does not depend on the order of the blocks.
+__global__ void __launch_bounds__(SB) row_best_kernel(SampleIO io) {
+    __shared__ unsigned long long s_key[32];
+    pdl_prologue();
+    const int row = blockIdx.y, tid = threadIdx.x, part = blockIdx.x, parts = gridDim.x;
+    if (io.finished && io.finished[row]) return;
+    const float* x = io.logits + (int64_t)row * io.ld;
+    const int V = io.vocab;
+    unsigned long long best = 0ull;
+    bool nan = false;
+    auto look = [&](float v, int i) {
+        nan |= v != v;
+        const unsigned long long key = pick_key(v, i);
+        best = key > best ? key : best;
+    };
+    if ((reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+        const float4* x4 = reinterpret_cast<const float4*>(x);
+        const int n4 = V / 4;
+        const int lo = (int)(((int64_t)n4 * part) / parts), hi = (int)(((int64_t)n4 * (part + 1)) / parts);
+        for (int j = lo + tid; j < hi; j += SB) {
+            const float4 v = x4[j];
+            look(v.x, 4 * j);
+            look(v.y, 4 * j + 1);
+            look(v.z, 4 * j + 2);
+            look(v.w, 4 * j + 3);
+        }
+        if (part == 0)
+            for (int i = 4 * n4 + tid; i < V; i += SB) look(x[i], i);
+    } else {
+        const int lo = (int)(((int64_t)V * part) / parts), hi = (int)(((int64_t)V * (part + 1)) / parts);
+        for (int i = lo + tid; i < hi; i += SB) look(x[i], i);
+    }
+    if (nan) best = ROW_BEST_NAN;
+    best = block_reduce(best, s_key, OpMax(), 0ull);
+    if (tid == 0 && best != 0ull) atomicMax(io.row_best + row, best);
+}
 
 __global__ void __launch_bounds__(SB, 1) sample_kernel(SampleIO io) {
     __shared__ float shf[33];
@@ -137,7 +180,7 @@ __global__ void __launch_bounds__(SB, 1) sample_kernel(SampleIO io) {
     if (row == 0 && tid == 0 && io.status) io.out_token[gridDim.x] = *io.status;
     if (io.finished && io.finished[row]) {
         if (tid == 0) io.out_token[row] = -2;
-        return;
+        return;      // (row_best_kernel leaves a finished row's word alone: it is still zero)
     }
     const float* x = io.logits + (int64_t)row * io.ld;
     const int V = io.vocab;
@@ -154,20 +197,27 @@ __global__ void __launch_bounds__(SB, 1) sample_kernel(SampleIO io) {
     // four logits per load where the row starts on a 16-byte boundary (one block scans the whole row,
     // so what it has in flight decides the time: 24 us for 151,936 logits one by one); the maximum of
     // the keys does not depend on the order they are looked at
-    int done = 0;
-    if ((reinterpret_cast<uintptr_t>(x) & 15) == 0) {
-        const float4* x4 = reinterpret_cast<const float4*>(x);
-        const int n4 = V / 4;
-        for (int j = tid; j < n4; j += SB) {
-            const float4 v = x4[j];
-            look(v.x, 4 * j);
-            look(v.y, 4 * j + 1);
-            look(v.z, 4 * j + 2);
-            look(v.w, 4 * j + 3);
+    if (io.row_best) {      // found by the launch before this one; the word goes back to zero for the next step
+        best = io.row_best[row];
+        nan = best == ROW_BEST_NAN;
+        __syncthreads();
+        if (tid == 0) io.row_best[row] = 0ull;
+    } else {
+        int done = 0;
+        if ((reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+            const float4* x4 = reinterpret_cast<const float4*>(x);
+            const int n4 = V / 4;
+            for (int j = tid; j < n4; j += SB) {
+                const float4 v = x4[j];
+                look(v.x, 4 * j);
+                look(v.y, 4 * j + 1);
+                look(v.z, 4 * j + 2);
+                look(v.w, 4 * j + 3);
+            }
+            done = 4 * n4;
         }
-        done = 4 * n4;
+        for (int i = done + tid; i < V; i += SB) look(x[i], i);
     }
-    for (int i = done + tid; i < V; i += SB) look(x[i], i);
     const bool any_nan = __syncthreads_or(nan);
     if (any_nan) {
         if (tid == 0) {
@@ -312,6 +362,22 @@ X0NE_API int x0ne_sample(SampleIO io, int n_rows, cudaStream_t stream) {
     X0NE_REQUIRE(io.logits && io.out_token, "sample: null logits or output");
     X0NE_REQUIRE(io.n_stop == 0 || io.stop_ids, "sample: %d stop ids but no list", io.n_stop);
     if (n_rows == 0) return 0;
+    if (io.row_best) {
+        // enough blocks per row to put about two on every SM
+        int sms = 0, dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        int parts = sms > 0 ? (2 * sms + n_rows - 1) / n_rows : 1;
+        const int most = (io.vocab + 4 * SB - 1) / (4 * SB);        // a block should have a sweep of its own
+        if (parts > most) parts = most;
+        if (parts < 1) parts = 1;
+        X0NE_REQUIRE(n_rows <= 65535, "sample: %d rows in one launch (limit 65535)", n_rows);
+        x0ne_launch(row_best_kernel, dim3(parts, n_rows), dim3(SB), 0, stream, io);
+        if (cudaError_t e = cudaGetLastError()) {
+            x0ne_set_error("sample: launching the search for the largest logits failed: %s", cudaGetErrorString(e));
+            return (int)e;
+        }
+    }
     x0ne_launch(sample_kernel, dim3(n_rows), dim3(SB), 0, stream, io);
     X0NE_LAUNCH_CHECK();
 }

@@ -83,6 +83,7 @@ class DeviceBatch:
         self.temperature = torch.zeros(max_batch, dtype=torch.float32, device=dev)
         self.top_p = torch.ones(max_batch, dtype=torch.float32, device=dev)
         self.seed = torch.zeros(max_batch, dtype=torch.int64, device=dev)
+        self.row_best = torch.zeros(max_batch, dtype=torch.int64, device=dev)     # the sampler's scratch: zero between steps
         self.seq_first_row = torch.arange(max_batch + 1, **i32)
         self.want_rows = torch.arange(max_batch, **i32)
         self.logits = torch.empty((max_batch, engine.vocab_size), dtype=torch.float32, device=dev)
@@ -175,7 +176,7 @@ class DeviceBatch:
     def _sample(self, logits: torch.Tensor, n: int) -> None:
         ops.sample(logits, n, self.out_token, temperature=self.temperature, top_p=self.top_p, seed=self.seed,
                    draw_counter=self.counter, stop_ids=self.stop_ids, finished=self.finished, budget=self.budget,
-                   next_token=self.tokens, next_pos=self.row_pos, status=self.status)
+                   next_token=self.tokens, next_pos=self.row_pos, status=self.status, row_best=self.row_best)
 
     def _queue_step(self, live: List[int]) -> None:
         """Queues one decode step for `live` and the copy of its picks to the host."""
