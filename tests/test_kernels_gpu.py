@@ -454,10 +454,16 @@ def test_decode_attention_bf16(q_heads, kv_heads, hd, window, splits):
     want = plain_attention_over_cache(q.reshape(n, q_heads, hd), storage, table, slots, pos, q_heads, kv_heads, hd, window)
     vmax = float(storage.float().abs().max())
     assert (out.double().cpu() - want).abs().max() / vmax < BF16_EPS
-    if 1 < splits <= 8:      # without scratch the splits merge inside a thread-block cluster: the same sums in the same order
+    if 1 < splits <= 8:      # without scratch the splits merge inside a thread-block cluster
         out2 = torch.full_like(q, 55.0)
         o.attention_decode_bf16(q, out2, view, slots, pos, n, q_heads, 1 / math.sqrt(hd), window, splits, None)
-        assert torch.equal(out2, out)
+        # (the same sums in the same order, unless the launch is small enough for blocks of 8 warps,
+        # which add their warps' partial sums in another grouping)
+        assert (out2.double().cpu() - want).abs().max() / vmax < BF16_EPS
+        assert (out2.float() - out.float()).abs().max() / vmax < BF16_EPS
+        out3 = torch.full_like(q, 55.0)
+        o.attention_decode_bf16(q, out3, view, slots, pos, n, q_heads, 1 / math.sqrt(hd), window, splits, None)
+        assert torch.equal(out3, out2)
     group_chunks = (q_heads // kv_heads + 15) // 16
     counters = scratch[: n * kv_heads * group_chunks * 4].view(torch.int32)
     assert int(counters.abs().sum()) == 0

@@ -371,18 +371,24 @@ __device__ __forceinline__ void cluster_sync_all() {
 // writes the output itself, several leave one partial result each in global scratch and the last
 // block to arrive merges those (a long context at a small batch: 4 clusters of 8 put 256 blocks on
 // 8 kv heads).  Not CLUSTER: every block's partial result goes through scratch.
-template <int HD, int STAGES, bool CLUSTER>
-__global__ void __launch_bounds__(128) attention_decode_kernel(DecodeArgs a, PagedCache cache) {
+// WARPS: 4, or 8 for launches whose blocks have an SM each (one sequence): the second four warps
+// take every other page.  Inside a step the kernel starts early and has its first pages in shared
+// memory when q arrives; what the step then waits for is each warp's chain of dependent
+// instructions over its pages, and with 8 warps a warp has half as many.
+template <int HD, int STAGES, bool CLUSTER, int WARPS>
+__global__ void __launch_bounds__(32 * WARPS) attention_decode_kernel(DecodeArgs a, PagedCache cache) {
+    constexpr int THREADS = 32 * WARPS, NPAR = WARPS / 4;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     constexpr int LD = HD + PADE;
     bf16* qs = reinterpret_cast<bf16*>(smem_raw);   // [16][LD]
-    bf16* ks = qs + 16 * LD;                        // [4 warps][STAGES][K, V][16][LD]: each warp's own ring
+    bf16* ks = qs + 16 * LD;                        // [WARPS][STAGES][K, V][16][LD]: each warp's own ring
     __shared__ int s_last;
     // What the kernel before this one (the q/k-norm + RoPE + cache write of this step) produced is q
     // and the newest row of the cache.  Positions, slots, the page table and all older rows are
     // older than that, so the first slices are requested before waiting for it.
     pdl_launch_dependents();
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int kq = warp & 3, par = warp >> 2;       // which 16 keys of a page, and which pages (every NPAR-th from par)
     const int split = blockIdx.x, b = blockIdx.z;
     const int csize = CLUSTER ? a.splits / a.groups : 1;        // blocks of one cluster
     const int crank = CLUSTER ? split % csize : 0;
@@ -406,7 +412,7 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(DecodeArgs a, Pag
     // The page numbers of this block's range, read once (a lookup inside the loop would put a
     // dependent global load in front of every copy).
     __shared__ int s_page[DEC_MAX_PAGES];
-    for (int i = tid; i < n_pages && i < DEC_MAX_PAGES; i += 128) {
+    for (int i = tid; i < n_pages && i < DEC_MAX_PAGES; i += THREADS) {
         const int pg = cache.page_table[(int64_t)slot * cache.table_stride + ((p_lo + i) % cache.ring_pages)];
         s_page[i] = (pg >= 0 && pg < cache.n_pages) ? pg : -1;
     }
@@ -424,19 +430,21 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(DecodeArgs a, Pag
         return pg < 0 ? nullptr : (const bf16*)cache.base + (int64_t)pg * cache.page_stride + head_off;
     };
 
-    // Each warp streams its own 16 keys of every page (K and V rows 16 w .. 16 w + 15) through a
+    // Each warp streams its own 16 keys of its pages (K and V rows 16 kq .. 16 kq + 15) through a
     // private ring of STAGES slots: no block-wide barrier inside the loop, STAGES - 1 slices in flight.
+    const int my_pages = n_pages > par ? (n_pages - par + NPAR - 1) / NPAR : 0;
     bf16* wring = ks + warp * STAGES * 2 * 16 * LD;
-    auto load_slice = [&](int st, int i) {
+    auto load_slice = [&](int st, int j) {
+        const int i = par + NPAR * j;
         const bf16* kp = tile_ptr(i);
         bf16* kd = wring + (st * 2) * 16 * LD;
         bf16* vd = kd + 16 * LD;
-        const int first_pos = (p_lo + i) * PAGE + warp * 16;
+        const int first_pos = (p_lo + i) * PAGE + kq * 16;
 #pragma unroll
         for (int c = lane; c < 16 * CH; c += 32) {
             const int r = c / CH, k = c % CH;
             if (kp != nullptr && first_pos + r <= pos) {
-                const bf16* src = kp + (warp * 16 + r) * HD + k * 8;
+                const bf16* src = kp + (kq * 16 + r) * HD + k * 8;
                 cp_async16(kd + r * LD + k * 8, src);
                 cp_async16(vd + r * LD + k * 8, src + v_off);
             } else {
@@ -448,8 +456,8 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(DecodeArgs a, Pag
     bool waited = false;
 #pragma unroll
     for (int s = 0; s < STAGES - 1; ++s) {
-        if (s < n_pages) {
-            if (!waited && (p_lo + s + 1) * PAGE > pos) {    // the page that holds the newest row
+        if (s < my_pages) {
+            if (!waited && (p_lo + par + NPAR * s + 1) * PAGE > pos) {    // the page that holds the newest row
                 pdl_wait();
                 waited = true;
             }
@@ -458,7 +466,7 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(DecodeArgs a, Pag
         cp_async_commit();
     }
     if (!waited) pdl_wait();
-    for (int c = tid; c < 16 * CH; c += 128) {
+    for (int c = tid; c < 16 * CH; c += THREADS) {
         const int r = c / CH, k = c % CH;
         bf16* d = qs + r * LD + k * 8;
         if (r < nheads)
@@ -475,27 +483,26 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(DecodeArgs a, Pag
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
     uint32_t qf[HD / 16][4];
 
-    for (int it = 0; it < n_pages; ++it) {
-        if (it == 0) {
-            cp_async_wait<0>();  // the first slice and q (q is the last group of the prologue)
-            __syncthreads();     // q was copied by all warps
+    cp_async_wait<0>();  // the first slices and q (q is the last group of the prologue)
+    __syncthreads();     // q was copied by all warps
 #pragma unroll
-            for (int kk = 0; kk < HD / 16; ++kk) {
-                const int row = lane & 15, col = kk * 16 + ((lane >> 4) << 3);
-                ldsm_x4(qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3], qs + row * LD + col);
-            }
-        } else {
+    for (int kk = 0; kk < HD / 16; ++kk) {
+        const int row = lane & 15, col = kk * 16 + ((lane >> 4) << 3);
+        ldsm_x4(qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3], qs + row * LD + col);
+    }
+    for (int it = 0; it < my_pages; ++it) {
+        if (it > 0) {
             cp_async_wait<STAGES - 2>();
             __syncwarp();        // the slice was copied by all lanes of this warp; all have left the last one
         }
         {   // refill the slot that was consumed in the previous iteration
             const int nx = it + STAGES - 1;
-            if (nx < n_pages) load_slice(nx % STAGES, nx);
+            if (nx < my_pages) load_slice(nx % STAGES, nx);
             cp_async_commit();
         }
         const bf16* kb = wring + ((it % STAGES) * 2) * 16 * LD;
         const bf16* vb = kb + 16 * LD;
-        const int first_pos = (p_lo + it) * PAGE + warp * 16;
+        const int first_pos = (p_lo + par + NPAR * it) * PAGE + kq * 16;
         if (first_pos <= pos) {
             float s[2][4];
             qk_tile<HD, 2>(s, qf, kb, 0, lane);
@@ -518,49 +525,55 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(DecodeArgs a, Pag
     cp_async_wait<0>();
     __syncthreads();
 
-    // merge the 4 warps through shared memory (the K/V stages are free now)
-    float* mo = reinterpret_cast<float*>(ks);            // [4][16][HD]
-    float* mml = mo + 4 * 16 * HD;                       // [4][16][2]
-    float* xml = mml + 4 * 16 * 2;                       // [16][2]: this block's (m, l) for the cluster; its o is mo[0]
+    // merge the warps through shared memory (the K/V stages are free now).  Rows of the group that
+    // hold no head are not written; a row takes HD + 8 floats, so that the rows of a warp's
+    // fragment fall into different banks; every thread then merges four consecutive values
+    // (1.3-1.9 us of a launch went to this step when it wrote all 16 rows value by value).
+    constexpr int MOS = HD + 8;
+    float* mo = reinterpret_cast<float*>(ks);            // [WARPS][16][MOS]
+    float* mml = mo + WARPS * 16 * MOS;                  // [WARPS][16][2]
+    float* xml = mml + WARPS * 16 * 2;                   // [16][2]: this block's (m, l) for the cluster; its o is mo[0]
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
         const int r = (lane >> 2) + 8 * h;
+        if (r < nheads) {
 #pragma unroll
-        for (int n = 0; n < HD / 8; ++n) {
-            float* d = mo + (warp * 16 + r) * HD + n * 8 + ((lane & 3) << 1);
-            d[0] = o[n][2 * h];
-            d[1] = o[n][2 * h + 1];
-        }
-        if ((lane & 3) == 0) {
-            mml[(warp * 16 + r) * 2] = m[h];
-            mml[(warp * 16 + r) * 2 + 1] = l[h];
+            for (int n = 0; n < HD / 8; ++n)
+                *reinterpret_cast<float2*>(mo + (warp * 16 + r) * MOS + n * 8 + ((lane & 3) << 1)) = make_float2(o[n][2 * h], o[n][2 * h + 1]);
+            if ((lane & 3) == 0) {
+                mml[(warp * 16 + r) * 2] = m[h];
+                mml[(warp * 16 + r) * 2 + 1] = l[h];
+            }
         }
     }
     __syncthreads();
     const int64_t qrow0 = (int64_t)b * a.q_heads + head0;
-    for (int e = tid; e < nheads * HD; e += 128) {
-        const int r = e / HD, d = e % HD;
+    for (int e = tid; e < nheads * (HD / 4); e += THREADS) {
+        const int r = e / (HD / 4), d = (e % (HD / 4)) * 4;
         float M = -INFINITY;
 #pragma unroll
-        for (int w = 0; w < 4; ++w) M = fmaxf(M, mml[(w * 16 + r) * 2]);
-        float acc = 0.f, L = 0.f;
+        for (int w = 0; w < WARPS; ++w) M = fmaxf(M, mml[(w * 16 + r) * 2]);
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        float L = 0.f;
 #pragma unroll
-        for (int w = 0; w < 4; ++w) {
+        for (int w = 0; w < WARPS; ++w) {
             const float mw = mml[(w * 16 + r) * 2];
             const float f = mw == -INFINITY ? 0.f : exp2f(mw - M);
-            acc += mo[(w * 16 + r) * HD + d] * f;
+            const float4 v = *reinterpret_cast<const float4*>(mo + (w * 16 + r) * MOS + d);
+            acc.x += v.x * f; acc.y += v.y * f; acc.z += v.z * f; acc.w += v.w * f;
             L += mml[(w * 16 + r) * 2 + 1] * f;
         }
         if (a.splits == 1) {
-            a.out[(qrow0 + r) * HD + d] = __float2bfloat16_rn(acc / L);
+            *reinterpret_cast<uint2*>(a.out + (qrow0 + r) * HD + d) =
+                make_uint2(pack_bf16(acc.x / L, acc.y / L), pack_bf16(acc.z / L, acc.w / L));
         } else if (CLUSTER) {
-            mo[r * HD + d] = acc;      // over the first warp's value of the same element, which only this thread read
+            *reinterpret_cast<float4*>(mo + r * MOS + d) = acc;      // over the first warp's values of the same elements, which only this thread read
             if (d == 0) {
                 xml[r * 2] = M;
                 xml[r * 2 + 1] = L;
             }
         } else {
-            a.part_o[((qrow0 + r) * parts + part) * HD + d] = acc;
+            *reinterpret_cast<float4*>(a.part_o + ((qrow0 + r) * parts + part) * HD + d) = acc;
             if (d == 0) {
                 a.part_ml[((qrow0 + r) * parts + part) * 2] = M;
                 a.part_ml[((qrow0 + r) * parts + part) * 2 + 1] = L;
@@ -571,7 +584,7 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(DecodeArgs a, Pag
     if constexpr (CLUSTER) {
         // Every block of the cluster takes a share of the output and sums the cluster's splits in their order.
         cluster_sync_all();
-        for (int e = crank * 128 + tid; e < nheads * (HD / 4); e += 128 * csize) {
+        for (int e = crank * THREADS + tid; e < nheads * (HD / 4); e += THREADS * csize) {
             const int r = e / (HD / 4), d = (e % (HD / 4)) * 4;
             float M = -INFINITY;
             for (int sp = 0; sp < csize; ++sp) M = fmaxf(M, ld_dsmem(dsmem_addr(xml + r * 2, sp)));
@@ -581,7 +594,7 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(DecodeArgs a, Pag
                 const float ms = ld_dsmem(dsmem_addr(xml + r * 2, sp));
                 const float f = ms == -INFINITY ? 0.f : exp2f(ms - M);
                 L += ld_dsmem(dsmem_addr(xml + r * 2 + 1, sp)) * f;
-                const float4 v = ld_dsmem4(dsmem_addr(mo + r * HD + d, sp));
+                const float4 v = ld_dsmem4(dsmem_addr(mo + r * MOS + d, sp));
                 acc.x += v.x * f; acc.y += v.y * f; acc.z += v.z * f; acc.w += v.w * f;
             }
             if (parts == 1) {
@@ -618,7 +631,7 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(DecodeArgs a, Pag
         // Few parts: every thread asks for all it needs at once (the parts' maxima and sums of its
         // row, and its four output values of every part), so the merge is one trip to L2; the sums
         // are taken in the order of the parts, as below.
-        for (int e = tid; e < nheads * (HD / 4); e += 128) {
+        for (int e = tid; e < nheads * (HD / 4); e += THREADS) {
             const int r = e / (HD / 4), d = (e % (HD / 4)) * 4;
             const float2* pml = reinterpret_cast<const float2*>(a.part_ml + (qrow0 + r) * parts * 2);
             const float* po = a.part_o + (qrow0 + r) * parts * HD + d;
@@ -653,7 +666,7 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(DecodeArgs a, Pag
     // consecutive output values over the parts in their order.
     float* wgt = reinterpret_cast<float*>(ks);           // [16][parts]: exp2(m_s - M); then [16]: 1 / L
     float* inv_l = wgt + 16 * parts;
-    for (int e = tid; e < nheads * parts; e += 128) {
+    for (int e = tid; e < nheads * parts; e += THREADS) {
         const int r = e / parts, sp = e % parts;
         wgt[r * parts + sp] = __ldcg(a.part_ml + ((qrow0 + r) * parts + sp) * 2);
     }
@@ -671,7 +684,7 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(DecodeArgs a, Pag
         inv_l[tid] = 1.0f / L;
     }
     __syncthreads();
-    for (int e = tid; e < nheads * (HD / 4); e += 128) {
+    for (int e = tid; e < nheads * (HD / 4); e += THREADS) {
         const int r = e / (HD / 4), d = (e % (HD / 4)) * 4;
         const float* po = a.part_o + (qrow0 + r) * parts * HD + d;
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -711,15 +724,52 @@ static int launch_prefill(const PrefillArgs& a, const PagedCache& cache, int n_t
 
 #define DECODE_STAGES 3
 #define DECODE_CLUSTER_MAX 8      // the largest cluster every launch may ask for
-template <int HD, bool CLUSTER>
-static int launch_decode_variant(const DecodeArgs& a, const PagedCache& cache, int n_rows, cudaStream_t stream) {
-    size_t smem = (size_t)(16 + 4 * DECODE_STAGES * 2 * 16) * (HD + PADE) * sizeof(bf16);
-    const size_t merge = (size_t)(4 * 16 * HD + 4 * 16 * 2 + 16 * 2) * sizeof(float);
+#define DECODE_WIDE_WARPS 8       // warps of a block that has an SM to itself
+
+template <int HD, int WARPS>
+static size_t decode_smem_bytes() {
+    size_t smem = (size_t)(16 + WARPS * DECODE_STAGES * 2 * 16) * (HD + PADE) * sizeof(bf16);
+    const size_t merge = (size_t)(WARPS * 16 * (HD + 8) + WARPS * 16 * 2 + 16 * 2) * sizeof(float);
     if (smem < 16 * (HD + PADE) * sizeof(bf16) + merge) smem = 16 * (HD + PADE) * sizeof(bf16) + merge;
+    return smem;
+}
+
+// How many clusters of `cluster` blocks of the kernel with this many warps run at once; 0 if unknown.
+template <int HD, int WARPS>
+static int decode_clusters_at_once(int cluster) {
+    const size_t smem = decode_smem_bytes<HD, WARPS>();
+    auto kernel = attention_decode_kernel<HD, DECODE_STAGES, true, WARPS>;
+    cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(cluster, 1024, 1);
+    cfg.blockDim = dim3(32 * WARPS);
+    cfg.dynamicSmemBytes = smem;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = cluster;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    return n;
+}
+
+template <int HD, bool CLUSTER, int WARPS>
+static int launch_decode_variant(const DecodeArgs& a, const PagedCache& cache, int n_rows, cudaStream_t stream) {
+    const size_t smem = decode_smem_bytes<HD, WARPS>();
     static OncePerDevice configured;
     if (configured.need()) {
-        cudaFuncSetAttribute(attention_decode_kernel<HD, DECODE_STAGES, CLUSTER>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
-        cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<HD, DECODE_STAGES, CLUSTER>,
+        cudaFuncSetAttribute(attention_decode_kernel<HD, DECODE_STAGES, CLUSTER, WARPS>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
+        cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<HD, DECODE_STAGES, CLUSTER, WARPS>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) {
             x0ne_set_error("attention_decode: cannot set %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
@@ -730,17 +780,36 @@ static int launch_decode_variant(const DecodeArgs& a, const PagedCache& cache, i
     const int G = a.q_heads / cache.kv_heads;
     dim3 grid(a.splits, cache.kv_heads * ((G + 15) / 16), n_rows);
     if (CLUSTER)
-        x0ne_launch_clusters(attention_decode_kernel<HD, DECODE_STAGES, CLUSTER>, dim3(grid), dim3(128), a.splits / a.groups, smem, stream, a, cache);
+        x0ne_launch_clusters(attention_decode_kernel<HD, DECODE_STAGES, CLUSTER, WARPS>, dim3(grid), dim3(32 * WARPS), a.splits / a.groups,
+                             smem, stream, a, cache);
     else
-        x0ne_launch(attention_decode_kernel<HD, DECODE_STAGES, CLUSTER>, dim3(grid), dim3(128), smem, stream, a, cache);
+        x0ne_launch(attention_decode_kernel<HD, DECODE_STAGES, CLUSTER, WARPS>, dim3(grid), dim3(32 * WARPS), smem, stream, a, cache);
     X0NE_LAUNCH_CHECK();
 }
 
 template <int HD>
 static int launch_decode(const DecodeArgs& a, const PagedCache& cache, int n_rows, cudaStream_t stream) {
-    if (a.cluster_merge && a.splits > 1 && a.splits / a.groups <= DECODE_CLUSTER_MAX)
-        return launch_decode_variant<HD, true>(a, cache, n_rows, stream);
-    return launch_decode_variant<HD, false>(a, cache, n_rows, stream);
+    const int cluster = a.splits / a.groups;
+    if (a.cluster_merge && a.splits > 1 && cluster <= DECODE_CLUSTER_MAX) {
+        // Eight warps per block where all clusters of the launch then still run at once (one block
+        // per SM: one sequence of a model with 8 kv heads); asked of the runtime once per device
+        // and cluster size.
+        static int wide_fit[64][DECODE_CLUSTER_MAX + 1];
+        static OncePerDevice asked[DECODE_CLUSTER_MAX + 1];
+        const int dev = OncePerDevice::device();
+        if (dev >= 0 && decode_smem_bytes<HD, DECODE_WIDE_WARPS>() <= 227 * 1024) {
+            if (asked[cluster].need()) {
+                wide_fit[dev][cluster] = decode_clusters_at_once<HD, DECODE_WIDE_WARPS>(cluster);
+                asked[cluster].done();
+            }
+            const int G = a.q_heads / cache.kv_heads;
+            const int64_t clusters = (int64_t)n_rows * cache.kv_heads * ((G + 15) / 16) * a.groups;
+            if (clusters <= wide_fit[dev][cluster])
+                return launch_decode_variant<HD, true, DECODE_WIDE_WARPS>(a, cache, n_rows, stream);
+        }
+        return launch_decode_variant<HD, true, 4>(a, cache, n_rows, stream);
+    }
+    return launch_decode_variant<HD, false, 4>(a, cache, n_rows, stream);
 }
 
 #define DISPATCH_HD(HDV, CALL)                     \
@@ -791,29 +860,7 @@ X0NE_API int x0ne_attention_decode_blocks_per_sm() { return DECODE_STAGES <= 2 ?
 // (sequences x kv heads x group chunks) within it so that a launch is one wave.
 template <int HD>
 static int decode_max_clusters(int splits) {
-    size_t smem = (size_t)(16 + 4 * DECODE_STAGES * 2 * 16) * (HD + PADE) * sizeof(bf16);
-    const size_t merge = (size_t)(4 * 16 * HD + 4 * 16 * 2 + 16 * 2) * sizeof(float);
-    if (smem < 16 * (HD + PADE) * sizeof(bf16) + merge) smem = 16 * (HD + PADE) * sizeof(bf16) + merge;
-    auto kernel = attention_decode_kernel<HD, DECODE_STAGES, true>;
-    cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
-    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return 0;
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(splits, 1024, 1);
-    cfg.blockDim = dim3(128);
-    cfg.dynamicSmemBytes = smem;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = splits;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    int n = 0;
-    if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess) {
-        cudaGetLastError();
-        return 0;
-    }
-    return n;
+    return decode_clusters_at_once<HD, 4>(splits);
 }
 
 X0NE_API int x0ne_attention_decode_max_clusters(int head_dim, int splits) {
